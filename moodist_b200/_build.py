@@ -1,0 +1,159 @@
+"""In-tree build of the native libraries (ninja + g++ + nvcc, sm_100a only).
+
+Three shared objects are produced beside this file:
+
+* ``libmoodist_b200.so`` — torch-free core: host runtime (store, transports, engine, queue, planners,
+  allocators, peer-memory mapper) and every CUDA kernel, with a plain C API.
+* ``_C.so`` — torch glue: c10d ``Backend``/``Store`` subclasses, allocator hooks, pybind11 bindings.
+* ``_serialize.so`` — the Python-object serializer (CPython C API).
+
+The reference builds the same three pieces with CMake (``CMakeLists.txt:150-293``); here a single
+torch/CUDA version is targeted so a generated ninja file is enough.  ``python -m moodist_b200._build``
+(re)builds whatever is out of date.
+"""
+
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+CSRC = ROOT / "csrc"
+BUILD = ROOT.parent / "build" / "native"
+
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+
+def _cuda_home() -> str:
+    for c in (os.environ.get("CUDA_HOME"), "/usr/local/cuda"):
+        if c and os.path.exists(os.path.join(c, "bin", "nvcc")):
+            return c
+    nvcc = shutil.which("nvcc")
+    if nvcc:
+        return str(Path(nvcc).resolve().parent.parent)
+    raise RuntimeError("nvcc not found")
+
+
+def _sources(sub: str, exts: tuple[str, ...]) -> list[Path]:
+    d = CSRC / sub
+    if not d.exists():
+        return []
+    return sorted(p for p in d.iterdir() if p.suffix in exts)
+
+
+def _q(s) -> str:
+    return str(s).replace(" ", "$ ")
+
+
+def generate(with_torch: bool = True) -> Path:
+    cuda = _cuda_home()
+    BUILD.mkdir(parents=True, exist_ok=True)
+    pyinc = sysconfig.get_paths()["include"]
+
+    cxx = os.environ.get("CXX", "g++")
+    common = f"-O2 -g1 -fPIC -std=c++20 -Wall -Wno-unused-function -pthread -I{CSRC} -I{cuda}/include"
+    nvcc_flags = (
+        " ".join(ARCH_FLAGS)
+        + f" -lineinfo -O3 -std=c++17 --expt-relaxed-constexpr -Xcompiler -fPIC -I{CSRC} -I{CSRC}/kernels"
+    )
+    lines = [
+        f"cxx = {cxx}",
+        f"nvcc = {cuda}/bin/nvcc",
+        f"cflags = {common}",
+        f"nvflags = {nvcc_flags}",
+        "rule cxx",
+        "  command = $cxx $cflags $extra -MMD -MF $out.d -c $in -o $out",
+        "  depfile = $out.d",
+        "  deps = gcc",
+        "rule nvcc",
+        "  command = $nvcc $nvflags -MD -MF $out.d -c $in -o $out",
+        "  depfile = $out.d",
+        "  deps = gcc",
+        "rule link",
+        "  command = $cxx -shared -o $out $in $ldflags",
+        "",
+    ]
+
+    core_objs = []
+    for src in _sources("core", (".cc",)):
+        obj = BUILD / "core" / (src.stem + ".o")
+        lines.append(f"build {_q(obj)}: cxx {_q(src)}")
+        core_objs.append(obj)
+    for src in _sources("kernels", (".cu",)):
+        obj = BUILD / "kernels" / (src.stem + ".o")
+        lines.append(f"build {_q(obj)}: nvcc {_q(src)}")
+        core_objs.append(obj)
+    core_lib = ROOT / "libmoodist_b200.so"
+    lines.append(f"build {_q(core_lib)}: link {' '.join(_q(o) for o in core_objs)}")
+    lines.append(f"  ldflags = -L{cuda}/lib64 -lcudart_static -lrt -ldl -pthread -Wl,--no-undefined")
+    targets = [core_lib]
+
+    ser_srcs = _sources("pyser", (".cc",))
+    if ser_srcs:
+        objs = []
+        for src in ser_srcs:
+            obj = BUILD / "pyser" / (src.stem + ".o")
+            lines.append(f"build {_q(obj)}: cxx {_q(src)}")
+            lines.append(f"  extra = -I{pyinc}")
+            objs.append(obj)
+        lib = ROOT / "_serialize.so"
+        lines.append(f"build {_q(lib)}: link {' '.join(_q(o) for o in objs)}")
+        lines.append("  ldflags = -pthread")
+        targets.append(lib)
+
+    glue_srcs = _sources("glue", (".cc",))
+    if with_torch and glue_srcs:
+        import torch
+        from torch.utils import cpp_extension
+
+        tinc = " ".join(f"-isystem {p}" for p in cpp_extension.include_paths())
+        tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
+        abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+        extra = (
+            f"{tinc} -isystem {pyinc} -D_GLIBCXX_USE_CXX11_ABI={abi} -DTORCH_EXTENSION_NAME=_C "
+            "-DTORCH_API_INCLUDE_EXTENSION_H -DUSE_C10D -Wno-deprecated-declarations -Wno-sign-compare"
+        )
+        objs = []
+        for src in glue_srcs:
+            obj = BUILD / "glue" / (src.stem + ".o")
+            lines.append(f"build {_q(obj)}: cxx {_q(src)}")
+            lines.append(f"  extra = {extra}")
+            objs.append(obj)
+        lib = ROOT / "_C.so"
+        lines.append(f"build {_q(lib)}: link {' '.join(_q(o) for o in objs)} | {_q(core_lib)}")
+        lines.append(
+            f"  ldflags = -L{ROOT} -lmoodist_b200 -L{tlib} -ltorch -ltorch_cpu -ltorch_python -lc10 "
+            f"-lc10_cuda -ltorch_cuda -Wl,-rpath,$$ORIGIN -Wl,-rpath,{tlib} -pthread"
+        )
+        targets.append(lib)
+
+    lines.append("default " + " ".join(_q(t) for t in targets))
+    path = BUILD / "build.ninja"
+    text = "\n".join(lines) + "\n"
+    if not path.exists() or path.read_text() != text:
+        path.write_text(text)
+    return path
+
+
+def build(with_torch: bool = True, verbose: bool = False) -> None:
+    """Build (incrementally) all native libraries for sm_100a."""
+    generate(with_torch)
+    jobs = os.environ.get("MOODIST_BUILD_JOBS", str(os.cpu_count() or 4))
+    cmd = [sys.executable, "-m", "ninja", "-C", str(BUILD), "-j", jobs]
+    if verbose:
+        cmd.append("-v")
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout[-20000:])
+        raise RuntimeError("native build failed")
+    if verbose:
+        print(r.stdout)
+
+
+if __name__ == "__main__":
+    build(with_torch="--no-torch" not in sys.argv, verbose="-v" in sys.argv)
+    print("built:", ", ".join(p.name for p in sorted(ROOT.glob("*.so"))))
