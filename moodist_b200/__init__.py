@@ -1,0 +1,47 @@
+"""moodist_b200: a Blackwell-native ``torch.distributed`` backend with the public API of moodist.
+
+Exports mirror the reference package (``py/moodist/__init__.py:62-89``).
+"""
+
+from queue import Empty
+
+from .version import __version__
+from ._core import (
+    MoodistProcessGroup,
+    MoodistBackend,
+    TcpStore,
+    serialize,
+    deserialize,
+    enable_profiling,
+    enable_cuda_allocator,
+    enable_cpu_allocator,
+    cpu_allocator_debug,
+    cuda_copy,
+    set_prefer_kernel_less,
+)
+from .backend import find_process_group, create_moodist_backend, get_backend, PreferKernelLessContext
+from .options import MoodistOptions, MoodistOptionsContext, install as _install_options
+
+_install_options(MoodistProcessGroup)
+
+__all__ = [
+    "__version__",
+    "MoodistProcessGroup",
+    "MoodistBackend",
+    "enable_profiling",
+    "enable_cuda_allocator",
+    "enable_cpu_allocator",
+    "cpu_allocator_debug",
+    "cuda_copy",
+    "set_prefer_kernel_less",
+    "TcpStore",
+    "serialize",
+    "deserialize",
+    "Empty",
+    "find_process_group",
+    "create_moodist_backend",
+    "get_backend",
+    "PreferKernelLessContext",
+    "MoodistOptions",
+    "MoodistOptionsContext",
+]

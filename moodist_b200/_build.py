@@ -8,7 +8,7 @@ Three shared objects are produced beside this file:
 * ``_serialize.so`` — the Python-object serializer (CPython C API).
 
 The reference builds the same three pieces with CMake (``CMakeLists.txt:150-293``); here a single
-torch/CUDA version is targeted so a generated ninja file is enough.  ``python -m moodist_b200._build``
+torch/CUDA version is targeted so a generated ninja file is enough.  ``python moodist_b200/_build.py``
 (re)builds whatever is out of date.
 """
 
@@ -127,7 +127,7 @@ def generate(with_torch: bool = True) -> Path:
         lines.append(f"build {_q(lib)}: link {' '.join(_q(o) for o in objs)} | {_q(core_lib)}")
         lines.append(
             f"  ldflags = -L{ROOT} -lmoodist_b200 -L{tlib} -ltorch -ltorch_cpu -ltorch_python -lc10 "
-            f"-lc10_cuda -ltorch_cuda -Wl,-rpath,$$ORIGIN -Wl,-rpath,{tlib} -pthread"
+            f"-lc10_cuda -ltorch_cuda -Wl,-rpath,'$$ORIGIN' -Wl,-rpath,{tlib} -pthread"
         )
         targets.append(lib)
 

@@ -1,0 +1,50 @@
+"""Loads the native extension modules.
+
+The reference picks one of several ``_C`` builds by torch version (``py/moodist/_core.py:13-27``) and
+tolerates missing optional symbols by exposing them as ``None`` (``:30-36``).  Here exactly one torch
+build is targeted; the extension is built in-tree (``python moodist_b200/_build.py``) and a missing
+build is an ImportError with the fix spelled out, never a silent fallback.
+"""
+
+from __future__ import annotations
+
+import importlib
+import os
+
+import torch
+import torch.distributed  # registers c10d's pybind types, which _C's classes derive from
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _load(name: str):
+    path = os.path.join(_HERE, name + ".so")
+    if not os.path.exists(path):
+        raise ImportError(
+            f"moodist_b200: native library {name}.so has not been built; run `python moodist_b200/_build.py`"
+        )
+    return importlib.import_module("moodist_b200." + name)
+
+
+_C = _load("_C")
+
+MoodistProcessGroup = _C.MoodistProcessGroup
+MoodistBackend = _C.MoodistBackend
+TcpStore = getattr(_C, "TcpStore", None)
+enable_profiling = getattr(_C, "enable_profiling", None)
+enable_cuda_allocator = getattr(_C, "enable_cuda_allocator", None)
+enable_cpu_allocator = getattr(_C, "enable_cpu_allocator", None)
+cpu_allocator_debug = getattr(_C, "cpu_allocator_debug", None)
+cuda_copy = getattr(_C, "cuda_copy", None)
+set_prefer_kernel_less = getattr(_C, "set_prefer_kernel_less", None)
+
+try:
+    _serialize = _load("_serialize")
+    serialize = _serialize.serialize
+    deserialize = _serialize.deserialize
+except ImportError:  # the serializer is a separate library; everything else works without it
+    _serialize = None
+    serialize = None
+    deserialize = None
+
+LIB_PATH = os.path.join(_HERE, "libmoodist_b200.so")

@@ -1,0 +1,274 @@
+#include "cuda_group.h"
+
+#include <cuda_runtime_api.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cstring>
+#include <mutex>
+
+#include "kernels/kernels_api.h"
+#include "log.h"
+#include "symm_heap.h"
+
+namespace moodist {
+namespace {
+
+void rt_check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) fail(std::string(what) + " failed: " + cudaGetErrorString(e));
+}
+#define RT_CHECK(x) rt_check((x), #x)
+
+const char* rc_name(int rc) {
+  switch (rc) {
+    case MB_ERR_ARG: return "unsupported argument combination";
+    case MB_ERR_ALIGN: return "misaligned pointer or pitch";
+    case MB_ERR_DRIVER: return "driver entry point unavailable";
+    case MB_ERR_LAUNCH: return "kernel launch failed";
+    case MB_ERR_TOO_BIG: return "message larger than the staging area";
+    default: return "unknown error";
+  }
+}
+
+std::string status_text(uint32_t st) {
+  uint32_t code = st & 0xffff, peer = st >> 16;
+  const char* what = "device-side failure";
+  switch (code) {
+    case 0x201: what = "timed out at entry waiting for a peer to finish the previous collective"; break;
+    case 0x202: what = "timed out waiting for a peer's data"; break;
+    case 0x203: what = "timed out waiting for a peer's address announcement"; break;
+    case 0x204: what = "timed out at exit waiting for a peer"; break;
+    case 0x101: what = "GEMM producer timed out"; break;
+    case 0x102: what = "GEMM MMA issuer timed out"; break;
+    case 0x103: what = "GEMM epilogue timed out"; break;
+    case 0x104: what = "fused all-gather GEMM timed out waiting for a shard"; break;
+    case 0x105: what = "GEMM drain timed out"; break;
+  }
+  return strf("moodist: collective failed on the device: %s (code 0x%x, peer rank %u)", what, code, peer);
+}
+
+class CudaGroupImpl final : public CudaGroup {
+ public:
+  CudaGroupImpl(KVStore& store, const std::string& key, int rank, int world, int device)
+      : key_(key), rank_(rank), world_(world), device_(device) {
+    if (world > MB_MAX_RANKS) fail(strf("moodist: CUDA groups support at most %d ranks per node", MB_MAX_RANKS));
+    RT_CHECK(cudaSetDevice(device));
+    RT_CHECK(cudaFree(nullptr));  // make sure the primary context exists
+    memset(&comm_, 0, sizeof(comm_));
+    comm_.rank = rank;
+    comm_.world = world;
+    comm_.wait_ns = (uint64_t)env_long("MOODIST_DEVICE_TIMEOUT_MS", 30000) * 1000000ull;
+    comm_.max_ctas = (int)env_long("MOODIST_MAX_CTAS", 0);
+    RT_CHECK(cudaHostAlloc((void**)&status_host_, 64, cudaHostAllocMapped));
+    memset((void*)status_host_, 0, 64);
+    void* dptr = nullptr;
+    RT_CHECK(cudaHostGetDevicePointer(&dptr, (void*)status_host_, 0));
+    comm_.status = (uint32_t*)dptr;
+    if (world > 1) {
+      size_t staging = (size_t)env_long("MOODIST_STAGING_MB", 1024) << 20;
+      heap_ = &SymmHeap::instance(device);
+      mem_ = heap_->attach_group(store, key, rank, world, staging, true);
+      attached_ = true;
+      for (int r = 0; r < world; ++r) {
+        comm_.peer[r] = mem_.heap_base[r];
+        comm_.stage[r] = mem_.stage[r];
+        comm_.flags[r] = mem_.flags[r];
+      }
+      comm_.staging_bytes = mem_.staging_bytes;
+      comm_.mc_stage = mem_.mc_stage;
+      comm_.mc_flags = mem_.mc_flags;
+    }
+    RT_CHECK(cudaEventCreateWithFlags(&order_, cudaEventDisableTiming));
+    log_verbose("cuda group %s rank %d/%d on device %d ready (nvls=%d)", key.c_str(), rank, world, device,
+                comm_.mc_stage != nullptr);
+  }
+
+  ~CudaGroupImpl() override {
+    cudaSetDevice(device_);
+    cudaDeviceSynchronize();
+    if (attached_) heap_->detach_group(key_);
+    if (order_) cudaEventDestroy(order_);
+    if (scratch_) cudaFree(scratch_);
+    if (status_host_) cudaFreeHost((void*)status_host_);
+  }
+
+  int rank() const override { return rank_; }
+  int world() const override { return world_; }
+  int device() const override { return device_; }
+  bool has_nvls() const override { return comm_.mc_stage != nullptr; }
+  GroupOptions& options() override { return opts_; }
+  const void* comm_struct() const override { return &comm_; }
+  uint64_t launches() const override { return launches_; }
+
+  uint32_t next_seq(CUstream_st* s) override {
+    check_status();
+    if (recorded_) RT_CHECK(cudaStreamWaitEvent(s, order_, 0));
+    return ++seq_;
+  }
+  void finish_op(CUstream_st* s) override {
+    RT_CHECK(cudaEventRecord(order_, s));
+    recorded_ = true;
+    ++launches_;
+  }
+
+  void* scratch(size_t bytes) override {
+    if (bytes > scratch_bytes_) {
+      if (scratch_) {
+        cudaDeviceSynchronize();
+        cudaFree(scratch_);
+      }
+      scratch_bytes_ = std::max<size_t>(bytes, 1 << 20);
+      RT_CHECK(cudaMalloc(&scratch_, scratch_bytes_));
+    }
+    return scratch_;
+  }
+
+  void check_status() override {
+    uint32_t st = *status_host_;
+    if (st != 0) {
+      *status_host_ = 0;
+      fail(status_text(st));
+    }
+  }
+
+  int64_t heap_off(const void* p, size_t bytes) const {
+    if (!heap_ || opts_.force_kernel_less == 2) return -1;
+    return heap_->offset_of(p, bytes);
+  }
+
+  void run(int rc, const char* what) {
+    if (rc != MB_OK) fail(strf("moodist: %s: %s", what, rc_name(rc)));
+  }
+
+  void all_gather(const void* in, void* out, size_t count, int idt, int odt, CUstream_st* s) override {
+    std::lock_guard<std::mutex> lk(mu_);
+    size_t osz = mb_dtype_size(odt), isz = mb_dtype_size(idt);
+    if (!osz || !isz) fail("moodist: all_gather: unsupported dtype");
+    if (count == 0) return;
+    int64_t off = idt == odt ? heap_off(in, count * isz) : -1;
+    size_t half = comm_.staging_bytes / 2;
+    size_t piece = count;
+    if (world_ > 1 && off < 0 && count * osz > half) piece = (half / osz) & ~(size_t)63;
+    for (size_t done = 0; done < count; done += piece) {
+      size_t n = std::min(piece, count - done);
+      uint32_t seq = next_seq(s);
+      run(mb_all_gather(&comm_, seq, (const uint8_t*)in + done * isz, off < 0 ? -1 : off + (int64_t)(done * isz),
+                        (uint8_t*)out + done * osz, n, count, idt, odt, s),
+          "all_gather");
+      finish_op(s);
+    }
+  }
+
+  void reduce_scatter(const void* in, void* out, size_t count, int idt, int odt, int op, float premul,
+                      CUstream_st* s) override {
+    std::lock_guard<std::mutex> lk(mu_);
+    size_t osz = mb_dtype_size(odt), isz = mb_dtype_size(idt);
+    if (!osz || !isz) fail("moodist: reduce_scatter: unsupported dtype");
+    if (count == 0) return;
+    int64_t off = heap_off(in, count * isz * world_);
+    size_t half = comm_.staging_bytes / 2;
+    size_t piece = count;
+    if (world_ > 1 && off < 0 && count * isz * world_ > half) piece = (half / (isz * world_)) & ~(size_t)63;
+    for (size_t done = 0; done < count; done += piece) {
+      size_t n = std::min(piece, count - done);
+      uint32_t seq = next_seq(s);
+      run(mb_reduce_scatter(&comm_, seq, (const uint8_t*)in + done * isz, off < 0 ? -1 : off + (int64_t)(done * isz),
+                            (uint8_t*)out + done * osz, n, count, idt, odt, op, premul, s),
+          "reduce_scatter");
+      finish_op(s);
+    }
+  }
+
+  void all_reduce(const void* in, void* out, size_t count, int dt, int op, float premul, CUstream_st* s) override {
+    std::lock_guard<std::mutex> lk(mu_);
+    size_t sz = mb_dtype_size(dt);
+    if (!sz) fail("moodist: all_reduce: unsupported dtype");
+    if (count == 0) return;
+    size_t half = comm_.staging_bytes / 2;
+    size_t oneshot_max = (size_t)env_long("MOODIST_AR_ONESHOT_BYTES", 256 * 1024);
+    // two-shot needs 2*world*chunk bytes of the half; keep pieces well inside
+    size_t piece = count;
+    if (world_ > 1 && count * sz * 2 + (size_t)world_ * 2 * 64 * sz > half)
+      piece = ((half / (2 * sz)) - (size_t)world_ * 128) & ~(size_t)63;
+    for (size_t done = 0; done < count; done += piece) {
+      size_t n = std::min(piece, count - done);
+      int variant = (n * sz <= oneshot_max) ? 0 : 1;
+      if (opts_.method == 0 || opts_.method == 1) variant = opts_.method;
+      uint32_t seq = next_seq(s);
+      run(mb_all_reduce(&comm_, seq, (const uint8_t*)in + done * sz, (uint8_t*)out + done * sz, n, dt, op, premul,
+                        variant, s),
+          "all_reduce");
+      finish_op(s);
+    }
+  }
+
+  void broadcast(void* data, size_t bytes, int root, CUstream_st* s) override {
+    std::lock_guard<std::mutex> lk(mu_);
+    if (bytes == 0 || world_ == 1) return;
+    size_t half = comm_.staging_bytes / 2;
+    size_t piece = std::min(bytes, half & ~(size_t)1023);
+    for (size_t done = 0; done < bytes; done += piece) {
+      size_t n = std::min(piece, bytes - done);
+      uint32_t seq = next_seq(s);
+      run(mb_broadcast(&comm_, seq, (uint8_t*)data + done, -1, n, root, s), "broadcast");
+      finish_op(s);
+    }
+  }
+
+  void all_to_all(const void* in, void* out, const uint64_t* send_off, const uint64_t* send_bytes,
+                  const uint64_t* recv_off, const uint64_t* recv_bytes, CUstream_st* s) override {
+    std::lock_guard<std::mutex> lk(mu_);
+    mb_a2a_table_t tab;
+    memset(&tab, 0, sizeof(tab));
+    size_t total = 0;
+    for (int r = 0; r < world_; ++r) {
+      tab.send_off[r] = send_off[r];
+      tab.send_bytes[r] = send_bytes[r];
+      tab.recv_off[r] = recv_off[r];
+      tab.recv_bytes[r] = recv_bytes[r];
+      total = std::max<size_t>(total, send_off[r] + send_bytes[r]);
+    }
+    int64_t off = heap_off(in, total);
+    uint32_t seq = next_seq(s);
+    run(mb_all_to_all(&comm_, seq, in, off, out, &tab, s), "all_to_all");
+    finish_op(s);
+  }
+
+  void barrier(CUstream_st* s) override {
+    std::lock_guard<std::mutex> lk(mu_);
+    uint32_t seq = next_seq(s);
+    run(mb_barrier(&comm_, seq, s), "barrier");
+    finish_op(s);
+  }
+
+  std::string describe() const override {
+    return strf("CudaGroup(%s, rank %d/%d, device %d, nvls=%d, seq=%u)", key_.c_str(), rank_, world_, device_,
+                (int)has_nvls(), seq_);
+  }
+
+ private:
+  std::string key_;
+  int rank_, world_, device_;
+  mb_comm_t comm_;
+  GroupOptions opts_;
+  SymmHeap* heap_ = nullptr;
+  GroupMemory mem_;
+  bool attached_ = false;
+  volatile uint32_t* status_host_ = nullptr;
+  cudaEvent_t order_ = nullptr;
+  bool recorded_ = false;
+  uint32_t seq_ = 0;
+  uint64_t launches_ = 0;
+  void* scratch_ = nullptr;
+  size_t scratch_bytes_ = 0;
+  std::mutex mu_;
+};
+
+}  // namespace
+
+std::unique_ptr<CudaGroup> CudaGroup::create(KVStore& store, const std::string& key, int rank, int world,
+                                             int device) {
+  return std::make_unique<CudaGroupImpl>(store, key, rank, world, device);
+}
+
+}  // namespace moodist

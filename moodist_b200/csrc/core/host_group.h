@@ -1,0 +1,100 @@
+// Host side of a process group: the progress engine ("moodist-cputhread") that owns the TCP data
+// plane, runs CPU-tensor collectives, the Queue protocol, compile_op execution across hosts, the
+// heartbeat and the coordinated shutdown. Needs no GPU and no CUDA library.
+//
+// Reference: core/cputhread.cc (engine + coroutine-style Work objects, :1080-1138, :6101-6340),
+// core/rdma_tcp.cc + core/tcpdev.cc (TCP emulation of one-sided RDMA), core/setup_comms.cc (bootstrap).
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <functional>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "kvstore.h"
+#include "wire.h"
+
+namespace moodist {
+
+// Engine message types. The numeric values are the ones the reference puts on the wire (they are the
+// source line numbers of its enum, core/cputhread.h:60-98), spelled out here as constants.
+enum OpType : uint32_t {
+  kOpBarrier = 60,
+  kOpInternalBarrier = 61,
+  kOpAllGatherCpu = 62,
+  kOpReduceScatterCpu = 63,
+  kOpBroadcastRingCpu = 64,
+  kOpGatherCpu = 65,
+  kOpAllToAllCpu = 66,  // not in the reference (its all_to_all is CUDA-only)
+  kOpAllGatherKernelLessCuda = 67,
+  kOpAllGatherLocalCuda = 68,
+  kOpReduceScatterKernelLessCuda = 72,
+  kOpBroadcastCuda = 75,
+  kOpReduceCuda = 76,
+  kOpAllToAllCuda = 77,
+  kOpBarrierCuda = 81,
+  kOpCreateQueue = 86,
+  kOpQueuePut = 87,
+  kOpQueueReadFinished = 88,
+  kOpQueueGet = 89,
+  kOpQueueTransaction = 90,
+  kOpCreateQueueNamed = 91,
+  kOpCreateQueueNamedResult = 92,
+  kOpCustom = 96,
+  kOpMessageShutdown = 98,
+  kOpHeartbeat = 99,    // the reference heartbeats with RDMA writes; over plain TCP it is a message
+  kOpScatterCpu = 100,  // not in the reference (scatter throws there)
+  kOpSendRecv = 101,    // point-to-point payloads (send/recv are unsupported in the reference)
+};
+
+struct TraceEvent {
+  std::string name;
+  int tid;
+  double ts_us;
+  double dur_us;
+};
+
+class HostGroup {
+ public:
+  static std::unique_ptr<HostGroup> create(KVStore& store, const std::string& key, int rank, int world);
+  virtual ~HostGroup() = default;
+
+  virtual int rank() const = 0;
+  virtual int world() const = 0;
+  virtual const std::string& name() const = 0;
+
+  // ---- blocking CPU-tensor collectives (the caller's thread sleeps on a futex-like wait while the
+  //      engine thread moves the data; reference: core/processgroup.cc:1088-1108) ----
+  virtual void all_gather(const void* in, void* out, size_t bytes) = 0;
+  virtual void reduce_scatter(const void* in, void* out, size_t count, int dtype, int op, double premul) = 0;
+  virtual void all_reduce(const void* in, void* out, size_t count, int dtype, int op, double premul) = 0;
+  virtual void broadcast(void* data, size_t bytes, int root) = 0;
+  virtual void gather(const void* in, void* out, size_t bytes, int root) = 0;
+  virtual void scatter(const void* in, void* out, size_t bytes, int root) = 0;
+  virtual void all_to_all(const void* in, void* out, const uint64_t* send_off, const uint64_t* send_bytes,
+                          const uint64_t* recv_off, const uint64_t* recv_bytes) = 0;
+  virtual void barrier() = 0;
+  virtual void send(const void* data, size_t bytes, int dst, uint32_t tag) = 0;
+  virtual void recv(void* data, size_t bytes, int src, uint32_t tag) = 0;
+
+  // ---- two-sided engine messages for subsystems layered on top (Queue, compile_op) ----
+  using Handler = std::function<void(int src, Reader& body)>;  // runs on the engine thread
+  virtual void set_handler(uint32_t op, Handler h) = 0;
+  virtual void send_message(int dst, uint32_t op, Bytes body) = 0;
+  // Post a closure to the engine thread.
+  virtual void run_on_engine(std::function<void()> fn) = 0;
+
+  // ---- health ----
+  virtual bool in_error() const = 0;
+  virtual std::string error_text() const = 0;
+  virtual void shutdown() = 0;  // coordinated: tells every peer, waits briefly for theirs
+
+  // ---- profiling (reference: core/cputhread.cc:1008-1078) ----
+  virtual void set_profiling(bool on) = 0;  // switching off writes moodist-trace-cpu-<group>-<rank>.json
+  virtual bool profiling() const = 0;
+  virtual std::string last_trace_path() const = 0;
+};
+
+}  // namespace moodist

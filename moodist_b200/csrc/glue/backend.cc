@@ -1,0 +1,552 @@
+#include "backend.h"
+
+#include <ATen/cuda/CUDAEvent.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/csrc/distributed/c10d/Types.hpp>
+#include <torch/csrc/distributed/c10d/NCCLUtils.hpp>
+
+#include <random>
+
+#include "core/log.h"
+#include "kernels/kernels_api.h"
+
+namespace moodist {
+namespace {
+
+// Work for stream-ordered CUDA collectives: "complete" as soon as it is created; wait() makes the
+// caller's current stream wait for the point in the launch stream where the collective ended.
+class CudaWork final : public c10d::Work {
+ public:
+  CudaWork(int rank, c10d::OpType op, std::vector<at::Tensor> outputs, c10::cuda::CUDAStream stream)
+      : c10d::Work(rank, op), outputs_(std::move(outputs)), device_(stream.device_index()) {
+    event_.record(stream);
+    future_ = c10::make_intrusive<at::ivalue::Future>(c10::ListType::create(c10::TensorType::get()),
+                                                      std::vector<c10::Device>{stream.device()});
+    future_->markCompleted(at::IValue(outputs_));
+  }
+  bool isCompleted() override { return true; }
+  bool isSuccess() const override { return true; }
+  bool wait(std::chrono::milliseconds) override {
+    auto cur = c10::cuda::getCurrentCUDAStream(device_);
+    event_.block(cur);
+    return true;
+  }
+  void synchronize() override { wait(std::chrono::milliseconds(0)); }
+  std::vector<at::Tensor> result() override { return outputs_; }
+  c10::intrusive_ptr<c10::ivalue::Future> getFuture() override { return future_; }
+
+ private:
+  std::vector<at::Tensor> outputs_;
+  c10::DeviceIndex device_;
+  at::cuda::CUDAEvent event_;
+  c10::intrusive_ptr<at::ivalue::Future> future_;
+};
+
+// CPU collectives block inside the call, so their Work is simply done.
+class DoneWork final : public c10d::Work {
+ public:
+  DoneWork(int rank, c10d::OpType op, std::vector<at::Tensor> outputs)
+      : c10d::Work(rank, op), outputs_(std::move(outputs)) {
+    future_ = c10::make_intrusive<at::ivalue::Future>(c10::ListType::create(c10::TensorType::get()));
+    future_->markCompleted(at::IValue(outputs_));
+  }
+  bool isCompleted() override { return true; }
+  bool isSuccess() const override { return true; }
+  bool wait(std::chrono::milliseconds) override { return true; }
+  void synchronize() override {}
+  std::vector<at::Tensor> result() override { return outputs_; }
+  c10::intrusive_ptr<c10::ivalue::Future> getFuture() override { return future_; }
+
+ private:
+  std::vector<at::Tensor> outputs_;
+  c10::intrusive_ptr<at::ivalue::Future> future_;
+};
+
+int dtype_code(at::ScalarType t) {
+  switch (t) {
+    case at::kByte: return MB_U8;
+    case at::kBool: return MB_U8;
+    case at::kChar: return MB_I8;
+    case at::kShort: return MB_I16;
+    case at::kInt: return MB_I32;
+    case at::kLong: return MB_I64;
+    case at::kHalf: return MB_F16;
+    case at::kFloat: return MB_F32;
+    case at::kDouble: return MB_F64;
+    case at::kBFloat16: return MB_BF16;
+    default: TORCH_CHECK(false, "moodist: unsupported dtype ", t);
+  }
+}
+
+// torch ReduceOp -> (kernel op code, premul factor)
+std::pair<int, double> reduce_code(const c10d::ReduceOp& op) {
+  switch (op.op_) {
+    case c10d::ReduceOp::SUM: return {MB_SUM, 1.0};
+    case c10d::ReduceOp::AVG: return {MB_AVG, 1.0};
+    case c10d::ReduceOp::MIN: return {MB_MIN, 1.0};
+    case c10d::ReduceOp::MAX: return {MB_MAX, 1.0};
+    case c10d::ReduceOp::PREMUL_SUM: {
+      // the factor travels in the same supplement type NCCL's backend uses (reference:
+      // wrapper/processgroup_wrapper.cc:41-53)
+      auto* sup = reinterpret_cast<c10d::NCCLPreMulSumSupplement*>(op.supplement_.get());
+      TORCH_CHECK(sup != nullptr, "moodist: PREMUL_SUM without a factor");
+      if (sup->tensor_factor.defined()) return {MB_PREMUL_SUM, sup->tensor_factor.item<double>()};
+      return {MB_PREMUL_SUM, sup->double_factor};
+    }
+    default: TORCH_CHECK(false, "moodist: unsupported reduce op (supported: SUM, AVG, MIN, MAX, PREMUL_SUM)");
+  }
+}
+
+void check_contig(const at::Tensor& t, const char* what) {
+  TORCH_CHECK(t.is_contiguous(), "moodist: ", what, " tensor must be contiguous");
+}
+
+std::string random_name() {
+  std::random_device rd;
+  uint64_t v = ((uint64_t)rd() << 32) ^ rd();
+  char buf[32];
+  snprintf(buf, sizeof(buf), "%016llx", (unsigned long long)v);
+  return buf;
+}
+
+CUstream_st* raw(const c10::cuda::CUDAStream& s) { return reinterpret_cast<CUstream_st*>(s.stream()); }
+
+}  // namespace
+
+#define MOODIST_TRANSLATE(body)                 \
+  try {                                         \
+    body                                        \
+  } catch (const moodist::Error& e) {           \
+    TORCH_CHECK(false, e.what());               \
+  }
+
+MoodistBackend::MoodistBackend(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size)
+    : c10d::Backend(rank, size), store_(store), kv_(std::make_unique<C10dStoreAdapter>(store)), rank_(rank),
+      size_(size) {
+  TORCH_CHECK(rank >= 0 && rank < size, "moodist: bad rank ", rank, " for world size ", size);
+  // rank 0 names the group; everyone learns it through the store (reference: core/processgroup.cc:977-1050)
+  if (rank == 0) {
+    name_ = random_name();
+    kv_->set_str("moodist_pg_key", name_);
+  } else {
+    name_ = kv_->get_str("moodist_pg_key");
+  }
+}
+
+MoodistBackend::~MoodistBackend() {
+  try {
+    if (host_) host_->shutdown();
+  } catch (...) {
+  }
+}
+
+CudaGroup& MoodistBackend::cudaGroup(int device) {
+  std::lock_guard<std::mutex> lk(mu_);
+  if (!cuda_) {
+    MOODIST_TRANSLATE(cuda_ = CudaGroup::create(*kv_, name_, rank_, size_, device);)
+    cuda_->options() = opts_;
+  }
+  TORCH_CHECK(cuda_->device() == device, "moodist: this process group is bound to cuda:", cuda_->device(),
+              " but got a tensor on cuda:", device);
+  return *cuda_;
+}
+
+HostGroup& MoodistBackend::hostGroup() {
+  std::lock_guard<std::mutex> lk(mu_);
+  if (!host_) {
+    MOODIST_TRANSLATE(host_ = HostGroup::create(*kv_, name_, rank_, size_);)
+  }
+  return *host_;
+}
+
+// ------------------------------------------------------------------------------------------------
+// collectives
+// ------------------------------------------------------------------------------------------------
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::_allgather_base(at::Tensor& output, at::Tensor& input,
+                                                               const c10d::AllgatherOptions&) {
+  check_contig(output, "all_gather output");
+  check_contig(input, "all_gather input");
+  TORCH_CHECK(output.device() == input.device(), "moodist: all_gather tensors must be on the same device");
+  TORCH_CHECK(output.scalar_type() == input.scalar_type(), "moodist: all_gather dtype mismatch");
+  TORCH_CHECK(output.numel() == input.numel() * size_, "moodist: all_gather output must be world_size x input");
+  if (input.is_cuda()) {
+    c10::cuda::CUDAGuard guard(input.device());
+    auto stream = c10::cuda::getCurrentCUDAStream();
+    int dt = dtype_code(input.scalar_type());
+    MOODIST_TRANSLATE(cudaGroup(input.get_device())
+                          .all_gather(input.data_ptr(), output.data_ptr(), input.numel(), dt, dt, raw(stream));)
+    return c10::make_intrusive<CudaWork>(rank_, c10d::OpType::_ALLGATHER_BASE, std::vector<at::Tensor>{output}, stream);
+  }
+  MOODIST_TRANSLATE(hostGroup().all_gather(input.data_ptr(), output.data_ptr(), input.nbytes());)
+  return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::_ALLGATHER_BASE, std::vector<at::Tensor>{output});
+}
+
+void MoodistBackend::allGatherCast(at::Tensor& output, const at::Tensor& input) {
+  check_contig(output, "all_gather output");
+  check_contig(input, "all_gather input");
+  TORCH_CHECK(input.is_cuda() && output.is_cuda(), "moodist: all_gather_cast needs CUDA tensors");
+  TORCH_CHECK(output.numel() == input.numel() * size_, "moodist: all_gather output must be world_size x input");
+  c10::cuda::CUDAGuard guard(input.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  MOODIST_TRANSLATE(cudaGroup(input.get_device())
+                        .all_gather(input.data_ptr(), output.data_ptr(), input.numel(),
+                                    dtype_code(input.scalar_type()), dtype_code(output.scalar_type()), raw(stream));)
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::allgather(std::vector<std::vector<at::Tensor>>& outputs,
+                                                         std::vector<at::Tensor>& inputs,
+                                                         const c10d::AllgatherOptions& opts) {
+  TORCH_CHECK(inputs.size() == 1 && outputs.size() == 1, "moodist: all_gather takes one tensor per rank");
+  auto& outs = outputs[0];
+  TORCH_CHECK((int)outs.size() == size_, "moodist: all_gather output list must have world_size entries");
+  at::Tensor in = inputs[0].contiguous();
+  // gather into one buffer, then hand the pieces out (reference: wrapper/processgroup_wrapper.cc:111-129)
+  at::Tensor flat = at::empty({size_ * in.numel()}, in.options());
+  auto work = _allgather_base(flat, in, opts);
+  if (in.is_cuda()) {
+    c10::cuda::CUDAGuard guard(in.device());
+    for (int r = 0; r < size_; ++r) outs[r].copy_(flat.narrow(0, r * in.numel(), in.numel()).view_as(in), true);
+    return c10::make_intrusive<CudaWork>(rank_, c10d::OpType::ALLGATHER, outs, c10::cuda::getCurrentCUDAStream());
+  }
+  for (int r = 0; r < size_; ++r) outs[r].copy_(flat.narrow(0, r * in.numel(), in.numel()).view_as(in));
+  return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::ALLGATHER, outs);
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::allgather_into_tensor_coalesced(std::vector<at::Tensor>& outputs,
+                                                                               std::vector<at::Tensor>& inputs,
+                                                                               const c10d::AllgatherOptions& opts) {
+  TORCH_CHECK(outputs.size() == inputs.size(), "moodist: coalesced all_gather list size mismatch");
+  c10::intrusive_ptr<c10d::Work> last;
+  for (size_t i = 0; i < inputs.size(); ++i) last = _allgather_base(outputs[i], inputs[i], opts);
+  if (!last) return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::ALLGATHER_COALESCED, outputs);
+  return last;
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::_reduce_scatter_base(at::Tensor& output, at::Tensor& input,
+                                                                    const c10d::ReduceScatterOptions& opts) {
+  check_contig(output, "reduce_scatter output");
+  check_contig(input, "reduce_scatter input");
+  TORCH_CHECK(output.device() == input.device(), "moodist: reduce_scatter tensors must be on the same device");
+  TORCH_CHECK(output.scalar_type() == input.scalar_type(), "moodist: reduce_scatter dtype mismatch");
+  TORCH_CHECK(input.numel() == output.numel() * size_, "moodist: reduce_scatter input must be world_size x output");
+  auto [op, premul] = reduce_code(opts.reduceOp);
+  int dt = dtype_code(input.scalar_type());
+  if (input.is_cuda()) {
+    c10::cuda::CUDAGuard guard(input.device());
+    auto stream = c10::cuda::getCurrentCUDAStream();
+    MOODIST_TRANSLATE(cudaGroup(input.get_device())
+                          .reduce_scatter(input.data_ptr(), output.data_ptr(), output.numel(), dt, dt, op,
+                                          (float)premul, raw(stream));)
+    return c10::make_intrusive<CudaWork>(rank_, c10d::OpType::_REDUCE_SCATTER_BASE, std::vector<at::Tensor>{output},
+                                         stream);
+  }
+  MOODIST_TRANSLATE(hostGroup().reduce_scatter(input.data_ptr(), output.data_ptr(), output.numel(), dt, op, premul);)
+  return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::_REDUCE_SCATTER_BASE, std::vector<at::Tensor>{output});
+}
+
+void MoodistBackend::reduceScatterCast(at::Tensor& output, const at::Tensor& input, int op, double premul) {
+  check_contig(output, "reduce_scatter output");
+  check_contig(input, "reduce_scatter input");
+  TORCH_CHECK(input.is_cuda() && output.is_cuda(), "moodist: reduce_scatter_cast needs CUDA tensors");
+  TORCH_CHECK(input.numel() == output.numel() * size_, "moodist: reduce_scatter input must be world_size x output");
+  c10::cuda::CUDAGuard guard(input.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  MOODIST_TRANSLATE(cudaGroup(input.get_device())
+                        .reduce_scatter(input.data_ptr(), output.data_ptr(), output.numel(),
+                                        dtype_code(input.scalar_type()), dtype_code(output.scalar_type()), op,
+                                        (float)premul, raw(stream));)
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::reduce_scatter(std::vector<at::Tensor>& outputs,
+                                                              std::vector<std::vector<at::Tensor>>& inputs,
+                                                              const c10d::ReduceScatterOptions& opts) {
+  TORCH_CHECK(outputs.size() == 1 && inputs.size() == 1, "moodist: reduce_scatter takes one output per rank");
+  TORCH_CHECK((int)inputs[0].size() == size_, "moodist: reduce_scatter input list must have world_size entries");
+  std::vector<at::Tensor> flat_list;
+  for (auto& t : inputs[0]) flat_list.push_back(t.reshape({-1}));
+  at::Tensor flat = at::cat(flat_list);
+  at::Tensor out = outputs[0];
+  check_contig(out, "reduce_scatter output");
+  return _reduce_scatter_base(out, flat, opts);
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::reduce_scatter_tensor_coalesced(
+    std::vector<at::Tensor>& outputs, std::vector<at::Tensor>& inputs, const c10d::ReduceScatterOptions& opts) {
+  TORCH_CHECK(outputs.size() == inputs.size(), "moodist: coalesced reduce_scatter list size mismatch");
+  c10::intrusive_ptr<c10d::Work> last;
+  for (size_t i = 0; i < inputs.size(); ++i) last = _reduce_scatter_base(outputs[i], inputs[i], opts);
+  if (!last) return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::REDUCE_SCATTER, outputs);
+  return last;
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::allreduce(std::vector<at::Tensor>& tensors,
+                                                         const c10d::AllreduceOptions& opts) {
+  TORCH_CHECK(tensors.size() == 1, "moodist: all_reduce takes one tensor");
+  at::Tensor& t = tensors[0];
+  check_contig(t, "all_reduce");
+  auto [op, premul] = reduce_code(opts.reduceOp);
+  int dt = dtype_code(t.scalar_type());
+  if (t.is_cuda()) {
+    c10::cuda::CUDAGuard guard(t.device());
+    auto stream = c10::cuda::getCurrentCUDAStream();
+    MOODIST_TRANSLATE(cudaGroup(t.get_device())
+                          .all_reduce(t.data_ptr(), t.data_ptr(), t.numel(), dt, op, (float)premul, raw(stream));)
+    return c10::make_intrusive<CudaWork>(rank_, c10d::OpType::ALLREDUCE, tensors, stream);
+  }
+  MOODIST_TRANSLATE(hostGroup().all_reduce(t.data_ptr(), t.data_ptr(), t.numel(), dt, op, premul);)
+  return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::ALLREDUCE, tensors);
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::allreduce_coalesced(std::vector<at::Tensor>& tensors,
+                                                                   const c10d::AllreduceCoalescedOptions& opts) {
+  c10::intrusive_ptr<c10d::Work> last;
+  for (auto& t : tensors) {
+    std::vector<at::Tensor> one{t};
+    last = allreduce(one, opts);
+  }
+  if (!last) return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::ALLREDUCE_COALESCED, tensors);
+  return last;
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::broadcast(std::vector<at::Tensor>& tensors,
+                                                         const c10d::BroadcastOptions& opts) {
+  TORCH_CHECK(tensors.size() == 1, "moodist: broadcast takes one tensor");
+  at::Tensor& t = tensors[0];
+  check_contig(t, "broadcast");
+  int root = (int)opts.rootRank;
+  TORCH_CHECK(root >= 0 && root < size_, "moodist: bad broadcast root");
+  if (t.is_cuda()) {
+    c10::cuda::CUDAGuard guard(t.device());
+    auto stream = c10::cuda::getCurrentCUDAStream();
+    MOODIST_TRANSLATE(cudaGroup(t.get_device()).broadcast(t.data_ptr(), t.nbytes(), root, raw(stream));)
+    return c10::make_intrusive<CudaWork>(rank_, c10d::OpType::BROADCAST, tensors, stream);
+  }
+  MOODIST_TRANSLATE(hostGroup().broadcast(t.data_ptr(), t.nbytes(), root);)
+  return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::BROADCAST, tensors);
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::reduce(std::vector<at::Tensor>& tensors, const c10d::ReduceOptions& opts) {
+  // reduce = all_reduce into a temporary, root keeps it (the reference supports CUDA SUM only,
+  // core/processgroup.cc:1937-1956; every op the kernels know works here)
+  TORCH_CHECK(tensors.size() == 1, "moodist: reduce takes one tensor");
+  at::Tensor& t = tensors[0];
+  check_contig(t, "reduce");
+  at::Tensor tmp = t.clone();
+  std::vector<at::Tensor> one{tmp};
+  c10d::AllreduceOptions ao;
+  ao.reduceOp = opts.reduceOp;
+  auto w = allreduce(one, ao);
+  if (rank_ == (int)opts.rootRank) {
+    if (t.is_cuda()) {
+      c10::cuda::CUDAGuard guard(t.device());
+      t.copy_(tmp, true);
+      return c10::make_intrusive<CudaWork>(rank_, c10d::OpType::REDUCE, tensors, c10::cuda::getCurrentCUDAStream());
+    }
+    t.copy_(tmp);
+  }
+  return w;
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::gather(std::vector<std::vector<at::Tensor>>& outputs,
+                                                      std::vector<at::Tensor>& inputs, const c10d::GatherOptions& opts) {
+  TORCH_CHECK(inputs.size() == 1, "moodist: gather takes one input tensor");
+  at::Tensor in = inputs[0].contiguous();
+  int root = (int)opts.rootRank;
+  if (in.is_cuda()) {
+    // CUDA gather = all_gather, root keeps the result (the reference throws for CUDA, core/processgroup.cc:2198-2262)
+    c10::cuda::CUDAGuard guard(in.device());
+    at::Tensor flat = at::empty({size_ * in.numel()}, in.options());
+    _allgather_base(flat, in);
+    if (rank_ == root) {
+      TORCH_CHECK(outputs.size() == 1 && (int)outputs[0].size() == size_, "moodist: gather output list size");
+      for (int r = 0; r < size_; ++r)
+        outputs[0][r].copy_(flat.narrow(0, r * in.numel(), in.numel()).view_as(in), true);
+    }
+    return c10::make_intrusive<CudaWork>(rank_, c10d::OpType::GATHER, std::vector<at::Tensor>{},
+                                         c10::cuda::getCurrentCUDAStream());
+  }
+  at::Tensor flat;
+  if (rank_ == root) flat = at::empty({size_ * in.numel()}, in.options());
+  MOODIST_TRANSLATE(hostGroup().gather(in.data_ptr(), rank_ == root ? flat.data_ptr() : nullptr, in.nbytes(), root);)
+  if (rank_ == root) {
+    TORCH_CHECK(outputs.size() == 1 && (int)outputs[0].size() == size_, "moodist: gather output list size");
+    for (int r = 0; r < size_; ++r) outputs[0][r].copy_(flat.narrow(0, r * in.numel(), in.numel()).view_as(in));
+  }
+  return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::GATHER, std::vector<at::Tensor>{});
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::scatter(std::vector<at::Tensor>& outputs,
+                                                       std::vector<std::vector<at::Tensor>>& inputs,
+                                                       const c10d::ScatterOptions& opts) {
+  TORCH_CHECK(outputs.size() == 1, "moodist: scatter takes one output tensor");
+  at::Tensor& out = outputs[0];
+  check_contig(out, "scatter output");
+  int root = (int)opts.rootRank;
+  at::Tensor flat;
+  if (rank_ == root) {
+    TORCH_CHECK(inputs.size() == 1 && (int)inputs[0].size() == size_, "moodist: scatter input list size");
+    std::vector<at::Tensor> fl;
+    for (auto& t : inputs[0]) fl.push_back(t.reshape({-1}));
+    flat = at::cat(fl);
+  }
+  if (out.is_cuda()) {
+    // CUDA scatter rides on the uneven all-to-all: only the root sends
+    c10::cuda::CUDAGuard guard(out.device());
+    auto stream = c10::cuda::getCurrentCUDAStream();
+    std::vector<uint64_t> so(size_, 0), sb(size_, 0), ro(size_, 0), rb(size_, 0);
+    if (rank_ == root)
+      for (int r = 0; r < size_; ++r) {
+        so[r] = (uint64_t)r * out.nbytes();
+        sb[r] = out.nbytes();
+      }
+    rb[root] = out.nbytes();
+    if (rank_ != root) flat = at::empty({1}, out.options());
+    MOODIST_TRANSLATE(cudaGroup(out.get_device())
+                          .all_to_all(flat.data_ptr(), out.data_ptr(), so.data(), sb.data(), ro.data(), rb.data(),
+                                      raw(stream));)
+    return c10::make_intrusive<CudaWork>(rank_, c10d::OpType::SCATTER, outputs, stream);
+  }
+  MOODIST_TRANSLATE(hostGroup().scatter(rank_ == root ? flat.data_ptr() : nullptr, out.data_ptr(), out.nbytes(), root);)
+  return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::SCATTER, outputs);
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::alltoall_base(at::Tensor& output, at::Tensor& input,
+                                                             std::vector<int64_t>& outputSplitSizes,
+                                                             std::vector<int64_t>& inputSplitSizes,
+                                                             const c10d::AllToAllOptions&) {
+  // Split sizes count rows of dim 0. The reference ignores them (wrapper/processgroup_wrapper.cc:265-283);
+  // here uneven splits are the point (MoE dispatch / combine).
+  check_contig(output, "all_to_all output");
+  check_contig(input, "all_to_all input");
+  TORCH_CHECK(output.scalar_type() == input.scalar_type(), "moodist: all_to_all dtype mismatch");
+  auto row_bytes = [](const at::Tensor& t) -> uint64_t {
+    return t.dim() == 0 || t.size(0) == 0 ? t.element_size() : (uint64_t)t.nbytes() / t.size(0);
+  };
+  std::vector<uint64_t> so(size_), sb(size_), ro(size_), rb(size_);
+  uint64_t irb = row_bytes(input), orb = row_bytes(output);
+  uint64_t acc = 0;
+  for (int r = 0; r < size_; ++r) {
+    uint64_t rows;
+    if (inputSplitSizes.empty()) {
+      TORCH_CHECK(input.size(0) % size_ == 0, "moodist: all_to_all input dim 0 must divide by world size");
+      rows = input.size(0) / size_;
+    } else {
+      TORCH_CHECK((int)inputSplitSizes.size() == size_, "moodist: input split sizes must have world_size entries");
+      rows = inputSplitSizes[r];
+    }
+    so[r] = acc;
+    sb[r] = rows * irb;
+    acc += sb[r];
+  }
+  TORCH_CHECK(acc == (uint64_t)input.nbytes(), "moodist: input split sizes do not add up to the input size");
+  acc = 0;
+  for (int r = 0; r < size_; ++r) {
+    uint64_t rows;
+    if (outputSplitSizes.empty()) {
+      TORCH_CHECK(output.size(0) % size_ == 0, "moodist: all_to_all output dim 0 must divide by world size");
+      rows = output.size(0) / size_;
+    } else {
+      TORCH_CHECK((int)outputSplitSizes.size() == size_, "moodist: output split sizes must have world_size entries");
+      rows = outputSplitSizes[r];
+    }
+    ro[r] = acc;
+    rb[r] = rows * orb;
+    acc += rb[r];
+  }
+  TORCH_CHECK(acc == (uint64_t)output.nbytes(), "moodist: output split sizes do not add up to the output size");
+  if (input.is_cuda()) {
+    c10::cuda::CUDAGuard guard(input.device());
+    auto stream = c10::cuda::getCurrentCUDAStream();
+    MOODIST_TRANSLATE(cudaGroup(input.get_device())
+                          .all_to_all(input.data_ptr(), output.data_ptr(), so.data(), sb.data(), ro.data(), rb.data(),
+                                      raw(stream));)
+    return c10::make_intrusive<CudaWork>(rank_, c10d::OpType::ALLTOALL_BASE, std::vector<at::Tensor>{output}, stream);
+  }
+  MOODIST_TRANSLATE(
+      hostGroup().all_to_all(input.data_ptr(), output.data_ptr(), so.data(), sb.data(), ro.data(), rb.data());)
+  return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::ALLTOALL_BASE, std::vector<at::Tensor>{output});
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::alltoall(std::vector<at::Tensor>& outputs, std::vector<at::Tensor>& inputs,
+                                                        const c10d::AllToAllOptions& opts) {
+  TORCH_CHECK((int)outputs.size() == size_ && (int)inputs.size() == size_, "moodist: all_to_all list sizes");
+  std::vector<at::Tensor> fl;
+  std::vector<int64_t> in_split, out_split;
+  for (auto& t : inputs) {
+    fl.push_back(t.reshape({-1}));
+    in_split.push_back(t.numel());
+  }
+  at::Tensor in = at::cat(fl);
+  int64_t total = 0;
+  for (auto& t : outputs) {
+    out_split.push_back(t.numel());
+    total += t.numel();
+  }
+  at::Tensor out = at::empty({total}, outputs[0].options());
+  auto w = alltoall_base(out, in, out_split, in_split, opts);
+  int64_t off = 0;
+  bool cuda = out.is_cuda();
+  c10::optional<c10::cuda::CUDAGuard> guard;
+  if (cuda) guard.emplace(out.device());
+  for (auto& t : outputs) {
+    t.copy_(out.narrow(0, off, t.numel()).view_as(t), cuda);
+    off += t.numel();
+  }
+  if (cuda) return c10::make_intrusive<CudaWork>(rank_, c10d::OpType::ALLTOALL, outputs, c10::cuda::getCurrentCUDAStream());
+  return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::ALLTOALL, outputs);
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::barrier(const c10d::BarrierOptions& opts) {
+  // CPU-side barrier through the engine, plus a device barrier when this group already runs on a GPU
+  bool use_cuda = false;
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    use_cuda = cuda_ != nullptr;
+  }
+  if (use_cuda || opts.device.has_value() && opts.device->is_cuda()) {
+    cudaBarrier();
+    return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::BARRIER, std::vector<at::Tensor>{});
+  }
+  MOODIST_TRANSLATE(hostGroup().barrier();)
+  return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::BARRIER, std::vector<at::Tensor>{});
+}
+
+void MoodistBackend::cudaBarrier() {
+  int dev = cuda_ ? cuda_->device() : (int)c10::cuda::current_device();
+  c10::cuda::CUDAGuard guard((c10::DeviceIndex)dev);
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  MOODIST_TRANSLATE(auto& g = cudaGroup(dev); g.barrier(raw(stream)); stream.synchronize(); g.check_status();)
+}
+
+int64_t MoodistBackend::getOption(const std::string& name) {
+  GroupOptions& o = opts_;
+  if (name == "prefer_kernel_less") return o.prefer_kernel_less;
+  if (name == "force_kernel_less") return o.force_kernel_less;
+  if (name == "num_chunks") return o.num_chunks;
+  if (name == "chunk_size") return o.chunk_size;
+  if (name == "method") return o.method;
+  TORCH_CHECK(false, "moodist: unknown option ", name);
+}
+
+void MoodistBackend::setOption(const std::string& name, int64_t value) {
+  GroupOptions& o = opts_;
+  if (name == "prefer_kernel_less") o.prefer_kernel_less = (int)value;
+  else if (name == "force_kernel_less") o.force_kernel_less = (int)value;
+  else if (name == "num_chunks") o.num_chunks = (int)value;
+  else if (name == "chunk_size") o.chunk_size = (int)value;
+  else if (name == "method") o.method = (int)value;
+  else TORCH_CHECK(false, "moodist: unknown option ", name);
+  if (cuda_) cuda_->options() = opts_;
+}
+
+uint64_t MoodistBackend::kernelLaunches() { return cuda_ ? cuda_->launches() : 0; }
+
+std::string MoodistBackend::describe() {
+  std::string s = "MoodistBackend(name=" + name_ + ", rank=" + std::to_string(rank_) + "/" + std::to_string(size_);
+  if (cuda_) s += ", " + cuda_->describe();
+  return s + ")";
+}
+
+}  // namespace moodist

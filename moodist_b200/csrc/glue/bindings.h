@@ -1,0 +1,17 @@
+// Hooks through which the other glue translation units add their bindings to the module.
+#pragma once
+
+#include <torch/extension.h>
+
+#include "backend.h"
+
+namespace moodist {
+
+using BackendClass = pybind11::class_<MoodistBackend, c10d::Backend, c10::intrusive_ptr<MoodistBackend>>;
+
+// ops.cc: GEMM and fused ops
+void bind_ops(pybind11::module_& m, BackendClass& backend);
+
+inline void bind_extras(pybind11::module_& m, BackendClass& backend) { bind_ops(m, backend); }
+
+}  // namespace moodist

@@ -1,0 +1,43 @@
+// Python bindings of the torch-facing objects (module `moodist_b200._C`).
+//
+// Exposes the same Python-visible names as the reference's hand-written CPython module
+// (wrapper/module.cc:1355-1428): MoodistProcessGroup / MoodistBackend with moodist_name, cuda_barrier,
+// _get_option/_set_option, get/set_prefer_kernel_less, Queue, compile_op_full; TcpStore; Queue objects;
+// serialize/deserialize live in the separate _serialize module. pybind11 (shipped with torch) replaces
+// the reference's manual subclassing of torch's pybind types since a single torch version is targeted.
+#include <torch/extension.h>
+#include <torch/csrc/distributed/c10d/Backend.hpp>
+#include <torch/csrc/distributed/c10d/Store.hpp>
+
+#include "backend.h"
+#include "bindings.h"
+
+namespace py = pybind11;
+using namespace moodist;
+
+PYBIND11_MODULE(_C, m) {
+  m.doc() = "moodist_b200 native extension";
+  py::module::import("torch.distributed");
+
+  auto backend =
+      py::class_<MoodistBackend, c10d::Backend, c10::intrusive_ptr<MoodistBackend>>(m, "MoodistBackend")
+          .def(py::init([](const c10::intrusive_ptr<c10d::Store>& store, int rank, int size) {
+                 return c10::make_intrusive<MoodistBackend>(store, rank, size);
+               }),
+               py::arg("store"), py::arg("rank"), py::arg("size"), py::call_guard<py::gil_scoped_release>())
+          .def("moodist_name", &MoodistBackend::moodistName)
+          .def("cuda_barrier", &MoodistBackend::cudaBarrier, py::call_guard<py::gil_scoped_release>())
+          .def("_get_option", &MoodistBackend::getOption)
+          .def("_set_option", &MoodistBackend::setOption)
+          .def("get_prefer_kernel_less", &MoodistBackend::getPreferKernelLess)
+          .def("set_prefer_kernel_less", &MoodistBackend::setPreferKernelLess)
+          .def("kernel_launches", &MoodistBackend::kernelLaunches)
+          .def("describe", &MoodistBackend::describe)
+          .def("all_gather_cast", &MoodistBackend::allGatherCast, py::arg("output"), py::arg("input"),
+               py::call_guard<py::gil_scoped_release>())
+          .def("reduce_scatter_cast", &MoodistBackend::reduceScatterCast, py::arg("output"), py::arg("input"),
+               py::arg("op") = 0, py::arg("premul") = 1.0, py::call_guard<py::gil_scoped_release>());
+  m.attr("MoodistProcessGroup") = backend;
+
+  bind_extras(m, backend);
+}

@@ -21,8 +21,9 @@ namespace coll {
 
 constexpr int kMaxCtas = 128;  // READY has room for this many producer CTAs per rank
 constexpr int F_DONE = 0;      // [8]
-constexpr int F_ANN = 16;      // [8][4]  {off_lo, off_hi, aux, seq}
-constexpr int F_LOCAL = 64;    // [8]     local-grid counters (own page only)
+constexpr int F_ANN = 16;      // [2][8][4]  {off_lo, off_hi, aux, seq}, bank = seq & 1 (a fast peer may already
+                               //            announce op seq+1 while this rank still reads the one for seq)
+constexpr int F_LOCAL = 96;    // [8]     local-grid counters (own page only)
 constexpr int F_TABLE = 128;   // [8][4]  all-to-all: {src_off_lo, src_off_hi, bytes_lo, bytes_hi}
 constexpr int F_READY = 256;   // [8][kMaxCtas]
 constexpr int F_READY2 = F_READY + MB_MAX_RANKS * kMaxCtas;  // second bank (two-phase ops)
@@ -36,12 +37,14 @@ enum Status : uint32_t {
   kTimeoutExit = 0x204,
 };
 
+// The status word may live in host-mapped memory, so no atomics: the first writer (nearly) wins.
 __device__ __forceinline__ void fail(const mb_comm_t& c, uint32_t code, int peer) {
-  atomicCAS(c.status, 0u, code | ((uint32_t)peer << 16));
+  volatile uint32_t* s = c.status;
+  if (*s == 0) *s = code | ((uint32_t)peer << 16);
 }
 
 __device__ __forceinline__ uint8_t* stage_ptr(const mb_comm_t& c, int r, uint32_t seq) {
-  return reinterpret_cast<uint8_t*>(c.peer[r]) + c.staging_off + (uint64_t)(seq & 1) * (c.staging_bytes >> 1);
+  return reinterpret_cast<uint8_t*>(c.stage[r]) + (uint64_t)(seq & 1) * (c.staging_bytes >> 1);
 }
 
 // All threads of the CTA call this. Threads 0..world-1 each wait on one peer.
@@ -57,7 +60,7 @@ __device__ __forceinline__ void entry_wait(const mb_comm_t& c, uint32_t seq) {
 __device__ __forceinline__ void announce(const mb_comm_t& c, uint32_t seq, uint64_t off, uint32_t aux) {
   int t = threadIdx.x;
   if (t < c.world && t != c.rank) {
-    uint32_t* a = c.flags[t] + F_ANN + c.rank * 4;
+    uint32_t* a = c.flags[t] + F_ANN + ((seq & 1) * MB_MAX_RANKS + c.rank) * 4;
     a[0] = (uint32_t)off;
     a[1] = (uint32_t)(off >> 32);
     a[2] = aux;
@@ -67,7 +70,7 @@ __device__ __forceinline__ void announce(const mb_comm_t& c, uint32_t seq, uint6
 }
 // Any thread: wait for peer p's announcement and read it.
 __device__ __forceinline__ bool wait_announce(const mb_comm_t& c, uint32_t seq, int p, uint64_t& off, uint32_t& aux) {
-  const uint32_t* a = c.flags[c.rank] + F_ANN + p * 4;
+  const uint32_t* a = c.flags[c.rank] + F_ANN + ((seq & 1) * MB_MAX_RANKS + p) * 4;
   if (!wait_geq_sys(a + 3, seq, c.wait_ns)) {
     fail(c, kTimeoutAnnounce, p);
     off = 0;

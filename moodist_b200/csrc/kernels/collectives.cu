@@ -1,0 +1,650 @@
+// sm_100a collective kernels over NVLink peer memory (plain P2P loads/stores; the NVLS multimem
+// variants live in collectives_nvls.cu). One launch per collective: rendezvous, data movement, the
+// reduction with fp32 accumulation, the premul/avg scale and any dtype cast all happen in the kernel.
+//
+// Reference counterparts: allgather_local (core/allgather.cc:381-390, 556-566), reduce_scatter_local
+// (core/reduce_scatter.cc:180-191, 344-352), alltoall (core/alltoall.cc:30-67), the all_reduce =
+// reduce_scatter + all_gather composition (core/processgroup.cc:1674-1722), and the pull-chain
+// broadcast (core/processgroup.cc:1728-1910). Differences by design: peers are reached through one
+// symmetric heap mapping instead of per-tensor IPC handles; tensors outside the heap go through a
+// double-buffered staging area so no exit barrier is needed; waits are bounded; AVG/PREMUL_SUM are
+// folded into the reduce loop (the reference runs a separate torch mul_, processgroup.cc:1664-1667);
+// bf16 accumulates in fp32 (the reference accumulates in bf16, core/kernels.cc:472-481).
+#include <cuda_runtime.h>
+
+#include "coll.cuh"
+
+namespace mb {
+namespace coll {
+
+constexpr int kThreads = 512;
+
+struct Launch {
+  int grid;
+};
+
+static inline int pick_grid(const mb_comm_t* c, size_t bytes) {
+  int maxc = c->max_ctas > 0 ? c->max_ctas : 64;
+  if (maxc > kMaxCtas) maxc = kMaxCtas;
+  size_t g = (bytes + 32767) / 32768;
+  if (g < 1) g = 1;
+  if (g > (size_t)maxc) g = maxc;
+  return (int)g;
+}
+
+// lane 0 waits for peer p's announcement, result broadcast to the warp
+// `direct` tells how peer p takes part in this op: 1 = its tensor lives in its symmetric heap at `off`
+// and is read in place, 0 = it goes through the staging areas. Each rank decides for itself, so a
+// consumer always follows what the producer announced.
+__device__ __forceinline__ bool wait_announce_warp(const mb_comm_t& c, uint32_t seq, int p, uint64_t& off,
+                                                   uint32_t& direct) {
+  uint32_t lo = 0, hi = 0, ok = 1, aux = 0;
+  if ((threadIdx.x & 31) == 0) {
+    uint64_t o;
+    ok = wait_announce(c, seq, p, o, aux);
+    lo = (uint32_t)o;
+    hi = (uint32_t)(o >> 32);
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  lo = __shfl_sync(0xffffffffu, lo, 0);
+  hi = __shfl_sync(0xffffffffu, hi, 0);
+  direct = __shfl_sync(0xffffffffu, aux, 0);
+  off = (uint64_t)lo | ((uint64_t)hi << 32);
+  return ok != 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// barrier
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(32, 1) barrier_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq) {
+  int t = threadIdx.x;
+  if (t < c.world) {
+    __threadfence_system();
+    st_release_sys(c.flags[t] + F_DONE + c.rank, seq);
+    if (!wait_geq_sys(c.flags[c.rank] + F_DONE + t, seq, c.wait_ns)) fail(c, kTimeoutExit, t);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// all-gather
+// ---------------------------------------------------------------------------------------------
+// kCast: 0 bytes (same dtype), else converts InT -> OutT while staging.
+template <typename InT, typename OutT, bool kCast>
+__global__ void __launch_bounds__(kThreads, 1)
+    all_gather_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, int64_t in_heap_off,
+                      void* out, size_t count, size_t out_stride) {
+  const int b = blockIdx.x, G = gridDim.x;
+  const bool direct = in_heap_off >= 0;
+  entry_wait(c, seq);
+  size_t begin, len;
+  slice_of(count, G, b, begin, len);
+  OutT* o = reinterpret_cast<OutT*>(out);
+  const InT* src_local = reinterpret_cast<const InT*>(in);
+  if (b == 0) announce(c, seq, direct ? (uint64_t)in_heap_off : 0, direct ? 1u : 0u);
+  if (!direct) {
+    OutT* st = reinterpret_cast<OutT*>(stage_ptr(c, c.rank, seq));
+    if constexpr (kCast) {
+      cta_cast_copy<InT, OutT>(st + begin, src_local + begin, len, 1.f, false);
+    } else {
+      cta_copy(st + begin, src_local + begin, len * sizeof(OutT));
+    }
+    signal_ready(c, seq, b, 0, -1);
+  }
+  // own shard straight into place
+  if constexpr (kCast) {
+    cta_cast_copy<InT, OutT>(o + (size_t)c.rank * out_stride + begin, src_local + begin, len, 1.f, false);
+  } else {
+    if ((const void*)(o + (size_t)c.rank * out_stride) != in)
+      cta_copy(o + (size_t)c.rank * out_stride + begin, src_local + begin, len * sizeof(OutT));
+  }
+  for (int i = 1; i < c.world; ++i) {
+    int p = (c.rank + i) % c.world;
+    const OutT* src;
+    uint64_t off;
+    uint32_t pdirect;
+    bool ok = wait_announce_warp(c, seq, p, off, pdirect);
+    if (!pdirect) {
+      ok = ok && wait_ready_warp(c, seq, p, b, 0);
+      src = reinterpret_cast<const OutT*>(stage_ptr(c, p, seq));
+    } else {
+      src = reinterpret_cast<const OutT*>(reinterpret_cast<const uint8_t*>(c.peer[p]) + off);
+    }
+    if (ok) cta_copy(o + (size_t)p * out_stride + begin, src + begin, len * sizeof(OutT));
+  }
+  exit_done(c, seq, direct);
+}
+
+// ---------------------------------------------------------------------------------------------
+// reduce-scatter
+// ---------------------------------------------------------------------------------------------
+template <typename InT, typename OutT, int kOp>
+__global__ void __launch_bounds__(kThreads, 1)
+    reduce_scatter_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, int64_t in_heap_off,
+                          void* out, size_t count, size_t in_stride, float scale, int use_scale) {
+  const int b = blockIdx.x, G = gridDim.x;
+  const bool direct = in_heap_off >= 0;
+  entry_wait(c, seq);
+  size_t begin, len;
+  slice_of(count, G, b, begin, len);
+  const InT* x = reinterpret_cast<const InT*>(in);
+  const InT* srcs[MB_MAX_RANKS];
+  srcs[0] = x + (size_t)c.rank * in_stride + begin;
+  if (b == 0) announce(c, seq, direct ? (uint64_t)in_heap_off : 0, direct ? 1u : 0u);
+  if (!direct) {
+    // push this rank's contribution for every other owner into that owner's staging slot [rank]
+    for (int i = 1; i < c.world; ++i) {
+      int p = (c.rank + i) % c.world;
+      InT* dst = reinterpret_cast<InT*>(stage_ptr(c, p, seq)) + (size_t)c.rank * count + begin;
+      cta_copy(dst, x + (size_t)p * in_stride + begin, len * sizeof(InT));
+      signal_ready(c, seq, b, 0, p);
+    }
+  }
+  bool ok = true;
+  for (int i = 1; i < c.world; ++i) {
+    int p = (c.rank + i) % c.world;
+    uint64_t off;
+    uint32_t pdirect;
+    ok = wait_announce_warp(c, seq, p, off, pdirect) && ok;
+    if (!pdirect) {
+      ok = wait_ready_warp(c, seq, p, b, 0) && ok;
+      srcs[i] = reinterpret_cast<const InT*>(stage_ptr(c, c.rank, seq)) + (size_t)p * count + begin;
+    } else {
+      srcs[i] = reinterpret_cast<const InT*>(reinterpret_cast<const uint8_t*>(c.peer[p]) + off) +
+                (size_t)c.rank * in_stride + begin;
+    }
+  }
+  if (ok) cta_reduce<InT, OutT, kOp>(reinterpret_cast<OutT*>(out) + begin, srcs, c.world, len, scale, use_scale);
+  exit_done(c, seq, direct);
+}
+
+// ---------------------------------------------------------------------------------------------
+// all-reduce
+// ---------------------------------------------------------------------------------------------
+// one-shot: every rank pushes its whole vector to every peer's slot [rank], then reduces world inputs.
+template <typename T, int kOp>
+__global__ void __launch_bounds__(kThreads, 1)
+    all_reduce_oneshot_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, void* out,
+                              size_t count, float scale, int use_scale) {
+  const int b = blockIdx.x, G = gridDim.x;
+  entry_wait(c, seq);
+  size_t begin, len;
+  slice_of(count, G, b, begin, len);
+  const T* x = reinterpret_cast<const T*>(in);
+  for (int i = 1; i < c.world; ++i) {
+    int p = (c.rank + i) % c.world;
+    T* dst = reinterpret_cast<T*>(stage_ptr(c, p, seq)) + (size_t)c.rank * count + begin;
+    cta_copy(dst, x + begin, len * sizeof(T));
+  }
+  signal_ready(c, seq, b, 0, -1);
+  const T* srcs[MB_MAX_RANKS];
+  // fixed source order (rank 0, 1, ...) so every rank computes bit-identical sums
+  bool ok = true;
+  for (int p = 0; p < c.world; ++p) {
+    if (p == c.rank) {
+      srcs[p] = x + begin;
+    } else {
+      ok = wait_ready_warp(c, seq, p, b, 0) && ok;
+      srcs[p] = reinterpret_cast<const T*>(stage_ptr(c, c.rank, seq)) + (size_t)p * count + begin;
+    }
+  }
+  if (ok) cta_reduce<T, T, kOp>(reinterpret_cast<T*>(out) + begin, srcs, c.world, len, scale, use_scale);
+  exit_done(c, seq, false);
+}
+
+// two-shot in one launch: reduce-scatter into the owner, owner pushes the reduced chunk to everyone.
+template <typename T, int kOp>
+__global__ void __launch_bounds__(kThreads, 1)
+    all_reduce_twoshot_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, void* out,
+                              size_t count, size_t chunk, float scale, int use_scale) {
+  const int b = blockIdx.x, G = gridDim.x;
+  entry_wait(c, seq);
+  const T* x = reinterpret_cast<const T*>(in);
+  T* y = reinterpret_cast<T*>(out);
+  auto chunk_len = [&](int r) -> size_t {
+    size_t s = (size_t)r * chunk;
+    if (s >= count) return 0;
+    return count - s < chunk ? count - s : chunk;
+  };
+  // phase 1: contributions to owners (region A of the staging half: [world][chunk])
+  for (int i = 1; i < c.world; ++i) {
+    int p = (c.rank + i) % c.world;
+    size_t begin, len;
+    slice_of(chunk_len(p), G, b, begin, len);
+    T* dst = reinterpret_cast<T*>(stage_ptr(c, p, seq)) + (size_t)c.rank * chunk + begin;
+    cta_copy(dst, x + (size_t)p * chunk + begin, len * sizeof(T));
+    signal_ready(c, seq, b, 0, p);
+  }
+  // phase 2: reduce own chunk, write it locally and into region B ([world][chunk]) of every peer
+  size_t begin, len;
+  slice_of(chunk_len(c.rank), G, b, begin, len);
+  const T* srcs[MB_MAX_RANKS];
+  bool ok = true;
+  for (int p = 0; p < c.world; ++p) {
+    if (p == c.rank) {
+      srcs[p] = x + (size_t)c.rank * chunk + begin;
+    } else {
+      ok = wait_ready_warp(c, seq, p, b, 0) && ok;
+      srcs[p] = reinterpret_cast<const T*>(stage_ptr(c, c.rank, seq)) + (size_t)p * chunk + begin;
+    }
+  }
+  T* mine = y + (size_t)c.rank * chunk + begin;
+  if (ok) cta_reduce<T, T, kOp>(mine, srcs, c.world, len, scale, use_scale);
+  __syncthreads();  // reduced slice visible to the whole CTA before it is pushed
+  for (int i = 1; i < c.world; ++i) {
+    int p = (c.rank + i) % c.world;
+    T* dst = reinterpret_cast<T*>(stage_ptr(c, p, seq)) + (size_t)(c.world + c.rank) * chunk + begin;
+    cta_copy(dst, mine, len * sizeof(T));
+  }
+  signal_ready(c, seq, b, 1, -1);
+  // phase 3: collect the other owners' chunks from region B
+  for (int i = 1; i < c.world; ++i) {
+    int p = (c.rank + i) % c.world;
+    slice_of(chunk_len(p), G, b, begin, len);
+    if (wait_ready_warp(c, seq, p, b, 1)) {
+      const T* src = reinterpret_cast<const T*>(stage_ptr(c, c.rank, seq)) + (size_t)(c.world + p) * chunk + begin;
+      cta_copy(y + (size_t)p * chunk + begin, src, len * sizeof(T));
+    }
+  }
+  exit_done(c, seq, false);
+}
+
+// ---------------------------------------------------------------------------------------------
+// broadcast (pull from the root's staging copy, or straight from the root's heap memory)
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1)
+    broadcast_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, void* data, int64_t heap_off, size_t bytes,
+                     int root) {
+  const int b = blockIdx.x, G = gridDim.x;
+  const bool direct = heap_off >= 0;
+  entry_wait(c, seq);
+  size_t begin, len;
+  slice_of(bytes, G, b, begin, len);
+  uint8_t* d = reinterpret_cast<uint8_t*>(data);
+  if (c.rank == root) {
+    if (b == 0) announce(c, seq, direct ? (uint64_t)heap_off : 0, direct ? 1u : 0u);
+    if (!direct) {
+      cta_copy(stage_ptr(c, root, seq) + begin, d + begin, len);
+      signal_ready(c, seq, b, 0, -1);
+    }
+  } else {
+    const uint8_t* src;
+    uint64_t off;
+    uint32_t rdirect;
+    bool ok = wait_announce_warp(c, seq, root, off, rdirect);
+    if (!rdirect) {
+      ok = ok && wait_ready_warp(c, seq, root, b, 0);
+      src = stage_ptr(c, root, seq);
+    } else {
+      src = reinterpret_cast<const uint8_t*>(c.peer[root]) + off;
+    }
+    if (ok) cta_copy(d + begin, src + begin, len);
+  }
+  exit_done(c, seq, direct && c.rank == root);
+}
+
+// ---------------------------------------------------------------------------------------------
+// all-to-all with per-peer byte counts
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1)
+    all_to_all_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, int64_t in_heap_off,
+                      void* out, const __grid_constant__ mb_a2a_table_t tab) {
+  const int b = blockIdx.x, G = gridDim.x;
+  const bool direct = in_heap_off >= 0;
+  entry_wait(c, seq);
+  const uint8_t* x = reinterpret_cast<const uint8_t*>(in);
+  uint8_t* y = reinterpret_cast<uint8_t*>(out);
+  size_t begin, len;
+  if (!direct) {
+    // stage every outgoing segment at the same offset it has in the input
+    for (int i = 1; i < c.world; ++i) {
+      int p = (c.rank + i) % c.world;
+      slice_of(tab.send_bytes[p], G, b, begin, len);
+      cta_copy(stage_ptr(c, c.rank, seq) + tab.send_off[p] + begin, x + tab.send_off[p] + begin, len);
+    }
+    signal_ready(c, seq, b, 0, -1);
+  }
+  if (b == 0) {
+    // tell each peer where its segment starts (staging-relative, or heap-relative in direct mode)
+    int t = threadIdx.x;
+    if (t < c.world && t != c.rank) {
+      uint64_t off = direct ? (uint64_t)in_heap_off + tab.send_off[t] : tab.send_off[t];
+      uint32_t* a = c.flags[t] + F_ANN + ((seq & 1) * MB_MAX_RANKS + c.rank) * 4;
+      a[0] = (uint32_t)off;
+      a[1] = (uint32_t)(off >> 32);
+      a[2] = direct ? 1u : 0u;
+      __threadfence_system();
+      st_release_sys(a + 3, seq);
+    }
+  }
+  // own segment
+  slice_of(tab.recv_bytes[c.rank], G, b, begin, len);
+  cta_copy(y + tab.recv_off[c.rank] + begin, x + tab.send_off[c.rank] + begin, len);
+  for (int i = 1; i < c.world; ++i) {
+    int p = (c.rank + i) % c.world;
+    uint64_t off;
+    uint32_t pdirect;
+    bool ok = wait_announce_warp(c, seq, p, off, pdirect);
+    const uint8_t* src;
+    if (!pdirect) {
+      ok = wait_ready_warp(c, seq, p, b, 0) && ok;
+      src = stage_ptr(c, p, seq) + off;
+    } else {
+      src = reinterpret_cast<const uint8_t*>(c.peer[p]) + off;
+    }
+    slice_of(tab.recv_bytes[p], G, b, begin, len);
+    if (ok) cta_copy(y + tab.recv_off[p] + begin, src + begin, len);
+  }
+  exit_done(c, seq, direct);
+}
+
+// ---------------------------------------------------------------------------------------------
+// compile_op lowering: 2-D pieces, sources in peers' staging areas (inputs are staged first)
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1)
+    gather_scatter_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const mb_stage_copy_t* stage_in,
+                          int num_stage, const mb_piece_t* pieces, int num_pieces) {
+  const int b = blockIdx.x, G = gridDim.x;
+  entry_wait(c, seq);
+  for (int i = 0; i < num_stage; ++i) {
+    size_t begin, len;
+    slice_of(stage_in[i].bytes, G, b, begin, len);
+    cta_copy(stage_ptr(c, c.rank, seq) + stage_in[i].dst_off + begin,
+             reinterpret_cast<const uint8_t*>(stage_in[i].src) + begin, len);
+  }
+  signal_ready(c, seq, b, 0, -1);
+  // every peer's inputs must be completely staged before pieces are read: wait for all of its CTAs
+  __shared__ uint32_t s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < c.world * G; idx += blockDim.x) {
+    int p = idx / G, pb = idx % G;
+    if (p != c.rank) {
+      if (!wait_geq_sys(c.flags[c.rank] + F_READY + p * kMaxCtas + pb, seq, c.wait_ns)) {
+        fail(c, kTimeoutReady, p);
+        s_ok = 0;
+      }
+    }
+  }
+  __syncthreads();
+  if (s_ok) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int i = 0; i < num_pieces; ++i) {
+      mb_piece_t pc = pieces[i];
+      const uint8_t* sbase = pc.src_rank == c.rank && pc.src_local
+                                 ? reinterpret_cast<const uint8_t*>(pc.src_local)
+                                 : stage_ptr(c, pc.src_rank, seq) + pc.src_off;
+      uint8_t* dbase = reinterpret_cast<uint8_t*>(pc.dst);
+      bool vec = ((pc.row_bytes | pc.src_pitch | pc.dst_pitch | (uintptr_t)sbase | (uintptr_t)dbase) & 15) == 0;
+      if (pc.rows == 1 || (pc.src_pitch == pc.row_bytes && pc.dst_pitch == pc.row_bytes)) {
+        size_t begin, len;
+        slice_of((size_t)pc.rows * pc.row_bytes, G, b, begin, len);
+        cta_copy(dbase + begin, sbase + begin, len);
+      } else {
+        // one warp per row, rows dealt round-robin over all warps of the grid
+        for (uint32_t r = b * nwarps + warp; r < pc.rows; r += G * nwarps) {
+          const uint8_t* s = sbase + (size_t)r * pc.src_pitch;
+          uint8_t* d = dbase + (size_t)r * pc.dst_pitch;
+          if (vec) {
+            for (uint64_t j = lane * 16; j < pc.row_bytes; j += 32 * 16) st_stream16(d + j, ld_stream16(s + j));
+          } else {
+            for (uint64_t j = lane; j < pc.row_bytes; j += 32) d[j] = s[j];
+          }
+        }
+      }
+    }
+  }
+  exit_done(c, seq, false);
+}
+
+// ---------------------------------------------------------------------------------------------
+// local cast / scale copy (world == 1 paths, staging helpers)
+// ---------------------------------------------------------------------------------------------
+template <typename InT, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+    copy_cast_kernel(const void* in, void* out, size_t count, float scale, int use_scale) {
+  size_t begin, len;
+  slice_of(count, gridDim.x, blockIdx.x, begin, len);
+  cta_cast_copy<InT, OutT>(reinterpret_cast<OutT*>(out) + begin, reinterpret_cast<const InT*>(in) + begin, len,
+                           scale, use_scale);
+}
+__global__ void __launch_bounds__(kThreads, 1) copy_bytes_kernel(const void* in, void* out, size_t bytes) {
+  size_t begin, len;
+  slice_of(bytes, gridDim.x, blockIdx.x, begin, len);
+  cta_copy(reinterpret_cast<uint8_t*>(out) + begin, reinterpret_cast<const uint8_t*>(in) + begin, len);
+}
+
+static inline int check_launch() { return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH; }
+
+static inline size_t dtype_size(int dt) {
+  switch (dt) {
+    case MB_U8:
+    case MB_I8: return 1;
+    case MB_I16:
+    case MB_F16:
+    case MB_BF16: return 2;
+    case MB_I32:
+    case MB_F32: return 4;
+    case MB_I64:
+    case MB_F64: return 8;
+    default: return 0;
+  }
+}
+
+}  // namespace coll
+}  // namespace mb
+
+using namespace mb::coll;
+
+#define MB_STREAM(s) static_cast<cudaStream_t>(s)
+
+extern "C" size_t mb_dtype_size(int dt) { return dtype_size(dt); }
+
+extern "C" int mb_barrier(const mb_comm_t* c, uint32_t seq, void* stream) {
+  if (c->world == 1) return MB_OK;
+  barrier_kernel<<<1, 32, 0, MB_STREAM(stream)>>>(*c, seq);
+  return check_launch();
+}
+
+extern "C" int mb_copy_cast(const void* in, void* out, size_t count, int in_dtype, int out_dtype, float scale,
+                            int use_scale, void* stream) {
+  if (count == 0) return MB_OK;
+  size_t bytes = count * dtype_size(in_dtype);
+  int grid = (int)((bytes + 65535) / 65536);
+  if (grid < 1) grid = 1;
+  if (grid > 592) grid = 592;
+  cudaStream_t s = MB_STREAM(stream);
+  if (in_dtype == out_dtype && !use_scale) {
+    copy_bytes_kernel<<<grid, kThreads, 0, s>>>(in, out, bytes);
+    return check_launch();
+  }
+#define CC(IDT, ODT, IT, OT)                                                             \
+  if (in_dtype == IDT && out_dtype == ODT) {                                             \
+    copy_cast_kernel<IT, OT><<<grid, kThreads, 0, s>>>(in, out, count, scale, use_scale); \
+    return check_launch();                                                               \
+  }
+  CC(MB_F32, MB_F32, float, float)
+  CC(MB_BF16, MB_BF16, __nv_bfloat16, __nv_bfloat16)
+  CC(MB_F16, MB_F16, __half, __half)
+  CC(MB_F64, MB_F64, double, double)
+  CC(MB_F32, MB_BF16, float, __nv_bfloat16)
+  CC(MB_BF16, MB_F32, __nv_bfloat16, float)
+  CC(MB_F32, MB_F16, float, __half)
+  CC(MB_F16, MB_F32, __half, float)
+  CC(MB_I32, MB_I32, int32_t, int32_t)
+  CC(MB_I64, MB_I64, int64_t, int64_t)
+#undef CC
+  return MB_ERR_ARG;
+}
+
+extern "C" int mb_all_gather(const mb_comm_t* c, uint32_t seq, const void* in, int64_t in_heap_off, void* out,
+                             size_t count, size_t out_stride, int in_dtype, int out_dtype, void* stream) {
+  size_t osz = dtype_size(out_dtype);
+  if (!osz || !dtype_size(in_dtype)) return MB_ERR_ARG;
+  if (c->world == 1) return mb_copy_cast(in, out, count, in_dtype, out_dtype, 1.f, 0, stream);
+  if (in_heap_off < 0 && count * osz > c->staging_bytes / 2) return MB_ERR_TOO_BIG;
+  if (in_heap_off >= 0 && in_dtype != out_dtype) return MB_ERR_ARG;
+  int grid = pick_grid(c, count * osz);
+  cudaStream_t s = MB_STREAM(stream);
+  if (in_dtype == out_dtype) {
+    // byte-wise: run as uint8 elements
+    all_gather_kernel<uint8_t, uint8_t, false><<<grid, kThreads, 0, s>>>(*c, seq, in, in_heap_off, out, count * osz,
+                                                                         out_stride * osz);
+    return check_launch();
+  }
+#define AG(IDT, ODT, IT, OT)                                                                             \
+  if (in_dtype == IDT && out_dtype == ODT) {                                                             \
+    all_gather_kernel<IT, OT, true><<<grid, kThreads, 0, s>>>(*c, seq, in, in_heap_off, out, count, out_stride); \
+    return check_launch();                                                                               \
+  }
+  AG(MB_F32, MB_BF16, float, __nv_bfloat16)
+  AG(MB_BF16, MB_F32, __nv_bfloat16, float)
+  AG(MB_F32, MB_F16, float, __half)
+  AG(MB_F16, MB_F32, __half, float)
+#undef AG
+  return MB_ERR_ARG;
+}
+
+namespace {
+template <typename InT, typename OutT>
+int launch_rs(const mb_comm_t* c, uint32_t seq, const void* in, int64_t off, void* out, size_t count, size_t stride,
+              int op, float scale, int use_scale, int grid, cudaStream_t s) {
+  switch (op) {
+    case MB_MIN:
+      reduce_scatter_kernel<InT, OutT, MB_MIN><<<grid, kThreads, 0, s>>>(*c, seq, in, off, out, count, stride, 1.f, 0);
+      break;
+    case MB_MAX:
+      reduce_scatter_kernel<InT, OutT, MB_MAX><<<grid, kThreads, 0, s>>>(*c, seq, in, off, out, count, stride, 1.f, 0);
+      break;
+    default:
+      reduce_scatter_kernel<InT, OutT, MB_SUM><<<grid, kThreads, 0, s>>>(*c, seq, in, off, out, count, stride, scale,
+                                                                         use_scale);
+  }
+  return check_launch();
+}
+template <typename T>
+int launch_ar(const mb_comm_t* c, uint32_t seq, const void* in, void* out, size_t count, int op, float scale,
+              int use_scale, int variant, cudaStream_t s) {
+  if (variant == 0) {
+    int grid = pick_grid(c, count * sizeof(T));
+    switch (op) {
+      case MB_MIN: all_reduce_oneshot_kernel<T, MB_MIN><<<grid, kThreads, 0, s>>>(*c, seq, in, out, count, 1.f, 0); break;
+      case MB_MAX: all_reduce_oneshot_kernel<T, MB_MAX><<<grid, kThreads, 0, s>>>(*c, seq, in, out, count, 1.f, 0); break;
+      default: all_reduce_oneshot_kernel<T, MB_SUM><<<grid, kThreads, 0, s>>>(*c, seq, in, out, count, scale, use_scale);
+    }
+  } else {
+    size_t chunk = (count + c->world - 1) / c->world;
+    chunk = (chunk + 63) & ~(size_t)63;
+    int grid = pick_grid(c, chunk * sizeof(T));
+    switch (op) {
+      case MB_MIN: all_reduce_twoshot_kernel<T, MB_MIN><<<grid, kThreads, 0, s>>>(*c, seq, in, out, count, chunk, 1.f, 0); break;
+      case MB_MAX: all_reduce_twoshot_kernel<T, MB_MAX><<<grid, kThreads, 0, s>>>(*c, seq, in, out, count, chunk, 1.f, 0); break;
+      default: all_reduce_twoshot_kernel<T, MB_SUM><<<grid, kThreads, 0, s>>>(*c, seq, in, out, count, chunk, scale, use_scale);
+    }
+  }
+  return check_launch();
+}
+bool op_scale(int op, int world, float premul, float* scale, int* use_scale) {
+  *scale = 1.f;
+  *use_scale = 0;
+  switch (op) {
+    case MB_SUM: return true;
+    case MB_AVG: *scale = 1.0f / (float)world; *use_scale = 1; return true;
+    case MB_PREMUL_SUM: *scale = premul; *use_scale = 1; return true;
+    case MB_MIN:
+    case MB_MAX: return true;
+    default: return false;
+  }
+}
+}  // namespace
+
+extern "C" int mb_reduce_scatter(const mb_comm_t* c, uint32_t seq, const void* in, int64_t in_heap_off, void* out,
+                                 size_t count, size_t in_stride, int in_dtype, int out_dtype, int op, float premul,
+                                 void* stream) {
+  size_t isz = dtype_size(in_dtype);
+  if (!isz || !dtype_size(out_dtype)) return MB_ERR_ARG;
+  float scale;
+  int use_scale;
+  if (!op_scale(op, c->world, premul, &scale, &use_scale)) return MB_ERR_ARG;
+  if (c->world == 1) return mb_copy_cast(in, out, count, in_dtype, out_dtype, scale, use_scale, stream);
+  if (in_heap_off < 0 && (size_t)c->world * count * isz > c->staging_bytes / 2) return MB_ERR_TOO_BIG;
+  (void)in_stride;
+  int grid = pick_grid(c, count * isz);
+  cudaStream_t s = MB_STREAM(stream);
+#define RS(IDT, ODT, IT, OT) \
+  if (in_dtype == IDT && out_dtype == ODT) \
+    return launch_rs<IT, OT>(c, seq, in, in_heap_off, out, count, in_stride, op, scale, use_scale, grid, s);
+  RS(MB_F32, MB_F32, float, float)
+  RS(MB_BF16, MB_BF16, __nv_bfloat16, __nv_bfloat16)
+  RS(MB_BF16, MB_F32, __nv_bfloat16, float)
+  RS(MB_F32, MB_BF16, float, __nv_bfloat16)
+  RS(MB_F16, MB_F16, __half, __half)
+  RS(MB_F64, MB_F64, double, double)
+  RS(MB_I32, MB_I32, int32_t, int32_t)
+  RS(MB_I64, MB_I64, int64_t, int64_t)
+  RS(MB_U8, MB_U8, uint8_t, uint8_t)
+#undef RS
+  return MB_ERR_ARG;
+}
+
+extern "C" int mb_all_reduce(const mb_comm_t* c, uint32_t seq, const void* in, void* out, size_t count, int dtype,
+                             int op, float premul, int variant, void* stream) {
+  size_t sz = dtype_size(dtype);
+  if (!sz) return MB_ERR_ARG;
+  float scale;
+  int use_scale;
+  if (!op_scale(op, c->world, premul, &scale, &use_scale)) return MB_ERR_ARG;
+  if (c->world == 1) return mb_copy_cast(in, out, count, dtype, dtype, scale, use_scale, stream);
+  size_t half = c->staging_bytes / 2;
+  if (variant == 0 && (size_t)c->world * count * sz > half) variant = 1;
+  if (variant == 1) {
+    size_t chunk = ((count + c->world - 1) / c->world + 63) & ~(size_t)63;
+    if (2 * (size_t)c->world * chunk * sz > half) return MB_ERR_TOO_BIG;
+  }
+  cudaStream_t s = MB_STREAM(stream);
+#define AR(DT, T) \
+  if (dtype == DT) return launch_ar<T>(c, seq, in, out, count, op, scale, use_scale, variant, s);
+  AR(MB_F32, float)
+  AR(MB_BF16, __nv_bfloat16)
+  AR(MB_F16, __half)
+  AR(MB_F64, double)
+  AR(MB_I32, int32_t)
+  AR(MB_I64, int64_t)
+  AR(MB_U8, uint8_t)
+#undef AR
+  return MB_ERR_ARG;
+}
+
+extern "C" int mb_broadcast(const mb_comm_t* c, uint32_t seq, void* data, int64_t heap_off, size_t bytes, int root,
+                            void* stream) {
+  if (c->world == 1 || bytes == 0) return MB_OK;
+  if (heap_off < 0 && bytes > c->staging_bytes / 2) return MB_ERR_TOO_BIG;
+  int grid = pick_grid(c, bytes);
+  broadcast_kernel<<<grid, kThreads, 0, MB_STREAM(stream)>>>(*c, seq, data, heap_off, bytes, root);
+  return check_launch();
+}
+
+extern "C" int mb_all_to_all(const mb_comm_t* c, uint32_t seq, const void* in, int64_t in_heap_off, void* out,
+                             const mb_a2a_table_t* tab, void* stream) {
+  size_t total = 0, biggest = 0;
+  for (int r = 0; r < c->world; ++r) {
+    size_t end = tab->send_off[r] + tab->send_bytes[r];
+    if (end > total) total = end;
+    if (tab->recv_bytes[r] > biggest) biggest = tab->recv_bytes[r];
+  }
+  if (c->world == 1) {
+    if (tab->send_bytes[0] == 0) return MB_OK;
+    return mb_copy_cast((const uint8_t*)in + tab->send_off[0], (uint8_t*)out + tab->recv_off[0], tab->send_bytes[0],
+                        MB_U8, MB_U8, 1.f, 0, stream);
+  }
+  if (in_heap_off < 0 && total > c->staging_bytes / 2) return MB_ERR_TOO_BIG;
+  int grid = pick_grid(c, biggest);
+  all_to_all_kernel<<<grid, kThreads, 0, MB_STREAM(stream)>>>(*c, seq, in, in_heap_off, out, *tab);
+  return check_launch();
+}
+
+extern "C" int mb_gather_scatter(const mb_comm_t* c, uint32_t seq, const mb_stage_copy_t* stage_in, int num_stage,
+                                 const mb_piece_t* pieces, int num_pieces, size_t max_bytes, void* stream) {
+  int grid = pick_grid(c, max_bytes);
+  gather_scatter_kernel<<<grid, kThreads, 0, MB_STREAM(stream)>>>(*c, seq, stage_in, num_stage, pieces, num_pieces);
+  return check_launch();
+}

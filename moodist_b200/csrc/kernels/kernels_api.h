@@ -39,25 +39,26 @@ enum { MB_SUM = 0, MB_AVG = 1, MB_MIN = 3, MB_MAX = 4, MB_PREMUL_SUM = 8 };
 #define MB_MAX_RANKS 8
 
 // Everything a collective kernel needs to know about the group's symmetric memory. All pointers are
-// addresses valid on THIS device: peer[r] is rank r's staging buffer mapped here (peer[rank] is the
-// local one), flags[r] is rank r's flag page mapped here. mc_* are NVLS multicast mappings or null.
+// addresses valid on THIS device: peer[r] is the base of rank r's symmetric heap as mapped here
+// (peer[rank] is the local heap), stage[r] / flags[r] are rank r's staging area and flag page mapped
+// here. The staging area has two halves used alternately by consecutive collectives.
 typedef struct {
   int rank;
   int world;
-  void* peer[MB_MAX_RANKS];
+  void* peer[MB_MAX_RANKS];   // heap base of each rank
+  void* stage[MB_MAX_RANKS];  // staging area of each rank
   uint32_t* flags[MB_MAX_RANKS];
-  void* mc_buf;         // multicast alias of the staging buffers (same offsets), or null
-  uint32_t* mc_flags;   // multicast alias of the flag pages, or null
-  uint32_t* status;     // local device word: 0 ok, else first failure code
-  uint64_t wait_ns;     // cap for device-side waits
+  uint64_t staging_bytes;  // both halves together
+  void* mc_stage;          // NVLS multicast alias of the staging areas, or null
+  uint32_t* mc_flags;      // NVLS multicast alias of the flag pages, or null
+  uint32_t* status;        // word the device can write (may be host-mapped): 0 ok, else code | peer << 16
+  uint64_t wait_ns;        // cap for device-side waits
+  int max_ctas;            // upper bound on CTAs a collective may occupy (0 = default)
 } mb_comm_t;
 
-// Flag page layout (uint32 words). Each rank owns one page of MB_FLAG_WORDS words.
-#define MB_FLAG_WORDS 4096
-#define MB_FLAG_BARRIER 0      // [MB_MAX_RANKS] arrival words written by peers (barrier "in")
-#define MB_FLAG_BARRIER2 16    // second bank for the exit barrier
-#define MB_FLAG_CHUNK 64       // [..] per-chunk / per-shard arrival words for fused ops
-#define MB_FLAG_LOCAL 1024     // CTA-arrival counters private to the local grid
+#define MB_FLAG_WORDS 4096  // uint32 words per flag page; layout in coll.cuh
+
+size_t mb_dtype_size(int dtype);
 
 // --- GEMM ------------------------------------------------------------------------------------
 // C[M,N] = A·B^T, bf16 inputs, fp32 accumulate. a_mn_major: A is given as [K,M] row-major instead of
@@ -66,53 +67,64 @@ int mb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
                  int a_mn_major, int b_mn_major, int out_fp32, int epilogue, uint32_t* status, uint64_t wait_ns,
                  void* stream);
 
-// --- collectives over symmetric staging buffers ------------------------------------------------
-// seq: per-group launch counter (monotone, same on every rank) used as the flag epoch.
-// variant: 0 = P2P (pull), 1 = NVLS multimem.
+// --- collectives -------------------------------------------------------------------------------
+// seq: per-group collective counter (starts at 1, +1 per call, identical on every rank).
+// *_heap_off: byte offset of the tensor inside this rank's symmetric heap when it lives there (peers
+// then read it in place and the kernel holds until they are done), or -1: the kernel stages it.
 int mb_barrier(const mb_comm_t* c, uint32_t seq, void* stream);
 
-// out[r*count .. (r+1)*count) = rank r's in[0..count). `in` may be null: then the input is already in
-// this rank's staging buffer at in_off. out is local memory; src/dst dtypes may differ (fused cast).
-int mb_all_gather(const mb_comm_t* c, uint32_t seq, const void* in, size_t in_off, void* out, size_t count,
-                  int in_dtype, int out_dtype, int variant, void* stream);
+// out[r*out_stride .. +count) = rank r's in[0..count), converted to out_dtype while staging.
+int mb_all_gather(const mb_comm_t* c, uint32_t seq, const void* in, int64_t in_heap_off, void* out, size_t count,
+                  size_t out_stride, int in_dtype, int out_dtype, void* stream);
 
-// out[0..count) = reduce over ranks r of (rank r's in[rank*count ..]) * scale, accumulated in fp32
-// (fp64 for f64, exact for ints). `in` is copied to staging first unless null (already at in_off).
-int mb_reduce_scatter(const mb_comm_t* c, uint32_t seq, const void* in, size_t in_off, void* out, size_t count,
-                      int in_dtype, int out_dtype, int op, float scale, int variant, void* stream);
+// out[0..count) = op over ranks r of rank r's in[rank*in_stride .. +count), accumulated in fp32 (fp64
+// for f64, int64 for integers), times 1/world for AVG or `premul` for PREMUL_SUM, converted to out_dtype.
+int mb_reduce_scatter(const mb_comm_t* c, uint32_t seq, const void* in, int64_t in_heap_off, void* out, size_t count,
+                      size_t in_stride, int in_dtype, int out_dtype, int op, float premul, void* stream);
 
-// in-place capable all-reduce of `count` elements. variant 0: one-shot (every rank reads all peers),
-// 1: two-shot in one launch (reduce-scatter then all-gather through staging), 2: NVLS.
+// all-reduce of `count` elements, in place allowed. variant 0: one-shot (each rank receives every
+// peer's vector and reduces), 1: two-shot in one launch (reduce at the owner, owner redistributes).
 int mb_all_reduce(const mb_comm_t* c, uint32_t seq, const void* in, void* out, size_t count, int dtype, int op,
-                  float scale, int variant, void* stream);
+                  float premul, int variant, void* stream);
 
-int mb_broadcast(const mb_comm_t* c, uint32_t seq, void* data, size_t bytes, int root, int variant, void* stream);
+int mb_broadcast(const mb_comm_t* c, uint32_t seq, void* data, int64_t heap_off, size_t bytes, int root, void* stream);
 
-// Uneven all-to-all of bytes: this rank sends send_bytes[r] from in+send_off[r] to rank r, which stores
-// it at out+recv_off (receiver's table). Tables live in device memory (8 entries each).
+// Uneven all-to-all of bytes: this rank sends send_bytes[r] from in+send_off[r] to rank r, and stores
+// what rank r sends at out+recv_off[r] (recv_bytes[r] must equal r's send_bytes[rank]).
 typedef struct {
   uint64_t send_off[MB_MAX_RANKS];
   uint64_t send_bytes[MB_MAX_RANKS];
   uint64_t recv_off[MB_MAX_RANKS];
   uint64_t recv_bytes[MB_MAX_RANKS];
 } mb_a2a_table_t;
-int mb_all_to_all(const mb_comm_t* c, uint32_t seq, const void* in, void* out, const mb_a2a_table_t* host_table,
-                  void* stream);
+int mb_all_to_all(const mb_comm_t* c, uint32_t seq, const void* in, int64_t in_heap_off, void* out,
+                  const mb_a2a_table_t* table, void* stream);
 
-// compile_op lowering: a list of 2-D pieces, each copied from (possibly peer) src to local dst.
+// compile_op lowering. Every rank first stages its inputs (stage_in: local tensor -> offset in its
+// staging half), then copies each 2-D piece from the source rank's staging area (or, for pieces whose
+// source is this rank, straight from src_local) into local dst.
 typedef struct {
   const void* src;
-  void* dst;
+  uint64_t dst_off;
+  uint64_t bytes;
+} mb_stage_copy_t;
+typedef struct {
+  int32_t src_rank;
   uint32_t rows;
-  uint32_t row_bytes;
+  uint64_t src_off;       // in the source rank's staging half
+  const void* src_local;  // non-null when src_rank == rank: read the input tensor directly
+  void* dst;
+  uint64_t row_bytes;
   uint64_t src_pitch;
   uint64_t dst_pitch;
 } mb_piece_t;
-// pieces: device array. Runs entry barrier, copies, exit barrier.
-int mb_gather_scatter(const mb_comm_t* c, uint32_t seq, const mb_piece_t* pieces, int num_pieces, void* stream);
+// stage_in / pieces are DEVICE arrays.
+int mb_gather_scatter(const mb_comm_t* c, uint32_t seq, const mb_stage_copy_t* stage_in, int num_stage,
+                      const mb_piece_t* pieces, int num_pieces, size_t max_bytes, void* stream);
 
-// plain local helpers (also used as world==1 paths)
-int mb_copy_cast(const void* in, void* out, size_t count, int in_dtype, int out_dtype, float scale, void* stream);
+// local cast / scale copy (also the world == 1 path of the collectives)
+int mb_copy_cast(const void* in, void* out, size_t count, int in_dtype, int out_dtype, float scale, int use_scale,
+                 void* stream);
 
 #ifdef __cplusplus
 }
