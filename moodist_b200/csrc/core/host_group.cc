@@ -1,9 +1,721 @@
 #include "host_group.h"
 
+#include <pthread.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <condition_variable>
+#include <cstring>
+#include <deque>
+#include <fstream>
+#include <list>
+#include <map>
+#include <mutex>
+#include <thread>
+
+#include "cpu_reduce.h"
 #include "log.h"
+#include "net.h"
+#include "tcp_transport.h"
 
 namespace moodist {
-std::unique_ptr<HostGroup> HostGroup::create(KVStore&, const std::string&, int, int) {
-  fail("moodist: the host engine is not built in this snapshot");
+namespace {
+
+// A blocked API call. The engine thread completes it; the caller sleeps in 1 s slices so that an engine
+// error (dead peer, heartbeat loss) can end the wait (reference: futex waits in 1 s / 10 s slices).
+struct Waiter {
+  std::mutex mu;
+  std::condition_variable cv;
+  bool done = false;
+  std::string error;
+  void finish(std::string err = {}) {
+    std::lock_guard<std::mutex> lk(mu);
+    done = true;
+    error = std::move(err);
+    cv.notify_all();
+  }
+};
+
+struct Announce {
+  uint64_t addr = 0;
+  uint32_t key = 0;
+  uint64_t size = 0;
+  uint64_t base_off = 0;  // where the receiver wants this particular sender's data to start
+};
+
+struct OutWrite {
+  int peer;
+  const void* src;
+  size_t bytes;
+  uint64_t remote_off;
+  bool posted = false;
+};
+
+// One collective in flight: a generic "everyone registers a receive buffer, announces it, and writes
+// into the others' buffers" exchange, the shape shared by every CPU collective here.
+struct Work {
+  uint32_t op = 0;
+  uint32_t step = 0;
+  void* recv_base = nullptr;
+  size_t recv_size = 0;
+  uint64_t expect_in = 0;
+  std::vector<uint64_t> base_off_for;  // per source rank (all_to_all), empty = 0
+  std::vector<OutWrite> outs;
+  bool need_all_announces = false;     // barrier semantics even with no data
+  std::function<void()> finish;        // runs on the engine thread when the exchange is complete
+  std::shared_ptr<Waiter> waiter;
+  std::string label;
+  // state
+  bool started = false;
+  uint32_t key = 0;
+  bool registered = false;
+  int acks_pending = 0;
+  bool failed = false;
+  double t0 = 0;
+};
+
+struct Mail {
+  uint32_t tag;
+  Bytes data;
+};
+
+class HostGroupImpl final : public HostGroup {
+ public:
+  HostGroupImpl(KVStore& store, std::string key, int rank, int world)
+      : name_(std::move(key)), rank_(rank), world_(world), transport_(poller_, name_, rank, world) {
+    last_heard_.assign(world, now_seconds());
+    peer_shutdown_.assign(world, 0);
+    heartbeat_s_ = (double)env_long("MOODIST_HEARTBEAT_MS", 30000) / 1000.0;
+    heartbeat_on_ = !env_flag("MOODIST_DISABLE_HEARTBEAT");
+    debug_cpu_ = env_flag("MOODIST_DEBUG_CPU");
+    transport_.on_recv([this](int src, Bytes payload) { on_message(src, std::move(payload)); });
+    transport_.on_error([this](int peer, const std::string& why) { on_peer_error(peer, why); });
+
+    // ---- bootstrap through the store: publish where this rank listens, learn the others
+    //      (keys as in the reference, core/processgroup.cc:977-1050) ----
+    std::vector<std::string> mine = transport_.listen();
+    const std::string pfx = "moodist/" + name_ + "/";
+    store.set_str(pfx + "moodist_pg_rank" + std::to_string(rank) + "_address", to_hex(encode(mine)));
+    std::vector<std::vector<std::string>> addrs(world);
+    for (int r = 0; r < world; ++r) {
+      if (r == rank) {
+        addrs[r] = mine;
+        continue;
+      }
+      Bytes b = from_hex(store.get_str(pfx + "moodist_pg_rank" + std::to_string(r) + "_address"));
+      decode_exact(b, addrs[r]);
+    }
+    transport_.connect_all(addrs);
+    thread_ = std::thread([this] { run(); });
+    // wait until the mesh is up (60 s like the reference's rank-info exchange, core/cputhread.cc:896-911)
+    double deadline = now_seconds() + (double)env_long("MOODIST_INIT_TIMEOUT_S", 60);
+    while (!mesh_ready_.load()) {
+      if (now_seconds() > deadline || in_error()) {
+        std::string why = in_error() ? error_text() : "timed out connecting to peers";
+        stop_thread();
+        fail("moodist: host engine start-up failed: " + why);
+      }
+      usleep(1000);
+    }
+    store.barrier(pfx + "moodist_ready", rank, world);
+  }
+
+  ~HostGroupImpl() override {
+    try {
+      shutdown();
+    } catch (...) {
+    }
+    stop_thread();
+  }
+
+  int rank() const override { return rank_; }
+  int world() const override { return world_; }
+  const std::string& name() const override { return name_; }
+
+  // ---------------------------------------------------------------------------------------------
+  // collectives (caller threads)
+  // ---------------------------------------------------------------------------------------------
+  void all_gather(const void* in, void* out, size_t bytes) override {
+    auto w = new_work(kOpAllGatherCpu, "all_gather");
+    uint8_t* o = static_cast<uint8_t*>(out);
+    if (o + (size_t)rank_ * bytes != in && bytes) memcpy(o + (size_t)rank_ * bytes, in, bytes);
+    w->recv_base = out;
+    w->recv_size = bytes * world_;
+    w->expect_in = (uint64_t)bytes * (world_ - 1);
+    for (int p = 0; p < world_; ++p)
+      if (p != rank_) w->outs.push_back({p, in, bytes, (uint64_t)rank_ * bytes});
+    submit_and_wait(w);
+  }
+
+  void reduce_scatter(const void* in, void* out, size_t count, int dtype, int op, double premul) override {
+    size_t esz = cpu_dtype_size(dtype);
+    if (!esz) fail("moodist: reduce_scatter: unsupported dtype for CPU tensors");
+    check_op(op);
+    size_t chunk = count * esz;
+    const uint8_t* x = static_cast<const uint8_t*>(in);
+    auto tmp = std::make_shared<Bytes>(chunk * world_);
+    auto w = new_work(kOpReduceScatterCpu, "reduce_scatter");
+    w->recv_base = tmp->data();
+    w->recv_size = tmp->size();
+    w->expect_in = (uint64_t)chunk * (world_ - 1);
+    for (int p = 0; p < world_; ++p)
+      if (p != rank_) w->outs.push_back({p, x + (size_t)p * chunk, chunk, (uint64_t)rank_ * chunk});
+    int world = world_, rank = rank_;
+    w->finish = [=] {
+      std::vector<const void*> srcs(world);
+      for (int r = 0; r < world; ++r) srcs[r] = r == rank ? (const void*)(x + (size_t)rank * chunk) : tmp->data() + (size_t)r * chunk;
+      double scale = op == kRedAvg ? 1.0 / world : premul;
+      bool use_scale = op == kRedAvg || op == kRedPremulSum;
+      cpu_reduce(out, srcs.data(), world, count, dtype, op, scale, use_scale);
+    };
+    submit_and_wait(w);
+  }
+
+  void all_reduce(const void* in, void* out, size_t count, int dtype, int op, double premul) override {
+    // reduce_scatter + all_gather over a [world, chunk] view, padded when count % world != 0
+    // (same decomposition as the reference, core/processgroup.cc:1674-1722)
+    size_t esz = cpu_dtype_size(dtype);
+    if (!esz) fail("moodist: all_reduce: unsupported dtype for CPU tensors");
+    if (count == 0) return;
+    if (world_ == 1) {
+      const void* srcs[1] = {in};
+      check_op(op);
+      cpu_reduce(out, srcs, 1, count, dtype, op, premul, op == kRedPremulSum);
+      return;
+    }
+    size_t chunk = (count + world_ - 1) / world_;
+    size_t padded = chunk * world_;
+    if (padded == count) {
+      Bytes mine(chunk * esz);
+      reduce_scatter(in, mine.data(), chunk, dtype, op, premul);
+      all_gather(mine.data(), out, chunk * esz);
+      return;
+    }
+    Bytes pin(padded * esz, 0), pout(padded * esz), mine(chunk * esz);
+    memcpy(pin.data(), in, count * esz);
+    reduce_scatter(pin.data(), mine.data(), chunk, dtype, op, premul);
+    all_gather(mine.data(), pout.data(), chunk * esz);
+    memcpy(out, pout.data(), count * esz);
+  }
+
+  void broadcast(void* data, size_t bytes, int root) override {
+    auto w = new_work(kOpBroadcastRingCpu, "broadcast");
+    if (rank_ == root) {
+      for (int p = 0; p < world_; ++p)
+        if (p != rank_) w->outs.push_back({p, data, bytes, 0});
+    } else {
+      w->recv_base = data;
+      w->recv_size = bytes;
+      w->expect_in = bytes;
+    }
+    submit_and_wait(w);
+  }
+
+  void gather(const void* in, void* out, size_t bytes, int root) override {
+    auto w = new_work(kOpGatherCpu, "gather");
+    if (rank_ == root) {
+      uint8_t* o = static_cast<uint8_t*>(out);
+      if (bytes) memcpy(o + (size_t)rank_ * bytes, in, bytes);
+      w->recv_base = out;
+      w->recv_size = bytes * world_;
+      w->expect_in = (uint64_t)bytes * (world_ - 1);
+    } else {
+      w->outs.push_back({root, in, bytes, (uint64_t)rank_ * bytes});
+    }
+    submit_and_wait(w);
+  }
+
+  void scatter(const void* in, void* out, size_t bytes, int root) override {
+    auto w = new_work(kOpScatterCpu, "scatter");
+    if (rank_ == root) {
+      const uint8_t* x = static_cast<const uint8_t*>(in);
+      if (bytes) memcpy(out, x + (size_t)rank_ * bytes, bytes);
+      for (int p = 0; p < world_; ++p)
+        if (p != rank_) w->outs.push_back({p, x + (size_t)p * bytes, bytes, 0});
+    } else {
+      w->recv_base = out;
+      w->recv_size = bytes;
+      w->expect_in = bytes;
+    }
+    submit_and_wait(w);
+  }
+
+  void all_to_all(const void* in, void* out, const uint64_t* send_off, const uint64_t* send_bytes,
+                  const uint64_t* recv_off, const uint64_t* recv_bytes) override {
+    auto w = new_work(kOpAllToAllCpu, "all_to_all");
+    const uint8_t* x = static_cast<const uint8_t*>(in);
+    uint8_t* o = static_cast<uint8_t*>(out);
+    size_t extent = 0;
+    w->base_off_for.assign(world_, 0);
+    for (int p = 0; p < world_; ++p) {
+      extent = std::max<size_t>(extent, recv_off[p] + recv_bytes[p]);
+      w->base_off_for[p] = recv_off[p];
+      if (p != rank_) {
+        w->expect_in += recv_bytes[p];
+        w->outs.push_back({p, x + send_off[p], (size_t)send_bytes[p], 0});
+      }
+    }
+    if (send_bytes[rank_]) memcpy(o + recv_off[rank_], x + send_off[rank_], send_bytes[rank_]);
+    w->recv_base = out;
+    w->recv_size = extent;
+    submit_and_wait(w);
+  }
+
+  void barrier() override {
+    auto w = new_work(kOpBarrier, "barrier");
+    w->need_all_announces = true;
+    submit_and_wait(w);
+  }
+
+  void send(const void* data, size_t bytes, int dst, uint32_t tag) override {
+    Writer wr;
+    wr(tag, (uint64_t)bytes);
+    wr.raw(data, bytes);
+    send_message(dst, kOpSendRecv, std::move(wr.out));
+  }
+
+  void recv(void* data, size_t bytes, int src, uint32_t tag) override {
+    auto waiter = std::make_shared<Waiter>();
+    run_on_engine([=, this] {
+      pending_recvs_.push_back(PendingRecv{src, tag, data, bytes, waiter});
+      match_recvs();
+    });
+    wait(*waiter, "recv");
+  }
+
+  // ---------------------------------------------------------------------------------------------
+  // messages
+  // ---------------------------------------------------------------------------------------------
+  void set_handler(uint32_t op, Handler h) override {
+    std::lock_guard<std::mutex> lk(handlers_mu_);
+    handlers_[op] = std::move(h);
+  }
+
+  void send_message(int dst, uint32_t op, Bytes body) override {
+    // header: u32 opType | u32 sourceRank | u32 seqid (reference: core/cputhread.cc:579-590)
+    auto send = [this, dst, op, body = std::move(body)]() mutable {
+      Writer w;
+      w(op, (uint32_t)rank_, next_seq_to_[dst]++);
+      w.raw(body.data(), body.size());
+      transport_.post_send(dst, std::move(w.out));
+    };
+    if (std::this_thread::get_id() == thread_.get_id())
+      send();
+    else
+      run_on_engine(std::move(send));
+  }
+
+  void run_on_engine(std::function<void()> fn) override {
+    {
+      std::lock_guard<std::mutex> lk(queue_mu_);
+      queue_.push_back(std::move(fn));
+    }
+    poller_.wake();
+  }
+
+  bool in_error() const override { return error_state_.load(); }
+  std::string error_text() const override {
+    std::lock_guard<std::mutex> lk(error_mu_);
+    return error_text_;
+  }
+
+  void shutdown() override {
+    if (shutdown_started_.exchange(true)) return;
+    if (!thread_.joinable()) return;
+    auto waiter = std::make_shared<Waiter>();
+    run_on_engine([this, waiter] {
+      shutting_down_ = true;
+      shutdown_waiter_ = waiter;
+      shutdown_deadline_ = now_seconds() + (double)env_long("MOODIST_SHUTDOWN_TIMEOUT_MS", 8000) / 1000.0;
+      for (int p = 0; p < world_; ++p)
+        if (p != rank_) send_message(p, kOpMessageShutdown, encode(true));
+      check_shutdown();
+    });
+    std::unique_lock<std::mutex> lk(waiter->mu);
+    waiter->cv.wait_for(lk, std::chrono::seconds(10), [&] { return waiter->done; });
+  }
+
+  void set_profiling(bool on) override {
+    auto waiter = std::make_shared<Waiter>();
+    run_on_engine([this, on, waiter] {
+      if (profiling_ && !on) flush_trace();
+      profiling_ = on;
+      waiter->finish();
+    });
+    std::unique_lock<std::mutex> lk(waiter->mu);
+    waiter->cv.wait_for(lk, std::chrono::seconds(10), [&] { return waiter->done; });
+  }
+  bool profiling() const override { return profiling_; }
+  std::string last_trace_path() const override {
+    std::lock_guard<std::mutex> lk(error_mu_);
+    return trace_path_;
+  }
+
+ private:
+  struct PendingRecv {
+    int src;
+    uint32_t tag;
+    void* data;
+    size_t bytes;
+    std::shared_ptr<Waiter> waiter;
+  };
+
+  void check_op(int op) {
+    if (op != kRedSum && op != kRedAvg && op != kRedMin && op != kRedMax && op != kRedPremulSum)
+      fail("moodist: unsupported reduce op (supported: SUM, AVG, MIN, MAX, PREMUL_SUM)");
+  }
+
+  std::shared_ptr<Work> new_work(uint32_t op, const char* label) {
+    auto w = std::make_shared<Work>();
+    w->op = op;
+    w->label = label;
+    w->waiter = std::make_shared<Waiter>();
+    return w;
+  }
+
+  void submit_and_wait(std::shared_ptr<Work> w) {
+    if (in_error()) fail("moodist: process group is in an error state: " + error_text());
+    // Collectives of one group must be issued by one thread at a time, in the same order on all ranks
+    // (the reference throws from a ThreadUnsafe guard, core/processgroup.cc:172-183).
+    if (busy_.exchange(true)) fail("moodist: concurrent collectives on one process group are not supported");
+    struct Unbusy {
+      std::atomic<bool>& b;
+      ~Unbusy() { b = false; }
+    } unbusy{busy_};
+    step_ += 0x1000;  // same stride as the reference's step values
+    w->step = step_;
+    run_on_engine([this, w] { works_.push_back(w); });
+    wait(*w->waiter, w->label.c_str());
+  }
+
+  void wait(Waiter& wt, const char* what) {
+    std::unique_lock<std::mutex> lk(wt.mu);
+    while (!wt.done) {
+      wt.cv.wait_for(lk, std::chrono::milliseconds(200));
+      if (!wt.done && in_error()) {
+        lk.unlock();
+        fail(std::string("moodist: ") + what + " failed: " + error_text());
+      }
+    }
+    if (!wt.error.empty()) fail(std::string("moodist: ") + what + " failed: " + wt.error);
+  }
+
+  void set_error(const std::string& why) {
+    {
+      std::lock_guard<std::mutex> lk(error_mu_);
+      if (error_text_.empty()) error_text_ = why;
+    }
+    if (!error_state_.exchange(true)) log_error("process group %s rank %d: %s", name_.c_str(), rank_, why.c_str());
+  }
+
+  void on_peer_error(int peer, const std::string& why) {
+    if (peer_shutdown_[peer] || shutting_down_) return;  // orderly exit of that peer
+    set_error(strf("connection to rank %d lost: %s", peer, why.c_str()));
+  }
+
+  void stop_thread() {
+    stop_ = true;
+    poller_.wake();
+    if (thread_.joinable()) thread_.join();
+  }
+
+  // ---------------------------------------------------------------------------------------------
+  // engine thread
+  // ---------------------------------------------------------------------------------------------
+  void run() {
+    pthread_setname_np(pthread_self(), "moodist-cputhrd");
+    double last_beat = now_seconds();
+    double last_iter = last_beat;
+    while (!stop_) {
+      bool busy = !works_.empty();
+      poller_.poll(busy ? 0 : 50);
+      double now = now_seconds();
+      if (debug_cpu_ && now - last_iter > 0.001 && busy) log_info("engine: lost %.1f ms between iterations", (now - last_iter) * 1e3);
+      last_iter = now;
+      if (!mesh_ready_.load() && transport_.all_connected()) mesh_ready_ = true;
+      // closures from other threads
+      std::deque<std::function<void()>> q;
+      {
+        std::lock_guard<std::mutex> lk(queue_mu_);
+        q.swap(queue_);
+      }
+      for (auto& f : q) f();
+      // progress
+      for (auto it = works_.begin(); it != works_.end();) {
+        if (step_work(**it))
+          it = works_.erase(it);
+        else
+          ++it;
+      }
+      if (heartbeat_on_ && mesh_ready_.load() && now - last_beat >= heartbeat_s_) {
+        last_beat = now;
+        heartbeat(now);
+      }
+      if (shutting_down_) check_shutdown();
+      if (shutdown_release_ && now >= shutdown_release_at_) {
+        shutdown_release_->finish();
+        shutdown_release_ = nullptr;
+      }
+    }
+    poller_.close_all();
+  }
+
+  void trace(const std::string& name, double t0, double t1, int tid) {
+    if (profiling_) trace_.push_back(TraceEvent{name, tid, t0 * 1e6, (t1 - t0) * 1e6});
+  }
+
+  void flush_trace() {
+    std::string path = "moodist-trace-cpu-" + name_ + "-" + std::to_string(rank_) + ".json";
+    std::ofstream f(path);
+    f << "{\"traceEvents\":[";
+    bool first = true;
+    for (auto& e : trace_) {
+      if (!first) f << ",";
+      first = false;
+      f << strf("{\"ph\":\"X\",\"name\":\"%s\",\"ts\":%.3f,\"dur\":%.3f,\"pid\":%d,\"tid\":%d}", e.name.c_str(), e.ts_us,
+                e.dur_us, rank_, e.tid);
+    }
+    f << "]}\n";
+    trace_.clear();
+    std::lock_guard<std::mutex> lk(error_mu_);
+    trace_path_ = path;
+  }
+
+  bool step_work(Work& w) {
+    if (error_state_) {
+      if (w.registered) MrTable::instance().remove(w.key);
+      w.waiter->finish(error_text());
+      return true;
+    }
+    if (!w.started) {
+      w.started = true;
+      w.t0 = now_seconds();
+      if (w.recv_size) {
+        w.key = MrTable::instance().add(w.recv_base, w.recv_size);
+        w.registered = true;
+      }
+      for (int p = 0; p < world_; ++p) {
+        if (p == rank_) continue;
+        uint64_t base_off = w.base_off_for.empty() ? 0 : w.base_off_for[p];
+        send_message(p, w.op, encode(w.step, (uint64_t)(uintptr_t)w.recv_base, w.key, (uint64_t)w.recv_size, base_off));
+      }
+    }
+    bool all_posted = true;
+    for (OutWrite& o : w.outs) {
+      if (o.posted) continue;
+      auto it = announces_.find(ann_key(w.step, o.peer));
+      if (it == announces_.end()) {
+        all_posted = false;
+        continue;
+      }
+      o.posted = true;
+      if (o.bytes == 0) continue;
+      const Announce& a = it->second;
+      ++w.acks_pending;
+      Work* wp = &w;
+      transport_.post_write(o.peer, o.src, o.bytes, a.key, (uintptr_t)(a.addr + a.base_off + o.remote_off),
+                            [this, wp](bool ok) {
+                              --wp->acks_pending;
+                              if (!ok) {
+                                wp->failed = true;
+                                set_error("a remote write was rejected (out of bounds or peer gone)");
+                              }
+                            });
+    }
+    if (!all_posted || w.acks_pending > 0) return false;
+    if (w.registered && MrTable::instance().landed(w.key) < w.expect_in) return false;
+    if (w.need_all_announces) {
+      for (int p = 0; p < world_; ++p)
+        if (p != rank_ && !announces_.count(ann_key(w.step, p))) return false;
+    }
+    // complete
+    if (w.registered) MrTable::instance().remove(w.key);
+    for (int p = 0; p < world_; ++p) announces_.erase(ann_key(w.step, p));
+    if (w.finish) w.finish();
+    trace(w.label, w.t0, now_seconds(), 0);
+    w.waiter->finish();
+    return true;
+  }
+
+  static uint64_t ann_key(uint32_t step, int peer) { return ((uint64_t)step << 16) | (uint32_t)peer; }
+
+  void on_message(int src, Bytes payload) {
+    try {
+      Reader r(payload);
+      uint32_t op, source, seq;
+      r(op, source, seq);
+      if ((int)source != src) {
+        set_error(strf("message from rank %d claims to be from rank %u", src, source));
+        return;
+      }
+      // TCP keeps order per connection; a gap or repeat means a lost / duplicated message
+      uint32_t& expect = next_seq_from_[src];
+      if (seq != expect) {
+        if ((int32_t)(seq - expect) < 0) return;  // duplicate: drop
+        set_error(strf("lost a message from rank %d (got sequence %u, expected %u)", src, seq, expect));
+        return;
+      }
+      ++expect;
+      last_heard_[src] = now_seconds();
+      switch (op) {
+        case kOpHeartbeat: return;
+        case kOpMessageShutdown: {
+          bool begin = r.read<bool>();
+          peer_shutdown_[src] = begin ? 1 : 2;
+          if (shutting_down_) check_shutdown();
+          return;
+        }
+        case kOpSendRecv: {
+          uint32_t tag;
+          uint64_t bytes;
+          r(tag, bytes);
+          Mail m;
+          m.tag = tag;
+          const uint8_t* b = r.take(bytes);
+          m.data.assign(b, b + bytes);
+          mailbox_[src].push_back(std::move(m));
+          match_recvs();
+          return;
+        }
+        case kOpBarrier:
+        case kOpAllGatherCpu:
+        case kOpReduceScatterCpu:
+        case kOpBroadcastRingCpu:
+        case kOpGatherCpu:
+        case kOpScatterCpu:
+        case kOpAllToAllCpu: {
+          uint32_t step;
+          Announce a;
+          r(step, a.addr, a.key, a.size, a.base_off);
+          // Mismatched collectives across ranks show up here as an announce whose op differs from the
+          // local work with the same step (reference: "Mismatched collectives detected", cputhread.h:100-112)
+          for (auto& w : works_) {
+            if (w->step == step && w->op != op) {
+              set_error(strf("mismatched collectives: rank %d runs op %u at step 0x%x, this rank runs %s (op %u)", src,
+                             op, step, w->label.c_str(), w->op));
+              return;
+            }
+          }
+          announces_[ann_key(step, src)] = a;
+          return;
+        }
+        default: break;
+      }
+      Handler h;
+      {
+        std::lock_guard<std::mutex> lk(handlers_mu_);
+        auto it = handlers_.find(op);
+        if (it != handlers_.end()) h = it->second;
+      }
+      if (h)
+        h(src, r);
+      else
+        log_error("engine: no handler for message type %u from rank %d", op, src);
+    } catch (const std::exception& e) {
+      set_error(strf("bad message from rank %d: %s", src, e.what()));
+    }
+  }
+
+  void match_recvs() {
+    for (auto it = pending_recvs_.begin(); it != pending_recvs_.end();) {
+      auto& box = mailbox_[it->src];
+      bool matched = false;
+      for (auto m = box.begin(); m != box.end(); ++m) {
+        if (m->tag != it->tag) continue;
+        if (m->data.size() != it->bytes) {
+          it->waiter->finish(strf("recv size mismatch: expected %zu bytes, message has %zu", it->bytes, m->data.size()));
+        } else {
+          if (it->bytes) memcpy(it->data, m->data.data(), it->bytes);
+          it->waiter->finish();
+        }
+        box.erase(m);
+        matched = true;
+        break;
+      }
+      if (matched)
+        it = pending_recvs_.erase(it);
+      else
+        ++it;
+    }
+  }
+
+  // Liveness: ping up to 16 neighbours on each side; silence for 3 intervals is logged, for 6 it puts
+  // the group into the error state (reference: core/cputhread.cc:5936-6016).
+  void heartbeat(double now) {
+    int reach = std::min(16, world_ - 1);
+    for (int d = 1; d <= reach; ++d) {
+      int a = (rank_ + d) % world_, b = (rank_ - d % world_ + world_) % world_;
+      send_message(a, kOpHeartbeat, {});
+      if (b != a) send_message(b, kOpHeartbeat, {});
+    }
+    for (int p = 0; p < world_; ++p) {
+      if (p == rank_ || peer_shutdown_[p]) continue;
+      int dist = std::min((p - rank_ + world_) % world_, (rank_ - p + world_) % world_);
+      if (dist > 16) continue;
+      double silent = now - last_heard_[p];
+      if (silent > 6 * heartbeat_s_) {
+        set_error(strf("no heartbeat from rank %d for %.1f s", p, silent));
+      } else if (silent > 3 * heartbeat_s_) {
+        log_error("process group %s rank %d: rank %d has been silent for %.1f s", name_.c_str(), rank_, p, silent);
+      }
+    }
+  }
+
+  // Coordinated shutdown: tell everyone, wait (bounded) until everyone said the same, then say "exited"
+  // (reference: core/cputhread.cc:5474-5580).
+  void check_shutdown() {
+    if (!shutdown_waiter_) return;
+    bool all = true;
+    for (int p = 0; p < world_; ++p)
+      if (p != rank_ && !peer_shutdown_[p]) all = false;
+    if (all || now_seconds() > shutdown_deadline_ || error_state_) {
+      for (int p = 0; p < world_; ++p)
+        if (p != rank_) send_message(p, kOpMessageShutdown, encode(false));
+      // the caller is released by the run loop a little later, so the final messages can leave the
+      // socket buffers (never poll from inside a handler: it would re-enter the connection being read)
+      shutdown_release_ = shutdown_waiter_;
+      shutdown_waiter_ = nullptr;
+      shutdown_release_at_ = now_seconds() + 0.02;
+    }
+  }
+
+  std::string name_;
+  int rank_, world_;
+  Poller poller_;
+  TcpTransport transport_;
+  std::thread thread_;
+  std::atomic<bool> stop_{false}, mesh_ready_{false}, error_state_{false}, busy_{false}, shutdown_started_{false};
+  mutable std::mutex error_mu_;
+  std::string error_text_, trace_path_;
+
+  std::mutex queue_mu_;
+  std::deque<std::function<void()>> queue_;
+  std::mutex handlers_mu_;
+  std::map<uint32_t, Handler> handlers_;
+
+  // engine-thread state
+  std::list<std::shared_ptr<Work>> works_;
+  std::map<uint64_t, Announce> announces_;
+  std::map<int, uint32_t> next_seq_to_, next_seq_from_;
+  std::map<int, std::deque<Mail>> mailbox_;
+  std::list<PendingRecv> pending_recvs_;
+  std::vector<double> last_heard_;
+  std::vector<int> peer_shutdown_;
+  bool shutting_down_ = false;
+  std::shared_ptr<Waiter> shutdown_waiter_, shutdown_release_;
+  double shutdown_deadline_ = 0, shutdown_release_at_ = 0;
+  double heartbeat_s_ = 30;
+  bool heartbeat_on_ = true, debug_cpu_ = false;
+  bool profiling_ = false;
+  std::vector<TraceEvent> trace_;
+
+  uint32_t step_ = 0;  // caller side, guarded by busy_
+};
+
+}  // namespace
+
+std::unique_ptr<HostGroup> HostGroup::create(KVStore& store, const std::string& key, int rank, int world) {
+  return std::make_unique<HostGroupImpl>(store, key, rank, world);
 }
+
 }  // namespace moodist

@@ -355,7 +355,8 @@ void Conn::handle_readable() {
         continue;
       }
       if (!on_data_) break;
-      size_t used = on_data_(inbuf_.data() + pos, inbuf_.size() - pos);
+      std::shared_ptr<DataFn> fn = on_data_;
+      size_t used = (*fn)(inbuf_.data() + pos, inbuf_.size() - pos);
       if (used == SIZE_MAX) {
         close("protocol error");
         return;

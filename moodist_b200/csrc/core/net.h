@@ -39,7 +39,7 @@ class Conn : public std::enable_shared_from_this<Conn> {
   int fd() const { return fd_; }
   bool open() const { return fd_ >= 0 && !closed_; }
 
-  void on_data(DataFn f) { on_data_ = std::move(f); }
+  void on_data(DataFn f) { on_data_ = f ? std::make_shared<DataFn>(std::move(f)) : nullptr; }
   void on_close(CloseFn f) { on_close_ = std::move(f); }
 
   // "Direct" receive: the next `n` incoming bytes are written straight into `dst` (no staging copy),
@@ -86,7 +86,7 @@ class Conn : public std::enable_shared_from_this<Conn> {
   uint8_t* direct_dst_ = nullptr;
   size_t direct_left_ = 0;
   std::function<void()> direct_done_;
-  DataFn on_data_;
+  std::shared_ptr<DataFn> on_data_;  // shared: a handler may replace itself while it runs
   CloseFn on_close_;
   std::function<void(bool)> on_connect_;
   std::deque<int> received_fds_;

@@ -1,0 +1,94 @@
+"""CPU-tensor collectives over the host engine and TCP transport, world size 2 and 3, checked against a
+single-process oracle (the seeded full input is known to every rank)."""
+
+import pytest
+import torch
+
+from moodist_b200.utils.testing import init_moodist, run_ranks
+
+
+def _full(world, n, dtype, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(world, n, generator=g)
+    if dtype in (torch.int32, torch.int64):
+        return (x * 100).to(dtype)
+    return x.to(dtype)
+
+
+def _collectives(rank, world, port, n):
+    dist = init_moodist(rank, world, port)
+    # all_reduce (sum)
+    full = _full(world, n, torch.float32)
+    t = full[rank].clone()
+    dist.all_reduce(t)
+    torch.testing.assert_close(t, full.sum(0), rtol=1e-5, atol=1e-5)
+    # all_gather_into_tensor
+    out = torch.empty(world * n)
+    dist.all_gather_into_tensor(out, full[rank].contiguous())
+    assert torch.equal(out.view(world, n), full)
+    # reduce_scatter_tensor (avg): rank r's input is [world, n]; chunk d goes to rank d
+    g = torch.Generator().manual_seed(1)
+    allin = torch.randn(world, world, n, generator=g)
+    o = torch.empty(n)
+    dist.reduce_scatter_tensor(o, allin[rank].reshape(-1).contiguous(), op=dist.ReduceOp.AVG)
+    torch.testing.assert_close(o, allin[:, rank].mean(0), rtol=1e-5, atol=1e-6)
+    # broadcast from rank 0
+    b = full[0].clone() if rank == 0 else torch.zeros(n)
+    dist.broadcast(b, src=0)
+    assert torch.equal(b, full[0])
+    # min / max / int / bf16
+    for dtype, op, ref in [
+        (torch.int64, dist.ReduceOp.MAX, lambda x: x.max(0).values),
+        (torch.int32, dist.ReduceOp.MIN, lambda x: x.min(0).values),
+        (torch.float64, dist.ReduceOp.SUM, lambda x: x.sum(0)),
+    ]:
+        f = _full(world, 257, dtype, seed=3)
+        t = f[rank].clone()
+        dist.all_reduce(t, op=op)
+        assert torch.equal(t, ref(f)), (dtype, op)
+    f = _full(world, 1000, torch.bfloat16, seed=4)
+    t = f[rank].clone()
+    dist.all_reduce(t)
+    torch.testing.assert_close(t.float(), f.float().sum(0), rtol=2e-2, atol=2e-2)
+    # gather / scatter / all_to_all / barrier
+    outs = [torch.empty(5) for _ in range(world)] if rank == 0 else None
+    dist.gather(torch.full((5,), float(rank)), outs, dst=0)
+    if rank == 0:
+        for r in range(world):
+            assert bool((outs[r] == r).all())
+    s = torch.empty(4)
+    dist.scatter(s, [torch.full((4,), float(10 + r)) for r in range(world)] if rank == 0 else None, src=0)
+    assert bool((s == 10 + rank).all())
+    splits = [[(s_ * 3 + d) % 4 for d in range(world)] for s_ in range(world)]
+    inp = torch.cat([torch.full((splits[rank][d], 2), float(rank * 10 + d)) for d in range(world)])
+    outp = torch.empty(sum(splits[s_][rank] for s_ in range(world)), 2)
+    dist.all_to_all_single(outp, inp, [splits[s_][rank] for s_ in range(world)], splits[rank])
+    ref = torch.cat([torch.full((splits[s_][rank], 2), float(s_ * 10 + rank)) for s_ in range(world)])
+    assert torch.equal(outp, ref)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n", [(2, 1 << 20), (3, 12345), (1, 100)])
+def test_cpu_collectives(world, n):
+    run_ranks(_collectives, world, n, timeout=120)
+
+
+def _odd_sizes(rank, world, port):
+    dist = init_moodist(rank, world, port)
+    for n in (1, 2, 3, 7, 9, 64, 255, 1024, 4097):
+        full = _full(world, n, torch.float32, seed=n)
+        t = full[rank].clone()
+        dist.all_reduce(t)
+        torch.testing.assert_close(t, full.sum(0), rtol=1e-5, atol=1e-5)
+    for i in range(100):  # back to back, mixed
+        t = torch.full((16,), float(rank + i))
+        dist.all_reduce(t)
+        assert bool((t == sum(r + i for r in range(world))).all())
+        o = torch.empty(world * 16)
+        dist.all_gather_into_tensor(o, t)
+    dist.destroy_process_group()
+
+
+def test_cpu_odd_sizes_and_stress():
+    run_ranks(_odd_sizes, 2, timeout=120)
