@@ -54,7 +54,7 @@ def generate(with_torch: bool = True) -> Path:
     BUILD.mkdir(parents=True, exist_ok=True)
     pyinc = sysconfig.get_paths()["include"]
 
-    cxx = os.environ.get("CXX", "g++")
+    cxx = os.environ.get("MOODIST_CXX", "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
     common = f"-O2 -g1 -fPIC -std=c++20 -Wall -Wno-unused-function -pthread -I{CSRC} -I{cuda}/include"
     nvcc_flags = (
         " ".join(ARCH_FLAGS)

@@ -38,13 +38,25 @@ cpu_allocator_debug = getattr(_C, "cpu_allocator_debug", None)
 cuda_copy = getattr(_C, "cuda_copy", None)
 set_prefer_kernel_less = getattr(_C, "set_prefer_kernel_less", None)
 
-try:
-    _serialize = _load("_serialize")
-    serialize = _serialize.serialize
-    deserialize = _serialize.deserialize
-except ImportError:  # the serializer is a separate library; everything else works without it
-    _serialize = None
-    serialize = None
-    deserialize = None
+_serialize = _load("_serialize")
+
+
+def serialize(obj) -> torch.Tensor:
+    """Serialize a Python object into a uint8 tensor (the reference's ``moodist.serialize``,
+    ``wrapper/serialize_wrapper.cc:58-118``). The tensor aliases the packed buffer; no copy is made."""
+    buf = _serialize.pack(obj)
+    if len(buf) == 0:  # cannot happen (every value has a tag byte), kept for torch.frombuffer's sake
+        return torch.empty(0, dtype=torch.uint8)
+    return torch.frombuffer(buf, dtype=torch.uint8)
+
+
+def deserialize(tensor: torch.Tensor):
+    """Inverse of :func:`serialize`; accepts any CPU uint8 tensor (or bytes-like object)."""
+    if isinstance(tensor, torch.Tensor):
+        if tensor.dtype != torch.uint8:
+            raise TypeError("moodist.deserialize expects a uint8 tensor")
+        tensor = tensor.detach().cpu().contiguous().numpy()
+    return _serialize.unpack(tensor)
+
 
 LIB_PATH = os.path.join(_HERE, "libmoodist_b200.so")

@@ -1,0 +1,641 @@
+// Python-object serializer (module `moodist_b200._serialize`): a faster, more compact pickle
+// replacement used by Queue.put_object / get_object and compile_op's metadata exchange.
+//
+// Byte format (identical to the reference, wrapper/serialize/serialize_object.cc:36-58, 293-337,
+// 524-556, 582-591, 651-748, 827-836, 854-859):
+//   every value starts with a one-byte tag
+//     0 none | 1 True | 2 False | 3 int8 | 4 int16 | 5 int32 | 6 int64 | 7 float (8-byte double)
+//     8 dict | 9 str (legacy, never written) | 10 list | 11 tuple | 12 bigint | 13 unicode | 14 bytes
+//     15 bytearray | 16 set | 17 frozenset | 18 global | 19 class | 20 offset
+//   ints use the smallest of 1/2/4/8 little-endian bytes; ints that are not "compact" in CPython
+//   (|v| >= 2^30) are written as bigint: u64 byte count + two's-complement little-endian bytes
+//   ((bits+7)/8 + 1 of them);
+//   list / tuple / dict carry their length as an int value (tag + bytes); set / frozenset as a raw u64;
+//   unicode = u8 kind (1, 2 or 4) + u64 byte count + raw UCS1/2/4 code units;
+//   bytes / bytearray = u64 count + bytes;
+//   global = qualified name value + module name value (functions and classes);
+//   class = callable value + args value + u8 bits {1 state, 2 list items, 4 dict items, 8 setstate} +
+//           [state [setstate]] [list value] [u64 n + n (key, value) pairs]   (from __reduce_ex__(5));
+//   shared and circular references: every container / string / object remembers the offset of its tag
+//   byte; when the same object is met again the ORIGINAL tag byte gets bit 0x80 set and an
+//   `offset` record (tag 20 + u64 offset) is written instead. A reader stores every value whose tag
+//   has 0x80 set under its offset before reading its children.
+//
+// Written against the CPython C API only (no pybind11), with explicit Packer / Unpacker classes.
+#define PY_SSIZE_T_CLEAN
+#include <Python.h>
+
+#include <cstdint>
+#include <cstring>
+#include <stdexcept>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+namespace {
+
+enum Tag : uint8_t {
+  T_NONE = 0,
+  T_TRUE = 1,
+  T_FALSE = 2,
+  T_INT8 = 3,
+  T_INT16 = 4,
+  T_INT32 = 5,
+  T_INT64 = 6,
+  T_FLOAT = 7,
+  T_DICT = 8,
+  T_STR = 9,
+  T_LIST = 10,
+  T_TUPLE = 11,
+  T_BIGINT = 12,
+  T_UNICODE = 13,
+  T_BYTES = 14,
+  T_BYTEARRAY = 15,
+  T_SET = 16,
+  T_FROZENSET = 17,
+  T_GLOBAL = 18,
+  T_CLASS = 19,
+  T_OFFSET = 20,
+};
+
+struct PyError {};  // a Python exception is already set
+
+struct Ref {  // owning reference
+  PyObject* p = nullptr;
+  Ref() = default;
+  explicit Ref(PyObject* o) : p(o) {}
+  Ref(const Ref&) = delete;
+  Ref& operator=(const Ref&) = delete;
+  Ref(Ref&& o) noexcept : p(o.p) { o.p = nullptr; }
+  Ref& operator=(Ref&& o) noexcept {
+    std::swap(p, o.p);
+    return *this;
+  }
+  ~Ref() { Py_XDECREF(p); }
+  PyObject* release() {
+    PyObject* r = p;
+    p = nullptr;
+    return r;
+  }
+  explicit operator bool() const { return p != nullptr; }
+};
+
+Ref checked(PyObject* o) {
+  if (!o) throw PyError{};
+  return Ref(o);
+}
+
+PyObject *s_qualname, *s_module, *s_reduce_ex, *s_dict, *s_setstate, *s_dot, *s_extend, *s_append, *s_five;
+
+void init_strings() {
+  if (s_qualname) return;
+  s_qualname = PyUnicode_InternFromString("__qualname__");
+  s_module = PyUnicode_InternFromString("__module__");
+  s_reduce_ex = PyUnicode_InternFromString("__reduce_ex__");
+  s_dict = PyUnicode_InternFromString("__dict__");
+  s_setstate = PyUnicode_InternFromString("__setstate__");
+  s_dot = PyUnicode_InternFromString(".");
+  s_extend = PyUnicode_InternFromString("extend");
+  s_append = PyUnicode_InternFromString("append");
+  s_five = PyLong_FromLong(5);
+}
+
+// ------------------------------------------------------------------------------------------------
+class Packer {
+ public:
+  std::vector<uint8_t> out;
+
+  void pack(PyObject* obj) {
+    if (obj == Py_None) return byte(T_NONE);
+    if (obj == Py_True) return byte(T_TRUE);
+    if (obj == Py_False) return byte(T_FALSE);
+    PyTypeObject* type = Py_TYPE(obj);
+    if (type == &PyLong_Type) return pack_long(obj);
+    if (type == &PyFloat_Type) {
+      byte(T_FLOAT);
+      double d = PyFloat_AS_DOUBLE(obj);
+      raw(&d, 8);
+      return;
+    }
+    // everything below is memoised by identity
+    auto [it, fresh] = memo_.try_emplace(obj, out.size());
+    if (!fresh) {
+      out[it->second] |= 0x80;
+      byte(T_OFFSET);
+      u64(it->second);
+      return;
+    }
+    if (depth_ > 2000) {
+      PyErr_SetString(PyExc_RecursionError, "moodist.serialize: object nesting too deep");
+      throw PyError{};
+    }
+    ++depth_;
+    pack_object(obj, type);
+    --depth_;
+  }
+
+ private:
+  std::unordered_map<PyObject*, size_t> memo_;
+  std::vector<Ref> keepalive_;  // temporaries (reduce results) must outlive the memo entries that point at them
+  int depth_ = 0;
+
+  void byte(uint8_t b) { out.push_back(b); }
+  void raw(const void* p, size_t n) {
+    const uint8_t* b = static_cast<const uint8_t*>(p);
+    out.insert(out.end(), b, b + n);
+  }
+  void u64(uint64_t v) { raw(&v, 8); }
+
+  void pack_int(int64_t v) {
+    if (v == (int8_t)v) {
+      byte(T_INT8);
+      int8_t x = (int8_t)v;
+      raw(&x, 1);
+    } else if (v == (int16_t)v) {
+      byte(T_INT16);
+      int16_t x = (int16_t)v;
+      raw(&x, 2);
+    } else if (v == (int32_t)v) {
+      byte(T_INT32);
+      int32_t x = (int32_t)v;
+      raw(&x, 4);
+    } else {
+      byte(T_INT64);
+      raw(&v, 8);
+    }
+  }
+
+  void pack_long(PyObject* obj) {
+    if (PyUnstable_Long_IsCompact((PyLongObject*)obj)) return pack_int((int64_t)PyUnstable_Long_CompactValue((PyLongObject*)obj));
+    size_t nbits = _PyLong_NumBits(obj);
+    if (nbits == (size_t)-1 && PyErr_Occurred()) throw PyError{};
+    size_t nbytes = (nbits + 7) / 8 + 1;
+    std::vector<unsigned char> tmp(nbytes);
+    if (_PyLong_AsByteArray((PyLongObject*)obj, tmp.data(), nbytes, 1, 1) < 0) throw PyError{};
+    byte(T_BIGINT);
+    u64(nbytes);
+    raw(tmp.data(), nbytes);
+  }
+
+  void pack_items(uint8_t tag, PyObject** items, Py_ssize_t n) {
+    byte(tag);
+    pack_int(n);
+    for (Py_ssize_t i = 0; i < n; ++i) pack(items[i]);
+  }
+
+  void pack_object(PyObject* obj, PyTypeObject* type) {
+    if (type == &PyList_Type) {
+      // the list may change size if a __reduce__ mutates it; index defensively
+      byte(T_LIST);
+      Py_ssize_t n = PyList_GET_SIZE(obj);
+      pack_int(n);
+      for (Py_ssize_t i = 0; i < n; ++i) {
+        if (i >= PyList_GET_SIZE(obj)) {
+          PyErr_SetString(PyExc_RuntimeError, "moodist.serialize: list changed size during serialization");
+          throw PyError{};
+        }
+        pack(PyList_GET_ITEM(obj, i));
+      }
+      return;
+    }
+    if (type == &PyTuple_Type) return pack_items(T_TUPLE, &PyTuple_GET_ITEM(obj, 0), PyTuple_GET_SIZE(obj));
+    if (type == &PyDict_Type) {
+      byte(T_DICT);
+      pack_int(PyDict_GET_SIZE(obj));
+      Py_ssize_t pos = 0;
+      PyObject *k, *v;
+      while (PyDict_Next(obj, &pos, &k, &v)) {
+        pack(k);
+        pack(v);
+      }
+      return;
+    }
+    if (type == &PyUnicode_Type) {
+      byte(T_UNICODE);
+      uint8_t kind = (uint8_t)PyUnicode_KIND(obj);
+      byte(kind);
+      uint64_t nbytes = (uint64_t)PyUnicode_GET_LENGTH(obj) * kind;
+      u64(nbytes);
+      raw(PyUnicode_DATA(obj), nbytes);
+      return;
+    }
+    if (type == &PyBytes_Type) {
+      byte(T_BYTES);
+      u64(PyBytes_GET_SIZE(obj));
+      raw(PyBytes_AS_STRING(obj), PyBytes_GET_SIZE(obj));
+      return;
+    }
+    if (type == &PyByteArray_Type) {
+      byte(T_BYTEARRAY);
+      u64(PyByteArray_GET_SIZE(obj));
+      raw(PyByteArray_AS_STRING(obj), PyByteArray_GET_SIZE(obj));
+      return;
+    }
+    if (type == &PySet_Type || type == &PyFrozenSet_Type) {
+      byte(type == &PySet_Type ? T_SET : T_FROZENSET);
+      u64(PySet_GET_SIZE(obj));
+      Ref it = checked(PyObject_GetIter(obj));
+      while (PyObject* item = PyIter_Next(it.p)) {
+        Ref hold(item);
+        pack(item);
+      }
+      if (PyErr_Occurred()) throw PyError{};
+      return;
+    }
+    // classes of any metaclass are globals (the reference only recognises exact `type`, so e.g. numpy.dtype fails there)
+    if (type == &PyFunction_Type || PyType_Check(obj)) return pack_global(obj);
+    if (type == &PyPickleBuffer_Type) {
+      // protocol-5 out-of-band buffers (numpy arrays reduce to these) are carried in-band, like pickle
+      // does without a buffer_callback: writable -> bytearray, read-only -> bytes. The reference cannot
+      // serialize these (tests/test_serialize.py:257-266).
+      const Py_buffer* view = PyPickleBuffer_GetBuffer(obj);
+      if (!view) throw PyError{};
+      if (!PyBuffer_IsContiguous(view, 'A')) {
+        PyErr_SetString(PyExc_ValueError, "moodist.serialize: cannot serialize a non-contiguous PickleBuffer");
+        throw PyError{};
+      }
+      byte(view->readonly ? T_BYTES : T_BYTEARRAY);
+      u64((uint64_t)view->len);
+      raw(view->buf, (size_t)view->len);
+      return;
+    }
+    pack_reduce(obj);
+  }
+
+  void pack_global(PyObject* obj) {
+    Ref name = checked(PyObject_GetAttr(obj, s_qualname));
+    Ref module = checked(PyObject_GetAttr(obj, s_module));
+    byte(T_GLOBAL);
+    pack_temp(std::move(name));
+    pack_temp(std::move(module));
+  }
+
+  // pack an object we own only temporarily: keep it alive so its address cannot be recycled for
+  // another object while it sits in the identity memo
+  void pack_temp(Ref r) {
+    PyObject* p = r.p;
+    keepalive_.push_back(std::move(r));
+    pack(p);
+  }
+
+  void pack_reduce(PyObject* obj) {
+    Ref fn = checked(PyObject_GetAttr(obj, s_reduce_ex));
+    Ref red = checked(PyObject_CallOneArg(fn.p, s_five));
+    if (PyUnicode_Check(red.p)) {  // "this is a global with that name"
+      Ref module = checked(PyObject_GetAttr(obj, s_module));
+      byte(T_GLOBAL);
+      pack_temp(std::move(red));
+      pack_temp(std::move(module));
+      return;
+    }
+    if (!PyTuple_Check(red.p)) {
+      PyErr_Format(PyExc_TypeError, "moodist.serialize: %s.__reduce__ must return a tuple or str", Py_TYPE(obj)->tp_name);
+      throw PyError{};
+    }
+    Py_ssize_t n = PyTuple_GET_SIZE(red.p);
+    if (n < 2) {
+      PyErr_Format(PyExc_TypeError, "moodist.serialize: %s.__reduce__ must return at least (callable, args)",
+                   Py_TYPE(obj)->tp_name);
+      throw PyError{};
+    }
+    auto item = [&](Py_ssize_t i) { return i < n ? PyTuple_GET_ITEM(red.p, i) : Py_None; };
+    PyObject *func = item(0), *args = item(1), *state = item(2), *listit = item(3), *dictit = item(4), *setstate = item(5);
+    PyObject* red_raw = red.p;
+    keepalive_.push_back(std::move(red));
+    (void)red_raw;
+    byte(T_CLASS);
+    pack(func);
+    pack(args);
+    uint8_t bits = (state != Py_None ? 1 : 0) | (listit != Py_None ? 2 : 0) | (dictit != Py_None ? 4 : 0) |
+                   (setstate != Py_None ? 8 : 0);
+    byte(bits);
+    if (bits & 1) {
+      pack(state);
+      if (bits & 8) pack(setstate);
+    }
+    if (bits & 2) {
+      std::vector<Ref> items;
+      while (PyObject* o = PyIter_Next(listit)) items.emplace_back(o);
+      if (PyErr_Occurred()) throw PyError{};
+      byte(T_LIST);
+      pack_int((int64_t)items.size());
+      for (Ref& r : items) pack_temp(std::move(r));
+    }
+    if (bits & 4) {
+      size_t at = out.size();
+      u64(0);
+      uint64_t count = 0;
+      while (PyObject* o = PyIter_Next(dictit)) {
+        Ref pair(o);
+        if (!PyTuple_Check(o) || PyTuple_GET_SIZE(o) != 2) {
+          PyErr_SetString(PyExc_TypeError, "moodist.serialize: dict item iterator must yield (key, value) pairs");
+          throw PyError{};
+        }
+        PyObject* k = PyTuple_GET_ITEM(o, 0);
+        PyObject* v = PyTuple_GET_ITEM(o, 1);
+        keepalive_.push_back(std::move(pair));
+        pack(k);
+        pack(v);
+        ++count;
+      }
+      if (PyErr_Occurred()) throw PyError{};
+      memcpy(out.data() + at, &count, 8);
+    }
+  }
+};
+
+// ------------------------------------------------------------------------------------------------
+class Unpacker {
+ public:
+  Unpacker(const uint8_t* data, size_t n) : base_(data), p_(data), end_(data + n) {}
+  ~Unpacker() {
+    for (auto& [off, o] : stored_) Py_DECREF(o);
+  }
+
+  size_t consumed() const { return (size_t)(p_ - base_); }
+
+  // returns a new reference
+  PyObject* unpack() {
+    size_t offset = consumed();
+    uint8_t tag = u8();
+    bool store = tag & 0x80;
+    tag &= 0x7f;
+    switch (tag) {
+      case T_NONE: Py_RETURN_NONE;
+      case T_TRUE: Py_RETURN_TRUE;
+      case T_FALSE: Py_RETURN_FALSE;
+      case T_INT8: return checked(PyLong_FromLong(read<int8_t>())).release();
+      case T_INT16: return checked(PyLong_FromLong(read<int16_t>())).release();
+      case T_INT32: return checked(PyLong_FromLong(read<int32_t>())).release();
+      case T_INT64: return checked(PyLong_FromLongLong(read<int64_t>())).release();
+      case T_FLOAT: return checked(PyFloat_FromDouble(read<double>())).release();
+      case T_BIGINT: {
+        uint64_t n = read<uint64_t>();
+        const uint8_t* b = take(n);
+        return checked(_PyLong_FromByteArray(b, n, 1, 1)).release();
+      }
+      case T_UNICODE: {
+        uint8_t kind = u8();
+        uint64_t nbytes = read<uint64_t>();
+        if (kind != 1 && kind != 2 && kind != 4) bad("bad unicode kind");
+        const uint8_t* b = take(nbytes);
+        return keep(store, offset, checked(PyUnicode_FromKindAndData(kind, b, (Py_ssize_t)(nbytes / kind))));
+      }
+      case T_STR:
+      case T_BYTES: {
+        uint64_t n = read<uint64_t>();
+        const uint8_t* b = take(n);
+        if (tag == T_STR) return keep(store, offset, checked(PyUnicode_DecodeUTF8((const char*)b, n, nullptr)));
+        return keep(store, offset, checked(PyBytes_FromStringAndSize((const char*)b, n)));
+      }
+      case T_BYTEARRAY: {
+        uint64_t n = read<uint64_t>();
+        const uint8_t* b = take(n);
+        return keep(store, offset, checked(PyByteArray_FromStringAndSize((const char*)b, n)));
+      }
+      case T_LIST: {
+        int64_t n = unpack_len();
+        Ref list = checked(PyList_New(n));
+        if (store) remember(offset, list.p);
+        for (int64_t i = 0; i < n; ++i) PyList_SET_ITEM(list.p, i, unpack());
+        return list.release();
+      }
+      case T_TUPLE: {
+        int64_t n = unpack_len();
+        Ref tup = checked(PyTuple_New(n));
+        // a tuple can only reach itself through a mutable member, which is stored on its own
+        for (int64_t i = 0; i < n; ++i) PyTuple_SET_ITEM(tup.p, i, unpack());
+        if (store) remember(offset, tup.p);
+        return tup.release();
+      }
+      case T_DICT: {
+        int64_t n = unpack_len();
+        Ref d = checked(PyDict_New());
+        if (store) remember(offset, d.p);
+        for (int64_t i = 0; i < n; ++i) {
+          Ref k(unpack());
+          Ref v(unpack());
+          if (PyDict_SetItem(d.p, k.p, v.p) < 0) throw PyError{};
+        }
+        return d.release();
+      }
+      case T_SET:
+      case T_FROZENSET: {
+        uint64_t n = read<uint64_t>();
+        if (n > remaining()) bad("set length exceeds buffer");
+        Ref s = checked(PySet_New(nullptr));
+        if (store && tag == T_SET) remember(offset, s.p);
+        for (uint64_t i = 0; i < n; ++i) {
+          Ref item(unpack());
+          if (PySet_Add(s.p, item.p) < 0) throw PyError{};
+        }
+        if (tag == T_SET) return s.release();
+        Ref fs = checked(PyFrozenSet_New(s.p));
+        if (store) remember(offset, fs.p);
+        return fs.release();
+      }
+      case T_GLOBAL: return keep(store, offset, unpack_global());
+      case T_CLASS: return unpack_class(store, offset);
+      case T_OFFSET: {
+        uint64_t off = read<uint64_t>();
+        auto it = stored_.find(off);
+        if (it == stored_.end()) bad("reference to an object that was not stored");
+        Py_INCREF(it->second);
+        return it->second;
+      }
+      default: bad("unknown type tag");
+    }
+    return nullptr;
+  }
+
+ private:
+  const uint8_t *base_, *p_, *end_;
+  std::unordered_map<size_t, PyObject*> stored_;
+
+  [[noreturn]] void bad(const char* what) {
+    PyErr_Format(PyExc_ValueError, "moodist.deserialize: %s (at byte %zu)", what, consumed());
+    throw PyError{};
+  }
+  size_t remaining() const { return (size_t)(end_ - p_); }
+  const uint8_t* take(uint64_t n) {
+    if (n > remaining()) bad("truncated buffer");
+    const uint8_t* r = p_;
+    p_ += n;
+    return r;
+  }
+  uint8_t u8() { return *take(1); }
+  template <typename T>
+  T read() {
+    T v;
+    memcpy(&v, take(sizeof(T)), sizeof(T));
+    return v;
+  }
+  void remember(size_t offset, PyObject* o) {
+    Py_INCREF(o);
+    auto [it, fresh] = stored_.try_emplace(offset, o);
+    if (!fresh) {
+      Py_DECREF(it->second);
+      it->second = o;
+    }
+  }
+  PyObject* keep(bool store, size_t offset, Ref r) {
+    if (store) remember(offset, r.p);
+    return r.release();
+  }
+
+  int64_t unpack_len() {
+    uint8_t tag = u8() & 0x7f;
+    int64_t n;
+    switch (tag) {
+      case T_NONE: n = 0; break;
+      case T_INT8: n = read<int8_t>(); break;
+      case T_INT16: n = read<int16_t>(); break;
+      case T_INT32: n = read<int32_t>(); break;
+      case T_INT64: n = read<int64_t>(); break;
+      default: bad("expected a length");
+    }
+    if (n < 0 || (uint64_t)n > remaining()) bad("length exceeds buffer");
+    return n;
+  }
+
+  Ref unpack_global() {
+    Ref name(unpack());
+    Ref module(unpack());
+    if (!PyUnicode_Check(name.p) || !PyUnicode_Check(module.p)) bad("global name/module must be str");
+    Ref obj = checked(PyImport_Import(module.p));
+    Ref parts = checked(PyUnicode_Split(name.p, s_dot, -1));
+    for (Py_ssize_t i = 0; i < PyList_GET_SIZE(parts.p); ++i) obj = checked(PyObject_GetAttr(obj.p, PyList_GET_ITEM(parts.p, i)));
+    return obj;
+  }
+
+  PyObject* unpack_class(bool store, size_t offset) {
+    Ref func(unpack());
+    Ref args(unpack());
+    if (!PyTuple_Check(args.p)) bad("class args must be a tuple");
+    Ref obj = checked(PyObject_Call(func.p, args.p, nullptr));
+    if (store) remember(offset, obj.p);
+    uint8_t bits = u8();
+    if (bits & 1) {
+      Ref state(unpack());
+      if (bits & 8) {
+        Ref setstate(unpack());
+        checked(PyObject_CallFunctionObjArgs(setstate.p, obj.p, state.p, nullptr));
+      } else if (PyObject_HasAttr(obj.p, s_setstate) && has_custom_setstate(obj.p)) {
+        checked(PyObject_CallMethodOneArg(obj.p, s_setstate, state.p));
+      } else {
+        apply_default_state(obj.p, state.p);
+      }
+    }
+    if (bits & 2) {
+      Ref items(unpack());
+      if (PyObject_HasAttr(obj.p, s_extend)) {
+        checked(PyObject_CallMethodOneArg(obj.p, s_extend, items.p));
+      } else {
+        for (Py_ssize_t i = 0; i < PyList_GET_SIZE(items.p); ++i)
+          checked(PyObject_CallMethodOneArg(obj.p, s_append, PyList_GET_ITEM(items.p, i)));
+      }
+    }
+    if (bits & 4) {
+      uint64_t n = read<uint64_t>();
+      for (uint64_t i = 0; i < n; ++i) {
+        Ref k(unpack());
+        Ref v(unpack());
+        if (PyObject_SetItem(obj.p, k.p, v.p) < 0) throw PyError{};
+      }
+    }
+    return obj.release();
+  }
+
+  static bool has_custom_setstate(PyObject* obj) {
+    // object.__setstate__ does not exist before 3.11; from 3.11 on a default one is absent too, so any
+    // __setstate__ found is the class's own
+    (void)obj;
+    return true;
+  }
+
+  // pickle's default: state is a dict for __dict__, or (dict_state, slots_state)
+  void apply_default_state(PyObject* obj, PyObject* state) {
+    PyObject* dstate = state;
+    PyObject* slots = nullptr;
+    if (PyTuple_Check(state) && PyTuple_GET_SIZE(state) == 2) {
+      dstate = PyTuple_GET_ITEM(state, 0);
+      slots = PyTuple_GET_ITEM(state, 1);
+    }
+    if (dstate != Py_None) {
+      if (!PyDict_Check(dstate)) bad("object state is not a dict");
+      Ref d = checked(PyObject_GetAttr(obj, s_dict));
+      Py_ssize_t pos = 0;
+      PyObject *k, *v;
+      while (PyDict_Next(dstate, &pos, &k, &v)) {
+        if (PyUnicode_CheckExact(k)) {
+          Py_INCREF(k);
+          PyUnicode_InternInPlace(&k);
+          int rc = PyObject_SetItem(d.p, k, v);
+          Py_DECREF(k);
+          if (rc < 0) throw PyError{};
+        } else if (PyObject_SetItem(d.p, k, v) < 0) {
+          throw PyError{};
+        }
+      }
+    }
+    if (slots && slots != Py_None) {
+      if (!PyDict_Check(slots)) bad("slots state is not a dict");
+      Py_ssize_t pos = 0;
+      PyObject *k, *v;
+      while (PyDict_Next(slots, &pos, &k, &v))
+        if (PyObject_SetAttr(obj, k, v) < 0) throw PyError{};
+    }
+  }
+};
+
+// ------------------------------------------------------------------------------------------------
+PyObject* py_pack(PyObject*, PyObject* obj) {
+  init_strings();
+  try {
+    Packer pk;
+    pk.out.reserve(256);
+    pk.pack(obj);
+    return PyByteArray_FromStringAndSize((const char*)pk.out.data(), (Py_ssize_t)pk.out.size());
+  } catch (const PyError&) {
+    return nullptr;
+  } catch (const std::exception& e) {
+    PyErr_SetString(PyExc_RuntimeError, e.what());
+    return nullptr;
+  }
+}
+
+PyObject* py_unpack(PyObject*, PyObject* arg) {
+  init_strings();
+  Py_buffer view;
+  if (PyObject_GetBuffer(arg, &view, PyBUF_SIMPLE) < 0) return nullptr;
+  PyObject* result = nullptr;
+  try {
+    Unpacker up((const uint8_t*)view.buf, (size_t)view.len);
+    result = up.unpack();
+    if (result && up.consumed() != (size_t)view.len) {
+      Py_DECREF(result);
+      result = nullptr;
+      PyErr_Format(PyExc_ValueError, "moodist.deserialize: %zu trailing bytes", (size_t)view.len - up.consumed());
+    }
+  } catch (const PyError&) {
+    result = nullptr;
+  } catch (const std::exception& e) {
+    PyErr_SetString(PyExc_RuntimeError, e.what());
+    result = nullptr;
+  }
+  PyBuffer_Release(&view);
+  return result;
+}
+
+PyMethodDef methods[] = {
+    {"pack", py_pack, METH_O, "pack(obj) -> bytearray in the moodist object format"},
+    {"unpack", py_unpack, METH_O, "unpack(buffer) -> object"},
+    {nullptr, nullptr, 0, nullptr},
+};
+
+PyModuleDef module_def = {PyModuleDef_HEAD_INIT, "_serialize", "moodist Python-object serializer", -1, methods,
+                          nullptr, nullptr, nullptr, nullptr};
+
+}  // namespace
+
+PyMODINIT_FUNC PyInit__serialize(void) { return PyModule_Create(&module_def); }

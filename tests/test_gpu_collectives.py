@@ -1,0 +1,64 @@
+"""CUDA collectives on 2 GPUs (P2P kernels over the symmetric heap) against CPU oracles."""
+
+import pytest
+import torch
+
+from moodist_b200.utils.testing import init_moodist, run_ranks
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _cuda_collectives(rank, world, port):
+    dist = init_moodist(rank, world, port, device="cuda")
+    dev = torch.device("cuda", rank)
+    for dtype in (torch.float32, torch.bfloat16, torch.int64):
+        for n in (1, 7, 1000, 65536, (1 << 20) + 3):
+            g = torch.Generator().manual_seed(n)
+            full = (torch.randn(world, n, generator=g) * 10).to(dtype)
+            out = torch.empty(world * n, device=dev, dtype=dtype)
+            dist.all_gather_into_tensor(out, full[rank].to(dev).contiguous())
+            assert torch.equal(out.cpu().view(world, n), full), ("all_gather", dtype, n)
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2), (torch.int32, 0)):
+        for op in (dist.ReduceOp.SUM, dist.ReduceOp.AVG, dist.ReduceOp.MAX, dist.ReduceOp.MIN):
+            if dtype == torch.int32 and op == dist.ReduceOp.AVG:
+                continue
+            for n in (1, 9, 4096, (1 << 18) + 5):
+                g = torch.Generator().manual_seed(n)
+                allin = (torch.randn(world, world, n, generator=g) * 4).to(dtype)
+                out = torch.empty(n, device=dev, dtype=dtype)
+                dist.reduce_scatter_tensor(out, allin[rank].reshape(-1).to(dev).contiguous(), op=op)
+                col = allin[:, rank].double()
+                ref = {dist.ReduceOp.SUM: col.sum(0), dist.ReduceOp.AVG: col.mean(0), dist.ReduceOp.MAX: col.max(0).values,
+                       dist.ReduceOp.MIN: col.min(0).values}[op]
+                err = (out.double().cpu() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
+                assert err <= tol, ("reduce_scatter", dtype, op, n, err)
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 3e-2)):
+        for n in (1, 5, 1000, 70000, (1 << 20) + 11):  # one-shot and two-shot paths
+            g = torch.Generator().manual_seed(n)
+            allin = torch.randn(world, n, generator=g).to(dtype)
+            t = allin[rank].to(dev).contiguous()
+            dist.all_reduce(t)
+            ref = allin.double().sum(0)
+            err = (t.double().cpu() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
+            assert err <= tol, ("all_reduce", dtype, n, err)
+    for root in (0, world - 1):
+        t = torch.full((100001,), float(rank + 1), device=dev)
+        dist.broadcast(t, src=root)
+        assert bool((t == root + 1).all())
+    torch.manual_seed(1234)
+    splits = torch.randint(0, 50, (world, world))
+    H = 64
+    inp = torch.cat([torch.full((int(splits[rank, d]), H), rank * 100 + d, dtype=torch.bfloat16) for d in range(world)]).to(dev)
+    out = torch.empty(int(splits[:, rank].sum()), H, dtype=torch.bfloat16, device=dev)
+    dist.all_to_all_single(out, inp, [int(x) for x in splits[:, rank]], [int(x) for x in splits[rank]])
+    ref = torch.cat([torch.full((int(splits[s, rank]), H), s * 100 + rank, dtype=torch.bfloat16) for s in range(world)])
+    assert torch.equal(out.cpu(), ref)
+    dist.barrier()
+    import moodist_b200
+
+    assert moodist_b200.get_backend().kernel_launches() > 0
+    dist.destroy_process_group()
+
+
+def test_cuda_collectives_2gpu():
+    run_ranks(_cuda_collectives, 2, timeout=240, env={"MOODIST_DEVICE_TIMEOUT_MS": 5000})

@@ -1,0 +1,162 @@
+"""Python-object serializer: golden bytes of the wire format plus round trips, following the cases of
+the reference's tests/test_serialize.py (every tag, big ints, special floats, UCS kinds, shared and
+circular references, functions, types, custom __reduce__, numpy arrays)."""
+
+import collections
+import math
+import struct
+
+import pytest
+import torch
+
+import moodist_b200 as moodist
+
+
+def pack(obj) -> bytes:
+    t = moodist.serialize(obj)
+    assert isinstance(t, torch.Tensor) and t.dtype == torch.uint8 and t.dim() == 1
+    return bytes(t.numpy())
+
+
+def roundtrip(obj):
+    return moodist.deserialize(moodist.serialize(obj))
+
+
+GOLDEN = [
+    (None, "00"),
+    (True, "01"),
+    (False, "02"),
+    (0, "0300"),
+    (-1, "03ff"),
+    (127, "037f"),
+    (128, "048000"),
+    (-129, "047fff"),
+    (70000, "0570110100"),
+    (2**30 - 1, "05ffffff3f"),
+    (1.5, "07" + struct.pack("<d", 1.5).hex()),
+    ("a", "0d01" + "0100000000000000" + "61"),
+    ("é", "0d01" + "0100000000000000" + "e9"),
+    ("中", "0d02" + "0200000000000000" + "2d4e"),
+    ("\U0001f600", "0d04" + "0400000000000000" + "00f60100"),
+    (b"xy", "0e" + "0200000000000000" + "7879"),
+    (bytearray(b"z"), "0f" + "0100000000000000" + "7a"),
+    ([], "0a0300"),
+    ([1, 300, "a", None], "0a0304" + "0301" + "042c01" + "0d01010000000000000061" + "00"),
+    ((1, 2), "0b0302" + "0301" + "0302"),
+    ({"k": 1}, "080301" + "0d0101000000000000006b" + "0301"),
+    ({5}, "10" + "0100000000000000" + "0305"),
+    (frozenset({5}), "11" + "0100000000000000" + "0305"),
+    # ints that CPython does not store compactly (>= 2**30) travel as bigint: u64 count + LE two's complement
+    (2**30, "0c" + "0500000000000000" + "0000004000"),
+    (2**64, "0c" + "0a00000000000000" + "00" * 8 + "0100"),
+    (len, "12" + "0d0103000000000000006c656e" + "0d01" + "0800000000000000" + b"builtins".hex()),
+]
+
+
+@pytest.mark.parametrize("obj,hexbytes", GOLDEN, ids=[repr(g[0])[:20] for g in GOLDEN])
+def test_golden_bytes(obj, hexbytes):
+    assert pack(obj).hex() == hexbytes
+    assert roundtrip(obj) == obj
+
+
+def test_shared_reference_marks_original_tag():
+    shared = [7]
+    data = pack([shared, shared])
+    # outer list @0, first inner list @3 gets 0x80, second occurrence is `offset` (tag 20) + u64 3
+    assert data.hex() == "0a0302" + "8a03010307" + "14" + "0300000000000000"
+    r = roundtrip([shared, shared])
+    assert r[0] is r[1] and r[0] == [7]
+
+
+def test_circular_reference():
+    l = [1, 2]
+    l.append(l)
+    r = roundtrip(l)
+    assert r[0] == 1 and r[2] is r
+    d = {}
+    d["self"] = d
+    r = roundtrip(d)
+    assert r["self"] is r
+
+
+def test_scalars_and_special_floats():
+    for v in (0, 1, -1, 2**7, -(2**7), 2**15, -(2**15) - 1, 2**31, -(2**31) - 1, 2**62, 2**63, -(2**63), 2**200, -(2**200)):
+        assert roundtrip(v) == v
+    assert roundtrip(float("inf")) == float("inf")
+    assert roundtrip(float("-inf")) == float("-inf")
+    assert math.isnan(roundtrip(float("nan")))
+    assert math.copysign(1, roundtrip(-0.0)) == -1
+
+
+def test_containers_nested():
+    obj = {"a": [1, (2, 3), {"b": {4, 5}}], "c": frozenset({6}), 7: None, (8, 9): b"ten", "e": bytearray(b"11")}
+    assert roundtrip(obj) == obj
+    big = list(range(-1000, 1000))
+    assert roundtrip(big) == big
+
+
+def top_level_function(x):
+    return x + 1
+
+
+class Point:
+    def __init__(self, x, y):
+        self.x, self.y = x, y
+
+    def __eq__(self, o):
+        return type(o) is Point and (o.x, o.y) == (self.x, self.y)
+
+
+class WithReduce:
+    def __init__(self, v):
+        self.v = v
+
+    def __reduce__(self):
+        return (WithReduce, (self.v * 2,))
+
+
+class WithSlots:
+    __slots__ = ("a", "b")
+
+    def __init__(self):
+        self.a, self.b = 1, [2]
+
+
+def test_functions_types_and_objects():
+    assert roundtrip(top_level_function) is top_level_function
+    assert roundtrip(Point) is Point
+    assert roundtrip(collections.OrderedDict) is collections.OrderedDict
+    assert roundtrip(Point(1, [2, 3])) == Point(1, [2, 3])
+    assert roundtrip(WithReduce(21)).v == 42
+    s = roundtrip(WithSlots())
+    assert s.a == 1 and s.b == [2]
+    od = collections.OrderedDict(a=1, b=2)
+    r = roundtrip(od)
+    assert r == od and type(r) is collections.OrderedDict
+    dd = collections.defaultdict(list)
+    dd["k"].append(1)
+    r = roundtrip(dd)
+    assert r == dd and r.default_factory is list
+    dq = collections.deque([1, 2, 3], maxlen=5)
+    r = roundtrip(dq)
+    assert r == dq and r.maxlen == 5
+
+
+def test_numpy_and_torch_payloads():
+    np = pytest.importorskip("numpy")
+    a = np.arange(12.0).reshape(3, 4)
+    r = roundtrip(a)
+    assert isinstance(r, np.ndarray) and (r == a).all() and r.dtype == a.dtype
+    t = torch.arange(6.0).view(2, 3)
+    assert torch.equal(roundtrip(t), t)
+
+
+def test_errors():
+    with pytest.raises(ValueError):
+        moodist.deserialize(torch.tensor([10, 3, 5, 3], dtype=torch.uint8))  # list of 5 but truncated
+    with pytest.raises(ValueError):
+        moodist.deserialize(torch.tensor([99], dtype=torch.uint8))  # unknown tag
+    with pytest.raises(ValueError):
+        moodist.deserialize(torch.tensor([0, 0], dtype=torch.uint8))  # trailing bytes
+    with pytest.raises(TypeError):
+        moodist.deserialize(torch.zeros(2))
