@@ -74,8 +74,8 @@ def main():
         g = torch.Generator().manual_seed(1000 * rank + i)
         return torch.randint(0, cfg.vocab_size, (1, seq + 1), generator=g, dtype=torch.int64).pin_memory()
 
-    batches = [host_batch(i) for i in range(args.warmup + args.steps)]
-    dev_batches = [b.to(dev) for b in batches]
+    batches = [host_batch(i) for i in range(args.warmup + 2 * args.steps)]
+    dev_batches = [b.to(dev) for b in batches[: args.warmup + args.steps]]
 
     def fence():
         dist.barrier()
@@ -108,7 +108,7 @@ def main():
     e2.record()
     last = 0.0
     for i in range(args.steps):
-        last = trainer.step(batches[args.warmup + i])
+        last = trainer.step(batches[args.warmup + args.steps + i])
     e3.record()
     fence()
     ms2 = torch.tensor([e2.elapsed_time(e3)], device=dev, dtype=torch.float32)

@@ -12,6 +12,12 @@ using BackendClass = pybind11::class_<MoodistBackend, c10d::Backend, c10::intrus
 // ops.cc: GEMM and fused ops
 void bind_ops(pybind11::module_& m, BackendClass& backend);
 
-inline void bind_extras(pybind11::module_& m, BackendClass& backend) { bind_ops(m, backend); }
+// store_glue.cc: TcpStore
+void bind_store(pybind11::module_& m);
+
+inline void bind_extras(pybind11::module_& m, BackendClass& backend) {
+  bind_ops(m, backend);
+  bind_store(m);
+}
 
 }  // namespace moodist

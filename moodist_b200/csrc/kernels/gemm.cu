@@ -27,8 +27,20 @@ static EncodeFn get_encode() {
 
 // 2-D bf16 tensor map over a row-major [rows, cols] matrix with row pitch `ld` elements,
 // box = [box_rows, 64 columns] with the 128-byte swizzle the MMA descriptors expect.
+// cuTensorMapEncodeTiled is a raw driver call and needs a current context. A thread that has only ever
+// used another CUDA runtime instance (torch's autograd workers) may not have bound one for this runtime
+// yet; any runtime call that initialises the device does it.
+static void ensure_context() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 int make_tmap_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
   EncodeFn enc = get_encode();
+  ensure_context();
   if (!enc) return MB_ERR_DRIVER;
   if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 2) & 15)) return MB_ERR_ALIGN;
   cuuint64_t dims[2] = {cols, rows};

@@ -144,4 +144,4 @@ class Llama(nn.Module):
 
 
 def loss_fn(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
-    return F.cross_entropy(logits.float().view(-1, logits.shape[-1]), targets.view(-1))
+    return F.cross_entropy(logits.float().reshape(-1, logits.shape[-1]), targets.reshape(-1))
