@@ -21,6 +21,7 @@ from ._core import (
 )
 from .backend import find_process_group, create_moodist_backend, get_backend, PreferKernelLessContext
 from .options import MoodistOptions, MoodistOptionsContext, install as _install_options
+from .queue import Queue, TransactionContextManager
 
 _install_options(MoodistProcessGroup)
 
@@ -37,6 +38,8 @@ __all__ = [
     "TcpStore",
     "serialize",
     "deserialize",
+    "Queue",
+    "TransactionContextManager",
     "Empty",
     "find_process_group",
     "create_moodist_backend",

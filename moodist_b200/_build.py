@@ -14,10 +14,15 @@ torch/CUDA version is targeted so a generated ninja file is enough.  ``python mo
 
 from __future__ import annotations
 
+import sys
+
+# Run as a script, this file's directory lands on sys.path and the package's queue.py would shadow the
+# standard library's `queue` for everything imported below.
+sys.path[:] = [p for p in sys.path if not p.rstrip("/").endswith("moodist_b200")]
+
 import os
 import shutil
 import subprocess
-import sys
 import sysconfig
 from pathlib import Path
 

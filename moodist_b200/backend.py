@@ -5,15 +5,12 @@
 from __future__ import annotations
 
 import urllib.parse
-import weakref
 from datetime import timedelta
 
 import torch
 import torch.distributed
 
-from ._core import MoodistProcessGroup, TcpStore
-
-_name_to_group: "weakref.WeakValueDictionary[str, MoodistProcessGroup]" = weakref.WeakValueDictionary()
+from ._core import MoodistProcessGroup, TcpStore, _C
 
 
 class PreferKernelLessContext:
@@ -37,18 +34,13 @@ MoodistProcessGroup.prefer_kernel_less = lambda self, value: PreferKernelLessCon
 
 def find_process_group(name: str):
     """Look a live moodist group up by its name (``group.moodist_name()``); ``None`` if unknown."""
-    return _name_to_group.get(name)
-
-
-def _register(group) -> None:
-    _name_to_group[group.moodist_name()] = group
+    return _C.find_process_group(name)
 
 
 def create_moodist_backend(store: torch.distributed.Store, rank: int, size: int, timeout: timedelta):
-    """Creator handed to ``Backend.register_backend``: builds the group and records it by name."""
-    group = MoodistProcessGroup(store, rank, size)
-    _register(group)
-    return group
+    """Creator handed to ``Backend.register_backend``. Groups register themselves by name natively, so
+    ``find_process_group`` works for as long as the group object is alive anywhere in the process."""
+    return MoodistProcessGroup(store, rank, size)
 
 
 def get_backend(group=None, device: str | torch.device = "cuda"):

@@ -287,8 +287,30 @@ class HostGroupImpl final : public HostGroup {
   // messages
   // ---------------------------------------------------------------------------------------------
   void set_handler(uint32_t op, Handler h) override {
-    std::lock_guard<std::mutex> lk(handlers_mu_);
-    handlers_[op] = std::move(h);
+    {
+      std::lock_guard<std::mutex> lk(handlers_mu_);
+      handlers_[op] = std::move(h);
+    }
+    // messages of this type that arrived before the subsystem registered (a peer may be a step ahead)
+    run_on_engine([this, op] {
+      auto it = unhandled_.find(op);
+      if (it == unhandled_.end()) return;
+      auto list = std::move(it->second);
+      unhandled_.erase(it);
+      Handler h;
+      {
+        std::lock_guard<std::mutex> lk(handlers_mu_);
+        h = handlers_[op];
+      }
+      for (auto& [src, body] : list) {
+        try {
+          Reader r(body);
+          h(src, r);
+        } catch (const std::exception& e) {
+          set_error(strf("bad message from rank %d: %s", src, e.what()));
+        }
+      }
+    });
   }
 
   void send_message(int dst, uint32_t op, Bytes body) override {
@@ -311,6 +333,12 @@ class HostGroupImpl final : public HostGroup {
       queue_.push_back(std::move(fn));
     }
     poller_.wake();
+  }
+
+  bool on_engine_thread() const override { return std::this_thread::get_id() == thread_.get_id(); }
+  void post_read(int src, void* local, size_t bytes, uint32_t rkey, uint64_t raddr,
+                 std::function<void(bool ok)> done) override {
+    transport_.post_read(src, local, bytes, rkey, (uintptr_t)raddr, std::move(done));
   }
 
   bool in_error() const override { return error_state_.load(); }
@@ -607,10 +635,15 @@ class HostGroupImpl final : public HostGroup {
         auto it = handlers_.find(op);
         if (it != handlers_.end()) h = it->second;
       }
-      if (h)
+      if (h) {
         h(src, r);
-      else
-        log_error("engine: no handler for message type %u from rank %d", op, src);
+      } else {
+        auto& list = unhandled_[op];
+        if (list.size() < 65536)
+          list.emplace_back(src, Bytes(r.p, r.end));
+        else
+          log_error("engine: dropping message type %u from rank %d: nobody handles it", op, src);
+      }
     } catch (const std::exception& e) {
       set_error(strf("bad message from rank %d: %s", src, e.what()));
     }
@@ -698,6 +731,7 @@ class HostGroupImpl final : public HostGroup {
   std::map<uint64_t, Announce> announces_;
   std::map<int, uint32_t> next_seq_to_, next_seq_from_;
   std::map<int, std::deque<Mail>> mailbox_;
+  std::map<uint32_t, std::deque<std::pair<int, Bytes>>> unhandled_;
   std::list<PendingRecv> pending_recvs_;
   std::vector<double> last_heard_;
   std::vector<int> peer_shutdown_;

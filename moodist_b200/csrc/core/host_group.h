@@ -85,6 +85,10 @@ class HostGroup {
   virtual void send_message(int dst, uint32_t op, Bytes body) = 0;
   // Post a closure to the engine thread.
   virtual void run_on_engine(std::function<void()> fn) = 0;
+  virtual bool on_engine_thread() const = 0;
+  // One-sided read of a peer's registered memory (engine thread only). Register with MrTable.
+  virtual void post_read(int src, void* local, size_t bytes, uint32_t rkey, uint64_t raddr,
+                         std::function<void(bool ok)> done) = 0;
 
   // ---- health ----
   virtual bool in_error() const = 0;

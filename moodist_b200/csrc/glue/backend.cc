@@ -6,6 +6,7 @@
 #include <torch/csrc/distributed/c10d/Types.hpp>
 #include <torch/csrc/distributed/c10d/NCCLUtils.hpp>
 
+#include <map>
 #include <random>
 
 #include "core/log.h"
@@ -121,6 +122,21 @@ CUstream_st* raw(const c10::cuda::CUDAStream& s) { return reinterpret_cast<CUstr
     TORCH_CHECK(false, e.what());               \
   }
 
+namespace {
+std::mutex g_registry_mu;
+std::map<std::string, MoodistBackend*>& registry() {
+  static auto* m = new std::map<std::string, MoodistBackend*>();
+  return *m;
+}
+}  // namespace
+
+c10::intrusive_ptr<MoodistBackend> MoodistBackend::find(const std::string& name) {
+  std::lock_guard<std::mutex> lk(g_registry_mu);
+  auto it = registry().find(name);
+  if (it == registry().end()) return nullptr;
+  return c10::intrusive_ptr<MoodistBackend>::reclaim_copy(it->second);
+}
+
 MoodistBackend::MoodistBackend(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size)
     : c10d::Backend(rank, size), store_(store), kv_(std::make_unique<C10dStoreAdapter>(store)), rank_(rank),
       size_(size) {
@@ -132,9 +148,16 @@ MoodistBackend::MoodistBackend(const c10::intrusive_ptr<c10d::Store>& store, int
   } else {
     name_ = kv_->get_str("moodist_pg_key");
   }
+  std::lock_guard<std::mutex> lk(g_registry_mu);
+  registry()[name_] = this;
 }
 
 MoodistBackend::~MoodistBackend() {
+  {
+    std::lock_guard<std::mutex> lk(g_registry_mu);
+    auto it = registry().find(name_);
+    if (it != registry().end() && it->second == this) registry().erase(it);
+  }
   try {
     if (host_) host_->shutdown();
   } catch (...) {
@@ -158,6 +181,13 @@ HostGroup& MoodistBackend::hostGroup() {
     MOODIST_TRANSLATE(host_ = HostGroup::create(*kv_, name_, rank_, size_);)
   }
   return *host_;
+}
+
+QueueManager& MoodistBackend::queues() {
+  HostGroup& h = hostGroup();
+  std::lock_guard<std::mutex> lk(mu_);
+  if (!queues_) queues_ = QueueManager::create(h);
+  return *queues_;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -505,7 +535,7 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::barrier(const c10d::BarrierOption
     std::lock_guard<std::mutex> lk(mu_);
     use_cuda = cuda_ != nullptr;
   }
-  if (use_cuda || opts.device.has_value() && opts.device->is_cuda()) {
+  if (use_cuda || (opts.device.has_value() && opts.device->is_cuda())) {
     cudaBarrier();
     return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::BARRIER, std::vector<at::Tensor>{});
   }

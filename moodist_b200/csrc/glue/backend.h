@@ -15,6 +15,7 @@
 #include "core/cuda_group.h"
 #include "core/host_group.h"
 #include "core/kvstore.h"
+#include "core/queue.h"
 
 namespace moodist {
 
@@ -81,6 +82,8 @@ class MoodistBackend final : public c10d::Backend {
 
   // ---- moodist-specific surface (reference: wrapper/module.cc:836-849) ----
   std::string moodistName() const { return name_; }
+  // Live group with that name in this process, or null (groups register themselves on construction).
+  static c10::intrusive_ptr<MoodistBackend> find(const std::string& name);
   void cudaBarrier();
   int64_t getOption(const std::string& name);
   void setOption(const std::string& name, int64_t value);
@@ -95,6 +98,7 @@ class MoodistBackend final : public c10d::Backend {
 
   CudaGroup& cudaGroup(int device);
   HostGroup& hostGroup();
+  QueueManager& queues();
   KVStore& kv() { return *kv_; }
   int rank() const { return rank_; }
   int size() const { return size_; }
@@ -108,6 +112,7 @@ class MoodistBackend final : public c10d::Backend {
   GroupOptions opts_;
   std::unique_ptr<CudaGroup> cuda_;
   std::unique_ptr<HostGroup> host_;
+  std::unique_ptr<QueueManager> queues_;  // declared after host_: destroyed first
 };
 
 }  // namespace moodist

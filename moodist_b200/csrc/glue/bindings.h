@@ -15,9 +15,13 @@ void bind_ops(pybind11::module_& m, BackendClass& backend);
 // store_glue.cc: TcpStore
 void bind_store(pybind11::module_& m);
 
+// queue_glue.cc: Queue, QueueWork, MoodistBackend.Queue
+void bind_queue(pybind11::module_& m, BackendClass& backend);
+
 inline void bind_extras(pybind11::module_& m, BackendClass& backend) {
   bind_ops(m, backend);
   bind_store(m);
+  bind_queue(m, backend);
 }
 
 }  // namespace moodist
