@@ -22,6 +22,7 @@ from ._core import (
 from .backend import find_process_group, create_moodist_backend, get_backend, PreferKernelLessContext
 from .options import MoodistOptions, MoodistOptionsContext, install as _install_options
 from .queue import Queue, TransactionContextManager
+from .compile import compile_op
 
 _install_options(MoodistProcessGroup)
 
@@ -47,4 +48,5 @@ __all__ = [
     "PreferKernelLessContext",
     "MoodistOptions",
     "MoodistOptionsContext",
+    "compile_op",
 ]

@@ -90,6 +90,7 @@ class MoodistBackend final : public c10d::Backend {
   bool getPreferKernelLess() { return getOption("prefer_kernel_less") != 0; }
   void setPreferKernelLess(bool v) { setOption("prefer_kernel_less", v ? 1 : 0); }
   uint64_t kernelLaunches();
+  uint32_t nextCustomOpId() { return ++custom_ops_; }  // compile_op is collective: same ids on every rank
   std::string describe();
 
   // dtype-converting variants used by the sharded-training helpers (fused cast / mixed-precision reduce)
@@ -110,6 +111,7 @@ class MoodistBackend final : public c10d::Backend {
   std::string name_;
   std::mutex mu_;
   GroupOptions opts_;
+  uint32_t custom_ops_ = 0;
   std::unique_ptr<CudaGroup> cuda_;
   std::unique_ptr<HostGroup> host_;
   std::unique_ptr<QueueManager> queues_;  // declared after host_: destroyed first

@@ -18,10 +18,14 @@ void bind_store(pybind11::module_& m);
 // queue_glue.cc: Queue, QueueWork, MoodistBackend.Queue
 void bind_queue(pybind11::module_& m, BackendClass& backend);
 
+// custom_op.cc: compile_op_full, CustomOp, Future
+void bind_custom_op(pybind11::module_& m, BackendClass& backend);
+
 inline void bind_extras(pybind11::module_& m, BackendClass& backend) {
   bind_ops(m, backend);
   bind_store(m);
   bind_queue(m, backend);
+  bind_custom_op(m, backend);
 }
 
 }  // namespace moodist

@@ -1,0 +1,112 @@
+"""compile_op on CPU ranks: the patterns of the reference's tests/test_compile_op.py (p2p, broadcast,
+gather, scatter, all-gather, 2-D shapes, multiple inputs, dtypes, reuse, ranks without inputs/outputs) plus
+strided reshards (row-sharded -> column-sharded [4096, 4096] fp32) checked against a single-process oracle."""
+
+import pytest
+import torch
+
+from moodist_b200.utils.testing import init_moodist, run_ranks
+
+
+def _global(shape, dtype, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    n = 1
+    for s in shape:
+        n *= s
+    if dtype in (torch.int32, torch.int64):
+        return torch.randint(-1000, 1000, shape, generator=g, dtype=dtype)
+    return torch.randn(n, generator=g).view(shape).to(dtype)
+
+
+def _cut(full, box):
+    sl = tuple(slice(o, o + s) for o, s in zip(box["offset"], box["shape"]))
+    return full[sl].contiguous()
+
+
+def _run(moodist, pg, full, inputs, outputs, device="cpu", repeat=1):
+    op = moodist.compile_op(pg, shape=tuple(full.shape), dtype=full.dtype, inputs=inputs, outputs=outputs)
+    for it in range(repeat):
+        src = full + it
+        ins = [_cut(src, b).to(device) for b in (inputs or [])]
+        outs = [torch.full(b["shape"], -7, dtype=full.dtype, device=device) for b in (outputs or [])]
+        op(ins, outs).wait()
+        if device != "cpu":
+            torch.cuda.synchronize()
+        for o, b in zip(outs, outputs or []):
+            assert torch.equal(o.cpu(), _cut(src, b)), (b, it)
+    return op
+
+
+def _patterns(rank, world, port, device):
+    dist = init_moodist(rank, world, port, device=device)
+    import moodist_b200 as moodist
+
+    pg = moodist.get_backend(device=device)
+    dev = "cpu" if device == "cpu" else f"cuda:{rank}"
+    last = world - 1
+    # point to point: rank 0 -> last rank
+    full = _global((64, 16), torch.float32, 1)
+    box = {"offset": [0, 0], "shape": [64, 16]}
+    _run(moodist, pg, full, [box] if rank == 0 else None, [box] if rank == last else None, dev)
+    # broadcast from rank 0
+    _run(moodist, pg, full, [box] if rank == 0 else None, [box], dev)
+    # gather to rank 0 / scatter from rank 0 / all-gather (row shards)
+    rows = 64 // world
+    mine = {"offset": [rank * rows, 0], "shape": [rows, 16]}
+    whole = {"offset": [0, 0], "shape": [rows * world, 16]}
+    _run(moodist, pg, full, [mine], [whole] if rank == 0 else None, dev)
+    _run(moodist, pg, full, [whole] if rank == 0 else None, [mine], dev)
+    _run(moodist, pg, full, [mine], [whole], dev, repeat=3)  # reuse of the compiled op
+    # dtypes
+    for dtype in (torch.float64, torch.float16, torch.bfloat16, torch.int32, torch.int64):
+        f = _global((8 * world, 6), dtype, 2)
+        m = {"offset": [rank * 8, 0], "shape": [8, 6]}
+        _run(moodist, pg, f, [m], [{"offset": [0, 0], "shape": [8 * world, 6]}], dev)
+    # multiple inputs per rank, 3-D shape, outputs that straddle inputs
+    f3 = _global((4 * world, 6, 10), torch.float32, 3)
+    ins = [{"offset": [rank * 4, 0, 0], "shape": [2, 6, 10]}, {"offset": [rank * 4 + 2, 0, 0], "shape": [2, 6, 10]}]
+    outs = [{"offset": [1, 2, 3], "shape": [4 * world - 2, 3, 5]}]
+    _run(moodist, pg, f3, ins, outs, dev)
+    # row-sharded -> column-sharded
+    n = ((4096 if device == "cpu" else 2048) // world) * world
+    fr = _global((n, n), torch.float32, 4)
+    r, c = n // world, n // world
+    _run(moodist, pg, fr, [{"offset": [rank * r, 0], "shape": [r, n]}], [{"offset": [0, rank * c], "shape": [n, c]}], dev)
+    # uncovered output is an error on every rank
+    with pytest.raises(RuntimeError, match="no input covers"):
+        moodist.compile_op(pg, shape=(4, 4), dtype=torch.float32, inputs=[{"offset": [0, 0], "shape": [2, 4]}] if rank == 0 else None,
+                           outputs=[{"offset": [0, 0], "shape": [4, 4]}])
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_compile_op_cpu(world):
+    run_ranks(_patterns, world, "cpu", timeout=240)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_compile_op_cuda_2gpu():
+    run_ranks(_patterns, 2, "cuda", timeout=240, env={"MOODIST_DEVICE_TIMEOUT_MS": 5000})
+
+
+def _planner_body(rank, world, port):
+    dist = init_moodist(rank, world, port)
+    import moodist_b200 as moodist
+
+    pg = moodist.get_backend(device="cpu")
+    op = moodist.compile_op(pg, shape=(8, 8), dtype=torch.float32,
+                            inputs=[{"offset": [rank * 4, 0], "shape": [4, 8]}],
+                            outputs=[{"offset": [0, rank * 4], "shape": [8, 4]}])
+    pieces = sorted(op.pieces())
+    assert len(pieces) == 2
+    for src_rank, src_input, dst_output, rows, row_bytes, src_off, src_pitch, dst_off, dst_pitch in pieces:
+        assert rows == 4 and row_bytes == 16 and src_pitch == 32 and dst_pitch == 16
+        assert src_off == rank * 16 and dst_off == src_rank * 4 * 16
+    dist.destroy_process_group()
+
+
+def test_planner_pieces_are_2d():
+    """Row -> column reshard of a [8, 8] tensor over 2 ranks: one strided piece per source."""
+    run_ranks(_planner_body, 2, timeout=60)
