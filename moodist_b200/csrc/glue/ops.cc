@@ -74,3 +74,100 @@ void bind_ops(pybind11::module_& m, BackendClass& backend) {
 }
 
 }  // namespace moodist
+
+// ------------------------------------------------------------------------------------------------
+// fused collective GEMMs (need a process group)
+// ------------------------------------------------------------------------------------------------
+namespace moodist {
+namespace {
+
+void run_rc(int rc, const char* what) {
+  TORCH_CHECK(rc == MB_OK, "moodist ", what, ": ",
+              rc == MB_ERR_TOO_BIG ? "operands do not fit the staging area (raise MOODIST_STAGING_MB)"
+              : rc == MB_ERR_ARG   ? "unsupported shape (rows must divide by world_size x tile, K and N by 8)"
+                                   : "launch failed",
+              " (code ", rc, ")");
+}
+
+// y = all_gather(x_shard) @ w.T  (gather_weight=false: x_shard [M/world, K], w [N, K])
+// y = x @ all_gather(w_shard).T  (gather_weight=true:  x [M, K], w_shard [N/world, K])
+// Returns (y, gathered): `gathered` is a view of the staging area holding the gathered operand; it stays
+// valid until the collective after next on this group.
+std::tuple<at::Tensor, at::Tensor> ag_gemm(c10::intrusive_ptr<MoodistBackend> pg, const at::Tensor& shard,
+                                           const at::Tensor& other, bool gather_weight, bool out_fp32, int64_t epilogue,
+                                           int64_t comm_ctas) {
+  TORCH_CHECK(shard.is_cuda() && other.is_cuda() && shard.scalar_type() == at::kBFloat16 &&
+                  other.scalar_type() == at::kBFloat16 && shard.dim() == 2 && other.dim() == 2,
+              "moodist ag_gemm: 2-D bf16 CUDA tensors");
+  TORCH_CHECK(shard.is_contiguous() && other.stride(1) == 1, "moodist ag_gemm: shard contiguous, other row-contiguous");
+  const int world = pg->size();
+  const int64_t K = shard.size(1);
+  TORCH_CHECK(other.size(1) == K, "moodist ag_gemm: inner dimensions differ");
+  const int64_t M = gather_weight ? other.size(0) : shard.size(0) * world;
+  const int64_t N = gather_weight ? shard.size(0) * world : other.size(0);
+  c10::cuda::CUDAGuard guard(shard.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  at::Tensor y = at::empty({M, N}, shard.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+  CudaGroup& g = pg->cudaGroup(shard.get_device());
+  const mb_comm_t* comm = static_cast<const mb_comm_t*>(g.comm_struct());
+  CUstream_st* raw = reinterpret_cast<CUstream_st*>(stream.stream());
+  at::Tensor gathered;
+  if (world == 1) {
+    int rc = mb_gemm_bf16(gather_weight ? other.data_ptr() : shard.data_ptr(), gather_weight ? shard.data_ptr() : other.data_ptr(),
+                          y.data_ptr(), (int)M, (int)N, (int)K, gather_weight ? other.stride(0) : K,
+                          gather_weight ? K : other.stride(0), N, 0, 0, out_fp32, (int)epilogue, comm->status, 0, raw);
+    run_rc(rc, "ag_gemm");
+    return {y, shard};
+  }
+  uint32_t seq = g.next_seq(raw);
+  int rc = mb_ag_gemm(comm, seq, shard.data_ptr(), other.data_ptr(), y.data_ptr(), (int)M, (int)N, (int)K, other.stride(0),
+                      N, gather_weight ? 1 : 0, 0, out_fp32, (int)epilogue, (int)comm_ctas, raw);
+  g.finish_op(raw);
+  run_rc(rc, "ag_gemm");
+  const int64_t rows = gather_weight ? N : M;
+  gathered = at::from_blob(mb_stage_pointer(comm, seq), {rows, K}, shard.options());
+  return {y, gathered};
+}
+
+// out[M/world, N] = reduce_scatter over rows of (a @ b.T), fp32 accumulation across ranks.
+at::Tensor gemm_rs(c10::intrusive_ptr<MoodistBackend> pg, const at::Tensor& a, const at::Tensor& b, bool trans_b,
+                   bool out_fp32, double scale) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 &&
+                  a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1,
+              "moodist gemm_rs: 2-D row-contiguous bf16 CUDA tensors");
+  const int world = pg->size();
+  const int64_t M = a.size(0), K = a.size(1);
+  const int64_t N = trans_b ? b.size(1) : b.size(0);
+  TORCH_CHECK((trans_b ? b.size(0) : b.size(1)) == K, "moodist gemm_rs: inner dimensions differ");
+  c10::cuda::CUDAGuard guard(a.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  CUstream_st* raw = reinterpret_cast<CUstream_st*>(stream.stream());
+  CudaGroup& g = pg->cudaGroup(a.get_device());
+  const mb_comm_t* comm = static_cast<const mb_comm_t*>(g.comm_struct());
+  at::Tensor out = at::empty({M / world, N}, a.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+  if (world == 1) {
+    TORCH_CHECK(scale == 1.0, "moodist gemm_rs: scale needs more than one rank");
+    int rc = mb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0), N, 0,
+                          trans_b, out_fp32, 0, comm->status, 0, raw);
+    run_rc(rc, "gemm_rs");
+    return out;
+  }
+  uint32_t seq = g.next_seq(raw);
+  int rc = mb_gemm_rs(comm, seq, a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
+                      N, trans_b, out_fp32, (float)scale, scale != 1.0, raw);
+  g.finish_op(raw);
+  run_rc(rc, "gemm_rs");
+  return out;
+}
+
+}  // namespace
+
+void bind_fused(pybind11::module_& m) {
+  m.def("ag_gemm", &ag_gemm, pybind11::arg("group"), pybind11::arg("shard"), pybind11::arg("other"),
+        pybind11::arg("gather_weight") = false, pybind11::arg("out_fp32") = false, pybind11::arg("epilogue") = 0,
+        pybind11::arg("comm_ctas") = 0);
+  m.def("gemm_rs", &gemm_rs, pybind11::arg("group"), pybind11::arg("a"), pybind11::arg("b"),
+        pybind11::arg("trans_b") = false, pybind11::arg("out_fp32") = false, pybind11::arg("scale") = 1.0);
+}
+
+}  // namespace moodist

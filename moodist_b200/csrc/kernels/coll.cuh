@@ -27,8 +27,9 @@ constexpr int F_LOCAL = 96;    // [8]     local-grid counters (own page only)
 constexpr int F_TABLE = 128;   // [8][4]  all-to-all: {src_off_lo, src_off_hi, bytes_lo, bytes_hi}
 constexpr int F_READY = 256;   // [8][kMaxCtas]
 constexpr int F_READY2 = F_READY + MB_MAX_RANKS * kMaxCtas;  // second bank (two-phase ops)
-constexpr int F_CHUNK = F_READY2 + MB_MAX_RANKS * kMaxCtas;  // fused ops: per-shard arrival words
-static_assert(F_CHUNK + 256 <= MB_FLAG_WORDS, "flag page too small");
+constexpr int F_CHUNK = F_READY2 + MB_MAX_RANKS * kMaxCtas;  // AG->GEMM: [8][32] arrival words (value = seq)
+constexpr int F_RSCNT = F_CHUNK + 256;                       // GEMM->RS: [2 banks][128] arrival counters
+static_assert(F_RSCNT + 256 <= MB_FLAG_WORDS, "flag page too small");
 
 enum Status : uint32_t {
   kTimeoutEntry = 0x201,

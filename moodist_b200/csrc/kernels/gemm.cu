@@ -30,7 +30,7 @@ static EncodeFn get_encode() {
 // cuTensorMapEncodeTiled is a raw driver call and needs a current context. A thread that has only ever
 // used another CUDA runtime instance (torch's autograd workers) may not have bound one for this runtime
 // yet; any runtime call that initialises the device does it.
-static void ensure_context() {
+void ensure_context() {
   static thread_local bool bound = false;
   if (!bound) {
     cudaFree(nullptr);

@@ -62,23 +62,29 @@ struct Params {
   int epilogue;
   uint32_t* status;  // device word, 0 = ok
   uint64_t wait_ns;  // cap for every wait inside the kernel
-  int num_gemm_ctas; // CTAs [0, num_gemm_ctas) run the GEMM; the rest are owned by the fused wrapper
+  int num_gemm_ctas; // how many CTAs of the grid run the GEMM
+  int cta_base;      // they are CTAs [cta_base, cta_base + num_gemm_ctas); lower ones belong to the fused wrapper
 
   // ---- AG->GEMM: arrival flags for the gathered operand ----
-  const uint32_t* ready;  // [num_shards], in local memory
-  uint32_t epoch;         // value that marks "shard landed" for this launch
-  int shard_rows;         // rows of the gathered operand per shard (multiple of the tile extent)
+  const uint32_t* ready;  // flag words in local memory, one per (shard, sub-chunk)
+  uint32_t epoch;         // a flag >= epoch means that sub-chunk has landed for this launch
+  int shard_rows;         // rows of the gathered operand per rank (multiple of the tile extent)
+  int sub_rows;           // rows per arrival flag (multiple of the tile extent)
+  int subs_per_shard;
   int gather_on_b;        // 0: A rows (M) are gathered, 1: B rows (N) are gathered
-  int first_shard;        // tile walk starts at this rank's own shard
+  int first_shard;        // this rank: its shard is consumed first, then rank-1, rank-2, ... (arrival order)
+  int num_shards;
 
-  // ---- GEMM->RS: per-destination output ----
-  void* const* scatter_dst;      // [num_shards] base of this rank's slot in each owner's staging buffer
-  uint32_t* const* scatter_cnt;  // [num_shards] arrival counter on each owner
-  int scatter_rows;              // output rows per owner shard (multiple of BM)
+  // ---- GEMM->RS: per-owner output ----
+  void* scatter_dst[8];      // this rank's slot in each owner's staging buffer ([scatter_rows, ldc])
+  uint32_t* scatter_cnt[8];  // arrival counters of each owner, one word per 128-row block of its shard
+  int scatter_rows;          // output rows per owner (multiple of BM)
 };
 
+// The status word may be host-mapped memory, so no atomics: first writer (nearly) wins.
 __device__ __forceinline__ void report(const Params& p, uint32_t code) {
-  if (p.status) atomicCAS(p.status, 0u, code);
+  volatile uint32_t* s = p.status;
+  if (s && *s == 0) *s = code;
 }
 
 // tile index -> (m, n) with a grouped raster so concurrently running CTAs share A and B panels in L2
@@ -90,6 +96,42 @@ __device__ __forceinline__ void tile_coords(const Params& p, int t, int& tm, int
   int r = t - g * per_group;
   tm = first_m + r % gsz;
   tn = r / gsz;
+}
+
+// Walk order of the fused variants.
+//  gather : all tiles of one shard of the gathered operand are consecutive; shards are visited own first,
+//           then in the order their pushes arrive (rank-1, rank-2, ...). flag = arrival word to wait on.
+//  scatter: tiles owned by other ranks first (rank+1, rank+2, ...), this rank's own rows last, so remote
+//           partial sums are on the wire while the local ones are still being computed.
+template <bool kGatherWait, bool kScatterOut>
+__device__ __forceinline__ void tile_map(const Params& p, int t, int& tm, int& tn, int& flag) {
+  flag = 0;
+  if constexpr (kGatherWait) {
+    const int ext = p.gather_on_b ? BN : BM;
+    const int other = p.gather_on_b ? p.tiles_m : p.tiles_n;
+    const int blocks = p.shard_rows / ext;
+    const int per_shard = blocks * other;
+    const int si = t / per_shard, within = t - si * per_shard;
+    const int shard = (p.first_shard - si + 2 * p.num_shards) % p.num_shards;
+    const int blk = within / other, o = within - blk * other;
+    if (p.gather_on_b) {
+      tn = shard * blocks + blk;
+      tm = o;
+    } else {
+      tm = shard * blocks + blk;
+      tn = o;
+    }
+    flag = shard * p.subs_per_shard + (blk * ext) / p.sub_rows;
+  } else if constexpr (kScatterOut) {
+    const int blocks = p.scatter_rows / BM;
+    const int per_shard = blocks * p.tiles_n;
+    const int si = t / per_shard, within = t - si * per_shard;
+    const int shard = (p.first_shard + 1 + si) % p.num_shards;
+    tm = shard * blocks + within / p.tiles_n;
+    tn = within % p.tiles_n;
+  } else {
+    tile_coords(p, t, tm, tn);
+  }
 }
 
 template <bool kAMn, bool kBMn, typename OutT, bool kGatherWait, bool kScatterOut>
@@ -111,7 +153,7 @@ __device__ __forceinline__ void gemm_body(const Params& p, const CUtensorMap* tm
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int kblocks = (p.K + BK - 1) / BK;
-  const int cta = blockIdx.x;
+  const int cta = blockIdx.x - p.cta_base;
   const int stride = p.num_gemm_ctas;
 
   if (threadIdx.x == 0) {
@@ -144,32 +186,15 @@ __device__ __forceinline__ void gemm_body(const Params& p, const CUtensorMap* tm
       uint32_t it = 0;  // k-blocks issued so far
       bool ok = true;
       for (int t = cta; t < num_tiles && ok; t += stride) {
-        int tm, tn;
-        int tt = t;
+        int tm, tn, flag;
+        tile_map<kGatherWait, kScatterOut>(p, t, tm, tn, flag);
         if constexpr (kGatherWait) {
-          // rotate the walk so tiles of this rank's own shard come first
-          int tiles_per_shard = (p.gather_on_b ? p.tiles_m : p.tiles_n) * (p.shard_rows / (p.gather_on_b ? BN : BM));
-          tt = (t + p.first_shard * tiles_per_shard) % num_tiles;
-        }
-        if constexpr (kGatherWait) {
-          // shard-major walk: all tiles of one shard of the gathered operand are consecutive
-          if (p.gather_on_b) {
-            tn = tt / p.tiles_m;
-            tm = tt % p.tiles_m;
-          } else {
-            tm = tt / p.tiles_n;
-            tn = tt % p.tiles_n;
-          }
-          int row0 = p.gather_on_b ? tn * BN : tm * BM;
-          int shard = row0 / p.shard_rows;
-          if (!wait_geq_gpu(p.ready + shard, p.epoch, p.wait_ns)) {
+          if (!wait_geq_sys(p.ready + flag, p.epoch, p.wait_ns)) {  // written by peers: system scope
             report(p, kTimeoutGather);
             ok = false;
             break;
           }
-          fence_proxy_async_all();
-        } else {
-          tile_coords(p, tt, tm, tn);
+          fence_proxy_async_all();  // the landed rows were written by ordinary stores; TMA reads them next
         }
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           int s = it % kStages;
@@ -254,21 +279,8 @@ __device__ __forceinline__ void gemm_body(const Params& p, const CUtensorMap* tm
     uint32_t local_tile = 0;
     bool ok = true;
     for (int t = cta; t < num_tiles && ok; t += stride, ++local_tile) {
-      int tm, tn;
-      int tt = t;
-      if constexpr (kGatherWait) {
-        int tiles_per_shard = (p.gather_on_b ? p.tiles_m : p.tiles_n) * (p.shard_rows / (p.gather_on_b ? BN : BM));
-        tt = (t + p.first_shard * tiles_per_shard) % num_tiles;
-        if (p.gather_on_b) {
-          tn = tt / p.tiles_m;
-          tm = tt % p.tiles_m;
-        } else {
-          tm = tt / p.tiles_n;
-          tn = tt % p.tiles_n;
-        }
-      } else {
-        tile_coords(p, tt, tm, tn);
-      }
+      int tm, tn, flag;
+      tile_map<kGatherWait, kScatterOut>(p, t, tm, tn, flag);
       uint32_t acc = local_tile & 1;
       uint32_t acc_ph = (local_tile >> 1) & 1;
       if (!mbar_wait(&acc_full[acc], acc_ph, p.wait_ns)) {
@@ -280,9 +292,8 @@ __device__ __forceinline__ void gemm_body(const Params& p, const CUtensorMap* tm
       const int row = tm * BM + q * 32 + lane;
       OutT* crow;
       if constexpr (kScatterOut) {
-        int owner = row / p.scatter_rows;
-        int owner_c = min(owner, (p.M - 1) / p.scatter_rows);
-        crow = reinterpret_cast<OutT*>(p.scatter_dst[owner_c]) + (int64_t)(row - owner_c * p.scatter_rows) * p.ldc;
+        const int owner = (tm * BM) / p.scatter_rows;  // M is a multiple of scatter_rows * num_shards here
+        crow = reinterpret_cast<OutT*>(p.scatter_dst[owner]) + (int64_t)(row - owner * p.scatter_rows) * p.ldc;
       } else {
         crow = reinterpret_cast<OutT*>(p.C) + (int64_t)row * p.ldc;
       }
@@ -329,12 +340,14 @@ __device__ __forceinline__ void gemm_body(const Params& p, const CUtensorMap* tm
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
       if constexpr (kScatterOut) {
-        // all four epilogue warps have pushed their rows of this tile: publish it to the owner
+        // this warp's 32 rows of the tile are on their way: one arrival per warp on the owner's counter
+        // of that 128-row block (the owner waits for 4 x tiles_n x ranks arrivals)
         __threadfence_system();
         __syncwarp();
         if (lane == 0) {
-          int owner = min((tm * BM) / p.scatter_rows, (p.M - 1) / p.scatter_rows);
-          red_add_release_sys(p.scatter_cnt[owner], 1u);
+          const int owner = (tm * BM) / p.scatter_rows;
+          const int blk = tm - owner * (p.scatter_rows / BM);
+          red_add_release_sys(p.scatter_cnt[owner] + blk, 1u);
         }
       }
     }

@@ -122,6 +122,19 @@ typedef struct {
 int mb_gather_scatter(const mb_comm_t* c, uint32_t seq, const mb_stage_copy_t* stage_in, int num_stage,
                       const mb_piece_t* pieces, int num_pieces, size_t max_bytes, void* stream);
 
+// --- fused collective GEMMs (fused_gemm.cu) -------------------------------------------------------
+// C = gather(A shards) · B^T (gather_on_b 0) or C = A · gather(B shards)^T (gather_on_b 1); `shard` is this
+// rank's [rows/world, K] bf16 slice, `other` the local operand. comm_ctas: copy CTAs (0 = default).
+int mb_ag_gemm(const mb_comm_t* c, uint32_t seq, const void* shard, const void* other, void* C, int M, int N, int K,
+               int64_t ld_other, int64_t ldc, int gather_on_b, int other_mn_major, int out_fp32, int epilogue,
+               int comm_ctas, void* stream);
+// Where collective `seq` staged this rank's data (the gathered operand after mb_ag_gemm).
+void* mb_stage_pointer(const mb_comm_t* c, uint32_t seq);
+// out[M/world, N] = scale * sum_r (A_r · B_r^T)[rows of this rank]; bf16 partials cross NVLink, fp32 sum.
+int mb_gemm_rs(const mb_comm_t* c, uint32_t seq, const void* A, const void* B, void* out, int M, int N, int K,
+               int64_t lda, int64_t ldb, int64_t ldo, int b_mn_major, int out_fp32, float scale, int use_scale,
+               void* stream);
+
 // local cast / scale copy (also the world == 1 path of the collectives)
 int mb_copy_cast(const void* in, void* out, size_t count, int in_dtype, int out_dtype, float scale, int use_scale,
                  void* stream);
