@@ -32,6 +32,8 @@ def parse_args():
     ap.add_argument("--impl", default="moodist_b200", choices=["moodist_b200", "reference"])
     ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "tiny"])
     ap.add_argument("--seq-len", type=int, default=8192)
+    ap.add_argument("--backend", default="moodist", choices=["moodist", "nccl"],
+                    help="process-group backend under FSDP2 (nccl = the baseline this library is compared with)")
     return ap.parse_args()
 
 
@@ -63,8 +65,13 @@ def main():
     os.environ.setdefault("MASTER_PORT", "29533")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    dist.init_process_group("moodist", rank=rank, world_size=world)
-    backend = moodist_b200.get_backend()
+    dist.init_process_group(args.backend, rank=rank, world_size=world, device_id=dev if args.backend == "nccl" else None)
+
+    class _NoBackend:
+        def kernel_launches(self):
+            return 0
+
+    backend = moodist_b200.get_backend() if args.backend == "moodist" else _NoBackend()
 
     cfg = LlamaConfig.llama3_8b() if args.model == "llama3-8b" else LlamaConfig.tiny()
     seq = min(args.seq_len, cfg.max_seq_len)
@@ -131,8 +138,9 @@ def main():
             "vs_baseline": None,
             "dtype": "bf16",
             "data": "synthetic token ids uniform in [0, vocab), random-init weights",
-            "impl": "moodist_b200",
+            "impl": "moodist_b200" if args.backend == "moodist" else "moodist_b200 model over the NCCL backend",
             "config": {
+                "backend": args.backend,
                 "model": "llama3-8b" if args.model == "llama3-8b" else "tiny",
                 "params": cfg.num_params(),
                 "global_batch": world,

@@ -12,13 +12,17 @@ from ._core import (
     TcpStore,
     serialize,
     deserialize,
-    enable_profiling,
-    enable_cuda_allocator,
-    enable_cpu_allocator,
-    cpu_allocator_debug,
     cuda_copy,
     set_prefer_kernel_less,
 )
+from .allocator import (
+    enable_cuda_allocator,
+    enable_cpu_allocator,
+    cpu_allocator_debug,
+    cuda_allocator_stats,
+    symmetric_pool,
+)
+from .utils.trace import enable_profiling
 from .backend import find_process_group, create_moodist_backend, get_backend, PreferKernelLessContext
 from .options import MoodistOptions, MoodistOptionsContext, install as _install_options
 from .queue import Queue, TransactionContextManager
@@ -49,4 +53,6 @@ __all__ = [
     "MoodistOptions",
     "MoodistOptionsContext",
     "compile_op",
+    "symmetric_pool",
+    "cuda_allocator_stats",
 ]

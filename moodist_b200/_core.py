@@ -31,12 +31,8 @@ _C = _load("_C")
 MoodistProcessGroup = _C.MoodistProcessGroup
 MoodistBackend = _C.MoodistBackend
 TcpStore = getattr(_C, "TcpStore", None)
-enable_profiling = getattr(_C, "enable_profiling", None)
-enable_cuda_allocator = getattr(_C, "enable_cuda_allocator", None)
-enable_cpu_allocator = getattr(_C, "enable_cpu_allocator", None)
-cpu_allocator_debug = getattr(_C, "cpu_allocator_debug", None)
-cuda_copy = getattr(_C, "cuda_copy", None)
-set_prefer_kernel_less = getattr(_C, "set_prefer_kernel_less", None)
+cuda_copy = _C.cuda_copy
+set_prefer_kernel_less = _C.set_prefer_kernel_less
 
 _serialize = _load("_serialize")
 

@@ -59,6 +59,11 @@ class CudaGroupImpl final : public CudaGroup {
     comm_.world = world;
     comm_.wait_ns = (uint64_t)env_long("MOODIST_DEVICE_TIMEOUT_MS", 30000) * 1000000ull;
     comm_.max_ctas = (int)env_long("MOODIST_MAX_CTAS", 0);
+    push_bytes_ = (size_t)env_long("MOODIST_AG_PUSH_BYTES", 1 << 20);
+    // smallest message (bytes) for which the NVLS variant is picked automatically; -1 = never
+    nvls_ar_min_ = env_long("MOODIST_NVLS_AR_MIN_BYTES", 512 << 10);
+    nvls_rs_min_ = env_long("MOODIST_NVLS_RS_MIN_BYTES", -1);
+    nvls_ag_min_ = env_long("MOODIST_NVLS_AG_MIN_BYTES", -1);
     RT_CHECK(cudaHostAlloc((void**)&status_host_, 64, cudaHostAllocMapped));
     memset((void*)status_host_, 0, 64);
     void* dptr = nullptr;
@@ -100,14 +105,19 @@ class CudaGroupImpl final : public CudaGroup {
   const void* comm_struct() const override { return &comm_; }
   uint64_t launches() const override { return launches_; }
 
+  // Ordering between collectives costs nothing while the caller stays on one stream: only when the
+  // stream changes is an event recorded at the tail of the previous stream and waited on by the new one.
   uint32_t next_seq(CUstream_st* s) override {
     check_status();
-    if (recorded_) RT_CHECK(cudaStreamWaitEvent(s, order_, 0));
+    if (have_last_ && last_stream_ != s) {
+      RT_CHECK(cudaEventRecord(order_, last_stream_));
+      RT_CHECK(cudaStreamWaitEvent(s, order_, 0));
+    }
     return ++seq_;
   }
   void finish_op(CUstream_st* s) override {
-    RT_CHECK(cudaEventRecord(order_, s));
-    recorded_ = true;
+    last_stream_ = s;
+    have_last_ = true;
     ++launches_;
   }
 
@@ -136,6 +146,13 @@ class CudaGroupImpl final : public CudaGroup {
     return heap_->offset_of(p, bytes);
   }
 
+  // method option: 0 forces the P2P kernels, 1 the NVLS kernels; otherwise the size threshold decides
+  bool want_nvls(long min_bytes, size_t bytes) const {
+    if (!mb_nvls_available(&comm_) || opts_.method == 0) return false;
+    if (opts_.method == 1) return true;
+    return min_bytes >= 0 && bytes >= (size_t)min_bytes;
+  }
+
   void run(int rc, const char* what) {
     if (rc != MB_OK) fail(strf("moodist: %s: %s", what, rc_name(rc)));
   }
@@ -146,13 +163,21 @@ class CudaGroupImpl final : public CudaGroup {
     if (!osz || !isz) fail("moodist: all_gather: unsupported dtype");
     if (count == 0) return;
     int64_t off = idt == odt ? heap_off(in, count * isz) : -1;
+    if (idt == odt && off < 0 && world_ > 1 && want_nvls(nvls_ag_min_, count * isz) &&
+        (size_t)world_ * count * isz <= comm_.staging_bytes / 2) {
+      uint32_t seq = next_seq(s);
+      run(mb_all_gather_nvls(&comm_, seq, in, out, count * isz, count * isz, s), "all_gather (NVLS)");
+      finish_op(s);
+      return;
+    }
+    if (off < 0 && count * osz <= push_bytes_) off = -2;  // small shard: push it
     size_t half = comm_.staging_bytes / 2;
     size_t piece = count;
     if (world_ > 1 && off < 0 && count * osz > half) piece = (half / osz) & ~(size_t)63;
     for (size_t done = 0; done < count; done += piece) {
       size_t n = std::min(piece, count - done);
       uint32_t seq = next_seq(s);
-      run(mb_all_gather(&comm_, seq, (const uint8_t*)in + done * isz, off < 0 ? -1 : off + (int64_t)(done * isz),
+      run(mb_all_gather(&comm_, seq, (const uint8_t*)in + done * isz, off < 0 ? off : off + (int64_t)(done * isz),
                         (uint8_t*)out + done * osz, n, count, idt, odt, s),
           "all_gather");
       finish_op(s);
@@ -168,6 +193,15 @@ class CudaGroupImpl final : public CudaGroup {
     int64_t off = heap_off(in, count * isz * world_);
     size_t half = comm_.staging_bytes / 2;
     size_t piece = count;
+    if (world_ > 1 && off < 0 && want_nvls(nvls_rs_min_, count * isz) && (size_t)world_ * count * isz <= half &&
+        (idt == MB_F32 || idt == MB_BF16) && (odt == MB_F32 || odt == MB_BF16) &&
+        (op == MB_SUM || op == MB_AVG || op == MB_PREMUL_SUM) && (count * isz) % 16 == 0 &&
+        (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+      uint32_t seq = next_seq(s);
+      run(mb_reduce_scatter_nvls(&comm_, seq, in, out, count, count, idt, odt, op, premul, s), "reduce_scatter (NVLS)");
+      finish_op(s);
+      return;
+    }
     if (world_ > 1 && off < 0 && count * isz * world_ > half) piece = (half / (isz * world_)) & ~(size_t)63;
     for (size_t done = 0; done < count; done += piece) {
       size_t n = std::min(piece, count - done);
@@ -193,11 +227,17 @@ class CudaGroupImpl final : public CudaGroup {
     for (size_t done = 0; done < count; done += piece) {
       size_t n = std::min(piece, count - done);
       int variant = (n * sz <= oneshot_max) ? 0 : 1;
-      if (opts_.method == 0 || opts_.method == 1) variant = opts_.method;
+      bool nvls = world_ > 1 && want_nvls(nvls_ar_min_, n * sz) && (dt == MB_F32 || dt == MB_BF16) &&
+                  (op == MB_SUM || op == MB_AVG || op == MB_PREMUL_SUM) &&
+                  ((((uintptr_t)in + done * sz) | ((uintptr_t)out + done * sz)) & 15) == 0;
       uint32_t seq = next_seq(s);
-      run(mb_all_reduce(&comm_, seq, (const uint8_t*)in + done * sz, (uint8_t*)out + done * sz, n, dt, op, premul,
-                        variant, s),
-          "all_reduce");
+      if (nvls)
+        run(mb_all_reduce_nvls(&comm_, seq, (const uint8_t*)in + done * sz, (uint8_t*)out + done * sz, n, dt, op, premul, s),
+            "all_reduce (NVLS)");
+      else
+        run(mb_all_reduce(&comm_, seq, (const uint8_t*)in + done * sz, (uint8_t*)out + done * sz, n, dt, op, premul,
+                          variant, s),
+            "all_reduce");
       finish_op(s);
     }
   }
@@ -256,8 +296,11 @@ class CudaGroupImpl final : public CudaGroup {
   bool attached_ = false;
   volatile uint32_t* status_host_ = nullptr;
   cudaEvent_t order_ = nullptr;
-  bool recorded_ = false;
+  CUstream_st* last_stream_ = nullptr;
+  bool have_last_ = false;
   uint32_t seq_ = 0;
+  size_t push_bytes_ = 0;
+  long nvls_ar_min_ = -1, nvls_rs_min_ = -1, nvls_ag_min_ = -1;
   uint64_t launches_ = 0;
   void* scratch_ = nullptr;
   size_t scratch_bytes_ = 0;

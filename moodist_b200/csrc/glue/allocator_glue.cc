@@ -1,0 +1,87 @@
+// enable_cpu_allocator / cpu_allocator_debug / cuda_copy / enable_profiling / set_prefer_kernel_less.
+// The CUDA allocator is installed from Python through torch's pluggable-allocator API with the
+// mb_cuda_alloc / mb_cuda_free hooks of the core library (moodist_b200/allocator.py); the reference
+// subclasses CUDACachingAllocator::CUDAAllocator instead (wrapper/allocator_wrapper.cc:14-199), an interface
+// that changes between torch releases.
+#include <c10/core/Allocator.h>
+#include <c10/core/CPUAllocator.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <cuda_runtime_api.h>
+#include <torch/extension.h>
+
+#include <mutex>
+#include <set>
+
+#include "bindings.h"
+#include "core/cpu_allocator.h"
+#include "core/log.h"
+
+namespace moodist {
+namespace {
+
+void delete_cpu(void* p) { cpu_free(p); }
+
+struct MoodistCpuAllocator final : c10::Allocator {
+  c10::DataPtr allocate(size_t n) override {
+    void* p = n ? cpu_alloc(n) : nullptr;
+    TORCH_CHECK(n == 0 || p, "moodist CPU allocator: out of memory allocating ", n, " bytes");
+    return {p, p, &delete_cpu, c10::Device(c10::kCPU)};
+  }
+  c10::DeleterFnPtr raw_deleter() const override { return &delete_cpu; }
+  void copy_data(void* dest, const void* src, std::size_t count) const override { default_copy_data(dest, src, count); }
+};
+
+MoodistCpuAllocator g_cpu_allocator;
+bool g_cpu_enabled = false;
+
+void enable_cpu_allocator() {
+  if (g_cpu_enabled) return;
+  c10::SetAllocator(c10::kCPU, &g_cpu_allocator, /*priority=*/10);
+  g_cpu_enabled = true;
+}
+
+// dst.copy_(src) between host and device where the host side may be pageable memory of the CPU allocator:
+// its whole region is pinned once (cudaHostRegister) so the copy is truly asynchronous
+// (reference: core/cuda_copy.h:14-41).
+void cuda_copy(at::Tensor dst, const at::Tensor& src) {
+  TORCH_CHECK(dst.is_contiguous() && src.is_contiguous() && dst.nbytes() == src.nbytes(),
+              "moodist.cuda_copy: contiguous tensors of equal byte size");
+  const at::Tensor& host = dst.is_cuda() ? src : dst;
+  const at::Tensor& devt = dst.is_cuda() ? dst : src;
+  TORCH_CHECK(devt.is_cuda() && !host.is_cuda(), "moodist.cuda_copy: one CUDA and one CPU tensor");
+  c10::cuda::CUDAGuard guard(devt.device());
+  void* base = nullptr;
+  size_t size = 0;
+  static std::mutex mu;
+  static std::set<void*> registered;
+  if (cpu_allocator_region(host.data_ptr(), &base, &size)) {
+    std::lock_guard<std::mutex> lk(mu);
+    if (!registered.count(base)) {
+      if (cudaHostRegister(base, size, cudaHostRegisterDefault) == cudaSuccess) registered.insert(base);
+      cudaGetLastError();
+    }
+  }
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  TORCH_CHECK(cudaMemcpyAsync(dst.data_ptr(), src.data_ptr(), dst.nbytes(),
+                              dst.is_cuda() ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, stream.stream()) == cudaSuccess,
+              "moodist.cuda_copy: cudaMemcpyAsync failed");
+}
+
+}  // namespace
+
+void bind_allocators(pybind11::module_& m, BackendClass& backend) {
+  m.def("enable_cpu_allocator", &enable_cpu_allocator);
+  m.def("cpu_allocator_debug", [] { return cpu_allocator_debug(); });
+  m.def("cpu_allocator_owns", [](const at::Tensor& t) { return cpu_allocator_owns(t.data_ptr()); });
+  m.def("cuda_copy", &cuda_copy, pybind11::arg("dst"), pybind11::arg("src"));
+  // profiling is per group in the engine; the module-level switch applies to every live group
+  backend.def("enable_profiling", [](c10::intrusive_ptr<MoodistBackend> self, bool on) {
+    pybind11::gil_scoped_release nogil;
+    self->hostGroup().set_profiling(on);
+    return self->hostGroup().last_trace_path();
+  });
+  m.def("set_prefer_kernel_less", [](bool v) { MoodistBackend::setDefaultPreferKernelLess(v); });
+}
+
+}  // namespace moodist

@@ -6,6 +6,7 @@
 #include <torch/csrc/distributed/c10d/Types.hpp>
 #include <torch/csrc/distributed/c10d/NCCLUtils.hpp>
 
+#include <atomic>
 #include <map>
 #include <random>
 
@@ -130,6 +131,9 @@ std::map<std::string, MoodistBackend*>& registry() {
 }
 }  // namespace
 
+static std::atomic<int> g_default_prefer_kernel_less{0};
+void MoodistBackend::setDefaultPreferKernelLess(bool v) { g_default_prefer_kernel_less = v ? 1 : 0; }
+
 c10::intrusive_ptr<MoodistBackend> MoodistBackend::find(const std::string& name) {
   std::lock_guard<std::mutex> lk(g_registry_mu);
   auto it = registry().find(name);
@@ -148,8 +152,16 @@ MoodistBackend::MoodistBackend(const c10::intrusive_ptr<c10d::Store>& store, int
   } else {
     name_ = kv_->get_str("moodist_pg_key");
   }
+  opts_.prefer_kernel_less = g_default_prefer_kernel_less.load();
   std::lock_guard<std::mutex> lk(g_registry_mu);
   registry()[name_] = this;
+}
+
+std::vector<c10::intrusive_ptr<MoodistBackend>> MoodistBackend::live() {
+  std::lock_guard<std::mutex> lk(g_registry_mu);
+  std::vector<c10::intrusive_ptr<MoodistBackend>> out;
+  for (auto& [name, p] : registry()) out.push_back(c10::intrusive_ptr<MoodistBackend>::reclaim_copy(p));
+  return out;
 }
 
 MoodistBackend::~MoodistBackend() {

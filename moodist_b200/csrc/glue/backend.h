@@ -84,6 +84,9 @@ class MoodistBackend final : public c10d::Backend {
   std::string moodistName() const { return name_; }
   // Live group with that name in this process, or null (groups register themselves on construction).
   static c10::intrusive_ptr<MoodistBackend> find(const std::string& name);
+  // Default of the prefer_kernel_less option for groups created afterwards (moodist.set_prefer_kernel_less).
+  static void setDefaultPreferKernelLess(bool v);
+  static std::vector<c10::intrusive_ptr<MoodistBackend>> live();
   void cudaBarrier();
   int64_t getOption(const std::string& name);
   void setOption(const std::string& name, int64_t value);

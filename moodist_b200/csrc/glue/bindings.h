@@ -22,12 +22,16 @@ void bind_queue(pybind11::module_& m, BackendClass& backend);
 // custom_op.cc: compile_op_full, CustomOp, Future
 void bind_custom_op(pybind11::module_& m, BackendClass& backend);
 
+// allocator_glue.cc: CPU allocator, cuda_copy, profiling switch
+void bind_allocators(pybind11::module_& m, BackendClass& backend);
+
 inline void bind_extras(pybind11::module_& m, BackendClass& backend) {
   bind_ops(m, backend);
   bind_fused(m);
   bind_store(m);
   bind_queue(m, backend);
   bind_custom_op(m, backend);
+  bind_allocators(m, backend);
 }
 
 }  // namespace moodist

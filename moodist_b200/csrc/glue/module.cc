@@ -38,6 +38,7 @@ PYBIND11_MODULE(_C, m) {
           .def("reduce_scatter_cast", &MoodistBackend::reduceScatterCast, py::arg("output"), py::arg("input"),
                py::arg("op") = 0, py::arg("premul") = 1.0, py::call_guard<py::gil_scoped_release>());
   m.attr("MoodistProcessGroup") = backend;
+  m.def("live_process_groups", &MoodistBackend::live, "every moodist group alive in this process");
   m.def("find_process_group", &MoodistBackend::find, "the live moodist group with this name, or None");
 
   bind_extras(m, backend);

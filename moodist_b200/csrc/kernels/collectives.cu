@@ -73,20 +73,34 @@ template <typename InT, typename OutT, bool kCast>
 __global__ void __launch_bounds__(kThreads, 1)
     all_gather_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, int64_t in_heap_off,
                       void* out, size_t count, size_t out_stride) {
+  // How this rank offers its shard (in_heap_off): >= 0 in place from its heap (mode 1), -1 staged locally and
+  // pulled by the peers (mode 0), -2 pushed into every peer's staging slot (mode 2: one NVLink write latency
+  // instead of an announce + read round trip, at the price of a local copy on the receiver; for small shards).
   const int b = blockIdx.x, G = gridDim.x;
-  const bool direct = in_heap_off >= 0;
+  const uint32_t mode = in_heap_off >= 0 ? 1u : (in_heap_off == -2 ? 2u : 0u);
   entry_wait(c, seq);
   size_t begin, len;
   slice_of(count, G, b, begin, len);
   OutT* o = reinterpret_cast<OutT*>(out);
   const InT* src_local = reinterpret_cast<const InT*>(in);
-  if (b == 0) announce(c, seq, direct ? (uint64_t)in_heap_off : 0, direct ? 1u : 0u);
-  if (!direct) {
+  if (b == 0) announce(c, seq, mode == 1 ? (uint64_t)in_heap_off : 0, mode);
+  if (mode == 0) {
     OutT* st = reinterpret_cast<OutT*>(stage_ptr(c, c.rank, seq));
     if constexpr (kCast) {
       cta_cast_copy<InT, OutT>(st + begin, src_local + begin, len, 1.f, false);
     } else {
       cta_copy(st + begin, src_local + begin, len * sizeof(OutT));
+    }
+    signal_ready(c, seq, b, 0, -1);
+  } else if (mode == 2) {
+    for (int i = 1; i < c.world; ++i) {
+      int p = (c.rank + i) % c.world;
+      OutT* st = reinterpret_cast<OutT*>(stage_ptr(c, p, seq)) + (size_t)c.rank * count;
+      if constexpr (kCast) {
+        cta_cast_copy<InT, OutT>(st + begin, src_local + begin, len, 1.f, false);
+      } else {
+        cta_copy(st + begin, src_local + begin, len * sizeof(OutT));
+      }
     }
     signal_ready(c, seq, b, 0, -1);
   }
@@ -98,20 +112,23 @@ __global__ void __launch_bounds__(kThreads, 1)
       cta_copy(o + (size_t)c.rank * out_stride + begin, src_local + begin, len * sizeof(OutT));
   }
   for (int i = 1; i < c.world; ++i) {
-    int p = (c.rank + i) % c.world;
+    int p = (c.rank - i + c.world) % c.world;  // pushes arrive from rank-1 first
     const OutT* src;
     uint64_t off;
-    uint32_t pdirect;
-    bool ok = wait_announce_warp(c, seq, p, off, pdirect);
-    if (!pdirect) {
+    uint32_t pmode;
+    bool ok = wait_announce_warp(c, seq, p, off, pmode);
+    if (pmode == 0) {
       ok = ok && wait_ready_warp(c, seq, p, b, 0);
       src = reinterpret_cast<const OutT*>(stage_ptr(c, p, seq));
+    } else if (pmode == 2) {
+      ok = ok && wait_ready_warp(c, seq, p, b, 0);
+      src = reinterpret_cast<const OutT*>(stage_ptr(c, c.rank, seq)) + (size_t)p * count;
     } else {
       src = reinterpret_cast<const OutT*>(reinterpret_cast<const uint8_t*>(c.peer[p]) + off);
     }
     if (ok) cta_copy(o + (size_t)p * out_stride + begin, src + begin, len * sizeof(OutT));
   }
-  exit_done(c, seq, direct);
+  exit_done(c, seq, mode == 1);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -481,6 +498,7 @@ extern "C" int mb_all_gather(const mb_comm_t* c, uint32_t seq, const void* in, i
   size_t osz = dtype_size(out_dtype);
   if (!osz || !dtype_size(in_dtype)) return MB_ERR_ARG;
   if (c->world == 1) return mb_copy_cast(in, out, count, in_dtype, out_dtype, 1.f, 0, stream);
+  if (in_heap_off == -2 && (size_t)c->world * count * osz > c->staging_bytes / 2) in_heap_off = -1;
   if (in_heap_off < 0 && count * osz > c->staging_bytes / 2) return MB_ERR_TOO_BIG;
   if (in_heap_off >= 0 && in_dtype != out_dtype) return MB_ERR_ARG;
   int grid = pick_grid(c, count * osz);

@@ -122,6 +122,15 @@ typedef struct {
 int mb_gather_scatter(const mb_comm_t* c, uint32_t seq, const mb_stage_copy_t* stage_in, int num_stage,
                       const mb_piece_t* pieces, int num_pieces, size_t max_bytes, void* stream);
 
+// --- NVLS variants (collectives_nvls.cu); need the multicast alias (mb_nvls_available) ------------------
+int mb_nvls_available(const mb_comm_t* c);
+int mb_all_reduce_nvls(const mb_comm_t* c, uint32_t seq, const void* in, void* out, size_t count, int dtype, int op,
+                       float premul, void* stream);
+int mb_reduce_scatter_nvls(const mb_comm_t* c, uint32_t seq, const void* in, void* out, size_t count, size_t in_stride,
+                           int in_dtype, int out_dtype, int op, float premul, void* stream);
+int mb_all_gather_nvls(const mb_comm_t* c, uint32_t seq, const void* in, void* out, size_t bytes,
+                       size_t out_stride_bytes, void* stream);
+
 // --- fused collective GEMMs (fused_gemm.cu) -------------------------------------------------------
 // C = gather(A shards) · B^T (gather_on_b 0) or C = A · gather(B shards)^T (gather_on_b 1); `shard` is this
 // rank's [rows/world, K] bf16 slice, `other` the local operand. comm_ctas: copy CTAs (0 = default).

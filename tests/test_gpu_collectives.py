@@ -62,3 +62,82 @@ def _cuda_collectives(rank, world, port):
 
 def test_cuda_collectives_2gpu():
     run_ranks(_cuda_collectives, 2, timeout=240, env={"MOODIST_DEVICE_TIMEOUT_MS": 5000})
+
+
+def _nvls_variants(rank, world, port):
+    dist = init_moodist(rank, world, port, device="cuda")
+    import moodist_b200
+
+    dev = torch.device("cuda", rank)
+    pg = moodist_b200.get_backend()
+    t = torch.ones(8, device=dev)
+    dist.all_reduce(t)  # creates the CUDA group
+    if "nvls=1" not in pg.describe():
+        dist.destroy_process_group()
+        return  # no multicast support on this machine: nothing to check
+    with pg.options(method=1):
+        for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 3e-2)):
+            for n in (64, 1000, 4096, (1 << 20) + 24):
+                g = torch.Generator().manual_seed(n)
+                allin = torch.randn(world, n, generator=g).to(dtype)
+                x = allin[rank].to(dev).contiguous()
+                dist.all_reduce(x)
+                ref = allin.double().sum(0)
+                err = (x.double().cpu() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
+                assert err <= tol, ("nvls all_reduce", dtype, n, err)
+                m = (n // 8) * 8
+                rs_in = torch.randn(world, world, m, generator=g).to(dtype)
+                out = torch.empty(m, device=dev, dtype=dtype)
+                dist.reduce_scatter_tensor(out, rs_in[rank].reshape(-1).to(dev).contiguous(), op=dist.ReduceOp.AVG)
+                ref = rs_in[:, rank].double().mean(0)
+                err = (out.double().cpu() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
+                assert err <= tol, ("nvls reduce_scatter", dtype, m, err)
+                full = torch.randn(world, n, generator=g).to(dtype)
+                ag = torch.empty(world * n, device=dev, dtype=dtype)
+                dist.all_gather_into_tensor(ag, full[rank].to(dev).contiguous())
+                assert torch.equal(ag.cpu().view(world, n), full), ("nvls all_gather", dtype, n)
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_nvls_variants_2gpu():
+    run_ranks(_nvls_variants, 2, timeout=240, env={"MOODIST_DEVICE_TIMEOUT_MS": 5000})
+
+
+def _absent_rank(rank, world, port):
+    """A device wait that runs out returns a status instead of hanging: rank 1 never launches."""
+    import time
+
+    dist = init_moodist(rank, world, port, device="cuda")
+    dev = torch.device("cuda", rank)
+    t = torch.ones(1024, device=dev)
+    dist.all_reduce(t)
+    torch.cuda.synchronize()
+    store = dist.distributed_c10d._get_default_store()
+    if rank == 0:
+        x = torch.ones(1 << 16, device=dev)
+        t0 = time.time()
+        dist.all_reduce(x)  # the peer is not there: the kernel gives up after the cap
+        torch.cuda.synchronize()
+        assert time.time() - t0 < 10
+        with pytest.raises(RuntimeError, match="timed out"):
+            dist.all_reduce(x)
+        y = torch.ones(4, device=dev) * 3  # the context is still usable
+        assert float(y.sum()) == 12.0
+        store.set("rank0_done", b"1")
+        store.wait(["rank1_done"])  # rank 0 hosts the store: it leaves last
+    else:
+        store.wait(["rank0_done"])  # leaves only between steps, nothing of its own in flight
+        store.set("rank1_done", b"1")
+    import os
+
+    os._exit(0)
+
+
+def test_absent_rank_times_out_without_hanging():
+    statuses = run_ranks(_absent_rank, 2, timeout=120, expect_failure=True,
+                         env={"MOODIST_DEVICE_TIMEOUT_MS": 800, "MOODIST_DISABLE_NVLS": 1, "NCCL_NVLS_ENABLE": 0})
+    # ranks leave through os._exit(0) without writing a status file; a Python failure would have written one
+    for s in statuses:
+        assert s.startswith("died with exit code 0"), s
