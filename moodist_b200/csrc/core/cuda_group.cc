@@ -59,9 +59,10 @@ class CudaGroupImpl final : public CudaGroup {
     comm_.world = world;
     comm_.wait_ns = (uint64_t)env_long("MOODIST_DEVICE_TIMEOUT_MS", 30000) * 1000000ull;
     comm_.max_ctas = (int)env_long("MOODIST_MAX_CTAS", 0);
+    comm_.tuning = env_flag("MOODIST_AG_STAGGER") ? MB_TUNE_STAGGER : 0;
     push_bytes_ = (size_t)env_long("MOODIST_AG_PUSH_BYTES", 1 << 20);
     // smallest message (bytes) for which the NVLS variant is picked automatically; -1 = never
-    nvls_ar_min_ = env_long("MOODIST_NVLS_AR_MIN_BYTES", 512 << 10);
+    nvls_ar_min_ = env_long("MOODIST_NVLS_AR_MIN_BYTES", 2 << 20);
     nvls_rs_min_ = env_long("MOODIST_NVLS_RS_MIN_BYTES", -1);
     nvls_ag_min_ = env_long("MOODIST_NVLS_AG_MIN_BYTES", -1);
     RT_CHECK(cudaHostAlloc((void**)&status_host_, 64, cudaHostAllocMapped));
@@ -219,7 +220,7 @@ class CudaGroupImpl final : public CudaGroup {
     if (!sz) fail("moodist: all_reduce: unsupported dtype");
     if (count == 0) return;
     size_t half = comm_.staging_bytes / 2;
-    size_t oneshot_max = (size_t)env_long("MOODIST_AR_ONESHOT_BYTES", 256 * 1024);
+    size_t oneshot_max = (size_t)env_long("MOODIST_AR_ONESHOT_BYTES", 2 << 20);
     // two-shot needs 2*world*chunk bytes of the half; keep pieces well inside
     size_t piece = count;
     if (world_ > 1 && count * sz * 2 + (size_t)world_ * 2 * 64 * sz > half)

@@ -104,6 +104,34 @@ __device__ __forceinline__ bool wait_ready_warp(const mb_comm_t& c, uint32_t seq
   return ok != 0;
 }
 
+// Every lane p < world of the calling warp waits for peer p at the same time: its announcement and, unless
+// that peer is read in place (mode 1), the READY word of slice b. Callers read a peer's answer with
+// __shfl_sync(field, p). Sequential waits cost one flag latency per peer; this costs one in total.
+struct PeerInfo {
+  uint32_t ok, lo, hi, mode;
+};
+__device__ __forceinline__ PeerInfo wait_peers_warp(const mb_comm_t& c, uint32_t seq, int b, int bank) {
+  const int lane = threadIdx.x & 31;
+  PeerInfo r{1u, 0u, 0u, 0u};
+  if (lane < c.world && lane != c.rank) {
+    uint64_t off;
+    uint32_t aux;
+    r.ok = wait_announce(c, seq, lane, off, aux);
+    r.lo = (uint32_t)off;
+    r.hi = (uint32_t)(off >> 32);
+    r.mode = aux;
+    if (r.ok && aux != 1u) {
+      r.ok = wait_geq_sys(c.flags[c.rank] + (bank ? F_READY2 : F_READY) + lane * kMaxCtas + b, seq, c.wait_ns);
+      if (!r.ok) fail(c, kTimeoutReady, lane);
+    }
+  }
+  __syncwarp();
+  return r;
+}
+__device__ __forceinline__ bool all_peers_ok(const PeerInfo& r) {
+  return __all_sync(0xffffffffu, r.ok != 0);
+}
+
 // End of op. The last CTA of the grid publishes DONE[rank] = seq everywhere; with `hold` it also waits
 // until every peer is done (their reads of this rank's user memory have finished).
 __device__ __forceinline__ void exit_done(const mb_comm_t& c, uint32_t seq, bool hold) {

@@ -111,17 +111,17 @@ __global__ void __launch_bounds__(kThreads, 1)
     if ((const void*)(o + (size_t)c.rank * out_stride) != in)
       cta_copy(o + (size_t)c.rank * out_stride + begin, src_local + begin, len * sizeof(OutT));
   }
-  for (int i = 1; i < c.world; ++i) {
-    int p = (c.rank - i + c.world) % c.world;  // pushes arrive from rank-1 first
+  const PeerInfo pi = wait_peers_warp(c, seq, b, 0);
+  const int start = (c.tuning & MB_TUNE_STAGGER) ? b : 0;  // staggered: CTAs read different peers at any moment
+  for (int i = 0; i < c.world - 1; ++i) {
+    int p = (c.rank - 1 - (start + i) % (c.world - 1) + 2 * c.world) % c.world;  // pushes arrive from rank-1 first
+    const bool ok = __shfl_sync(0xffffffffu, pi.ok, p) != 0;
+    const uint32_t pmode = __shfl_sync(0xffffffffu, pi.mode, p);
+    const uint64_t off = (uint64_t)__shfl_sync(0xffffffffu, pi.lo, p) | ((uint64_t)__shfl_sync(0xffffffffu, pi.hi, p) << 32);
     const OutT* src;
-    uint64_t off;
-    uint32_t pmode;
-    bool ok = wait_announce_warp(c, seq, p, off, pmode);
     if (pmode == 0) {
-      ok = ok && wait_ready_warp(c, seq, p, b, 0);
       src = reinterpret_cast<const OutT*>(stage_ptr(c, p, seq));
     } else if (pmode == 2) {
-      ok = ok && wait_ready_warp(c, seq, p, b, 0);
       src = reinterpret_cast<const OutT*>(stage_ptr(c, c.rank, seq)) + (size_t)p * count;
     } else {
       src = reinterpret_cast<const OutT*>(reinterpret_cast<const uint8_t*>(c.peer[p]) + off);
@@ -148,22 +148,22 @@ __global__ void __launch_bounds__(kThreads, 1)
   srcs[0] = x + (size_t)c.rank * in_stride + begin;
   if (b == 0) announce(c, seq, direct ? (uint64_t)in_heap_off : 0, direct ? 1u : 0u);
   if (!direct) {
-    // push this rank's contribution for every other owner into that owner's staging slot [rank]
+    // push this rank's contribution for every other owner into that owner's staging slot [rank];
+    // one fence + flag round for all of them (the owners need every source before they can reduce anyway)
     for (int i = 1; i < c.world; ++i) {
       int p = (c.rank + i) % c.world;
       InT* dst = reinterpret_cast<InT*>(stage_ptr(c, p, seq)) + (size_t)c.rank * count + begin;
       cta_copy(dst, x + (size_t)p * in_stride + begin, len * sizeof(InT));
-      signal_ready(c, seq, b, 0, p);
     }
+    signal_ready(c, seq, b, 0, -1);
   }
-  bool ok = true;
+  const PeerInfo pi = wait_peers_warp(c, seq, b, 0);
+  const bool ok = all_peers_ok(pi);
   for (int i = 1; i < c.world; ++i) {
     int p = (c.rank + i) % c.world;
-    uint64_t off;
-    uint32_t pdirect;
-    ok = wait_announce_warp(c, seq, p, off, pdirect) && ok;
-    if (!pdirect) {
-      ok = wait_ready_warp(c, seq, p, b, 0) && ok;
+    const uint32_t pdirect = __shfl_sync(0xffffffffu, pi.mode, p);
+    const uint64_t off = (uint64_t)__shfl_sync(0xffffffffu, pi.lo, p) | ((uint64_t)__shfl_sync(0xffffffffu, pi.hi, p) << 32);
+    if (pdirect != 1u) {
       srcs[i] = reinterpret_cast<const InT*>(stage_ptr(c, c.rank, seq)) + (size_t)p * count + begin;
     } else {
       srcs[i] = reinterpret_cast<const InT*>(reinterpret_cast<const uint8_t*>(c.peer[p]) + off) +

@@ -39,7 +39,9 @@ constexpr int kStageBytes = kATileBytes + kBTileBytes;
 constexpr int kNumThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr int kAccCols = BN;  // fp32 columns per accumulator buffer
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int kEpiRowBytes = 144;                  // 128-byte line + 16 bytes of padding: conflict-free 16-byte accesses
+constexpr int kEpiPatchBytes = 32 * kEpiRowBytes;  // one patch per epilogue warp
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/ + 4 * kEpiPatchBytes;
 
 enum Epilogue : int { kEpiNone = 0, kEpiSilu = 1 };
 
@@ -148,6 +150,7 @@ __device__ __forceinline__ void gemm_body(const Params& p, const CUtensorMap* tm
   uint64_t* acc_empty = acc_full + 2;      // [2]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
+  uint8_t* epi_patch = reinterpret_cast<uint8_t*>(bars) + 256;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -289,51 +292,61 @@ __device__ __forceinline__ void gemm_body(const Params& p, const CUtensorMap* tm
         break;
       }
       tc_fence_after_sync();
-      const int row = tm * BM + q * 32 + lane;
-      OutT* crow;
+      // Output rows of this warp: 32 consecutive rows starting at row0. Each lane owns one row in TMEM; to
+      // write full 128-byte lines (instead of 32 scattered 16-byte pieces per instruction, which wastes DRAM
+      // sectors locally and NVLink packets remotely) the row pieces go through a per-warp shared-memory
+      // patch and leave as 4 rows x 128 bytes per store instruction.
+      const int row0 = tm * BM + q * 32;
+      OutT* cbase;
       if constexpr (kScatterOut) {
         const int owner = (tm * BM) / p.scatter_rows;  // M is a multiple of scatter_rows * num_shards here
-        crow = reinterpret_cast<OutT*>(p.scatter_dst[owner]) + (int64_t)(row - owner * p.scatter_rows) * p.ldc;
+        cbase = reinterpret_cast<OutT*>(p.scatter_dst[owner]) + (int64_t)(row0 - owner * p.scatter_rows) * p.ldc;
       } else {
-        crow = reinterpret_cast<OutT*>(p.C) + (int64_t)row * p.ldc;
+        cbase = reinterpret_cast<OutT*>(p.C) + (int64_t)row0 * p.ldc;
       }
+      uint8_t* patch = epi_patch + (warp - 2) * kEpiPatchBytes;
       const uint32_t taddr = tmem_base + acc * kAccCols + ((uint32_t)(q * 32) << 16);
+      constexpr int kColsPerPass = 128 / (int)sizeof(OutT);  // columns that make one 128-byte line
+      constexpr int kLdsPerPass = kColsPerPass / 32;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = tn * BN + c * 32;
-        if (p.epilogue == kEpiSilu) {
+      for (int c = 0; c < BN / kColsPerPass; ++c) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float x = __uint_as_float(r[i]);
-            r[i] = __float_as_uint(x / (1.0f + __expf(-x)));
+        for (int h = 0; h < kLdsPerPass; ++h) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * kColsPerPass + h * 32, r);
+          tmem_ld_wait();
+          if (p.epilogue == kEpiSilu) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float x = __uint_as_float(r[i]);
+              r[i] = __float_as_uint(x / (1.0f + __expf(-x)));
+            }
           }
-        }
-        if (row < p.M) {
+          uint4* dst = reinterpret_cast<uint4*>(patch + lane * kEpiRowBytes + h * (32 * (int)sizeof(OutT)));
           if constexpr (sizeof(OutT) == 2) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
-              if (col0 + g * 8 < p.N) {
-                uint4 v;
-                v.x = pack_bf16x2(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
-                v.y = pack_bf16x2(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
-                v.z = pack_bf16x2(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
-                v.w = pack_bf16x2(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
-                *reinterpret_cast<uint4*>(crow + col0 + g * 8) = v;
-              }
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
+              dst[g] = v;
             }
           } else {
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              if (col0 + g * 4 < p.N) {
-                uint4 v = make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
-                *reinterpret_cast<uint4*>(crow + col0 + g * 4) = v;
-              }
-            }
+            for (int g = 0; g < 8; ++g) dst[g] = make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
           }
         }
+        __syncwarp();
+        const int col = tn * BN + c * kColsPerPass + (lane & 7) * (16 / (int)sizeof(OutT));
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rr = i * 4 + (lane >> 3);
+          const uint4 v = *reinterpret_cast<const uint4*>(patch + rr * kEpiRowBytes + (lane & 7) * 16);
+          if (row0 + rr < p.M && col < p.N) *reinterpret_cast<uint4*>(cbase + (int64_t)rr * p.ldc + col) = v;
+        }
+        __syncwarp();
       }
       // accumulator buffer may be overwritten by the MMA warp from here on
       tc_fence_before_sync();

@@ -54,7 +54,10 @@ typedef struct {
   uint32_t* status;        // word the device can write (may be host-mapped): 0 ok, else code | peer << 16
   uint64_t wait_ns;        // cap for device-side waits
   int max_ctas;            // upper bound on CTAs a collective may occupy (0 = default)
+  uint32_t tuning;         // MB_TUNE_* bits
 } mb_comm_t;
+
+#define MB_TUNE_STAGGER 1u  // all-gather: CTA b starts its pulls at peer rank-1-b instead of rank-1
 
 #define MB_FLAG_WORDS 4096  // uint32 words per flag page; layout in coll.cuh
 

@@ -81,6 +81,8 @@ __device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
 }
 
 // Wait until *p >= v (wrap-safe signed distance). false = gave up.
+// (Polling with relaxed loads and one system fence at the end measured slower than acquire loads: the
+// fence costs more than the polls it saves.)
 __device__ __forceinline__ bool wait_geq_sys(const uint32_t* p, uint32_t v, uint64_t limit_ns) {
   SpinGuard g(limit_ns);
   while ((int32_t)(ld_acquire_sys(p) - v) < 0) {

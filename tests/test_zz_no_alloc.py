@@ -46,6 +46,7 @@ class Comm(ctypes.Structure):
         ("status", ctypes.c_void_p),
         ("wait_ns", ctypes.c_uint64),
         ("max_ctas", ctypes.c_int),
+        ("tuning", ctypes.c_uint32),
     ]
 
 
