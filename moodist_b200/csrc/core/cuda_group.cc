@@ -59,18 +59,22 @@ class CudaGroupImpl final : public CudaGroup {
     comm_.world = world;
     comm_.wait_ns = (uint64_t)env_long("MOODIST_DEVICE_TIMEOUT_MS", 30000) * 1000000ull;
     comm_.max_ctas = (int)env_long("MOODIST_MAX_CTAS", 0);
-    comm_.tuning = env_flag("MOODIST_AG_STAGGER") ? MB_TUNE_STAGGER : 0;
+    comm_.tuning = env_long("MOODIST_AG_STAGGER", 1) ? MB_TUNE_STAGGER : 0;
     push_bytes_ = (size_t)env_long("MOODIST_AG_PUSH_BYTES", 1 << 20);
     // smallest message (bytes) for which the NVLS variant is picked automatically; -1 = never
     nvls_ar_min_ = env_long("MOODIST_NVLS_AR_MIN_BYTES", 2 << 20);
     nvls_rs_min_ = env_long("MOODIST_NVLS_RS_MIN_BYTES", -1);
-    nvls_ag_min_ = env_long("MOODIST_NVLS_AG_MIN_BYTES", -1);
+    // measured on 8 GPUs: the multimem.st all-gather wins between 32 KiB and ~2 MiB per rank, the P2P pull above
+    nvls_ag_min_ = env_long("MOODIST_NVLS_AG_MIN_BYTES", 32 << 10);
+    nvls_ag_max_ = env_long("MOODIST_NVLS_AG_MAX_BYTES", 3 << 20);
     RT_CHECK(cudaHostAlloc((void**)&status_host_, 64, cudaHostAllocMapped));
     memset((void*)status_host_, 0, 64);
     void* dptr = nullptr;
     RT_CHECK(cudaHostGetDevicePointer(&dptr, (void*)status_host_, 0));
     comm_.status = (uint32_t*)dptr;
-    if (world > 1) {
+    // MOODIST_FORCE_STAGING=1 gives a one-rank group its staging area too, so the fused kernels can be run
+    // (and profiled) on a single GPU
+    if (world > 1 || env_flag("MOODIST_FORCE_STAGING")) {
       size_t staging = (size_t)env_long("MOODIST_STAGING_MB", 1024) << 20;
       heap_ = &SymmHeap::instance(device);
       mem_ = heap_->attach_group(store, key, rank, world, staging, true);
@@ -165,6 +169,7 @@ class CudaGroupImpl final : public CudaGroup {
     if (count == 0) return;
     int64_t off = idt == odt ? heap_off(in, count * isz) : -1;
     if (idt == odt && off < 0 && world_ > 1 && want_nvls(nvls_ag_min_, count * isz) &&
+        (opts_.method == 1 || nvls_ag_max_ < 0 || count * isz <= (size_t)nvls_ag_max_) &&
         (size_t)world_ * count * isz <= comm_.staging_bytes / 2) {
       uint32_t seq = next_seq(s);
       run(mb_all_gather_nvls(&comm_, seq, in, out, count * isz, count * isz, s), "all_gather (NVLS)");
@@ -301,7 +306,7 @@ class CudaGroupImpl final : public CudaGroup {
   bool have_last_ = false;
   uint32_t seq_ = 0;
   size_t push_bytes_ = 0;
-  long nvls_ar_min_ = -1, nvls_rs_min_ = -1, nvls_ag_min_ = -1;
+  long nvls_ar_min_ = -1, nvls_rs_min_ = -1, nvls_ag_min_ = -1, nvls_ag_max_ = -1;
   uint64_t launches_ = 0;
   void* scratch_ = nullptr;
   size_t scratch_bytes_ = 0;

@@ -112,7 +112,7 @@ std::tuple<at::Tensor, at::Tensor> ag_gemm(c10::intrusive_ptr<MoodistBackend> pg
   const mb_comm_t* comm = static_cast<const mb_comm_t*>(g.comm_struct());
   CUstream_st* raw = reinterpret_cast<CUstream_st*>(stream.stream());
   at::Tensor gathered;
-  if (world == 1) {
+  if (world == 1 && comm->staging_bytes == 0) {
     int rc = mb_gemm_bf16(gather_weight ? other.data_ptr() : shard.data_ptr(), gather_weight ? shard.data_ptr() : other.data_ptr(),
                           y.data_ptr(), (int)M, (int)N, (int)K, gather_weight ? other.stride(0) : K,
                           gather_weight ? K : other.stride(0), N, 0, 0, out_fp32, (int)epilogue, comm->status, 0, raw);
@@ -145,7 +145,7 @@ at::Tensor gemm_rs(c10::intrusive_ptr<MoodistBackend> pg, const at::Tensor& a, c
   CudaGroup& g = pg->cudaGroup(a.get_device());
   const mb_comm_t* comm = static_cast<const mb_comm_t*>(g.comm_struct());
   at::Tensor out = at::empty({M / world, N}, a.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
-  if (world == 1) {
+  if (world == 1 && comm->staging_bytes == 0) {
     TORCH_CHECK(scale == 1.0, "moodist gemm_rs: scale needs more than one rank");
     int rc = mb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0), N, 0,
                           trans_b, out_fp32, 0, comm->status, 0, raw);

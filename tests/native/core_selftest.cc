@@ -1,0 +1,213 @@
+// Stand-alone checks of the torch-free core: wire format golden bytes, the registered-memory table,
+// the bootstrap ring (ranks as threads), the store mesh, and the CPU reduce loops.
+#include <cmath>
+#include <condition_variable>
+#include <cstdio>
+#include <map>
+#include <mutex>
+#include <optional>
+#include <thread>
+#include <variant>
+
+#include "core/cpu_allocator.h"
+#include "core/cpu_reduce.h"
+#include "core/log.h"
+#include "core/setup_comms.h"
+#include "core/store.h"
+#include "core/tcp_transport.h"
+#include "core/wire.h"
+
+using namespace moodist;
+
+static int failures = 0;
+#define CHECK(cond)                                              \
+  do {                                                           \
+    if (!(cond)) {                                               \
+      fprintf(stderr, "FAILED %s:%d: %s\n", __FILE__, __LINE__, #cond); \
+      ++failures;                                                \
+    }                                                            \
+  } while (0)
+
+struct MemStore : KVStore {
+  std::mutex mu;
+  std::condition_variable cv;
+  std::map<std::string, std::vector<uint8_t>> kv;
+  void set(const std::string& k, const std::vector<uint8_t>& v) override {
+    std::lock_guard<std::mutex> lk(mu);
+    kv[k] = v;
+    cv.notify_all();
+  }
+  std::vector<uint8_t> get(const std::string& k) override {
+    std::unique_lock<std::mutex> lk(mu);
+    cv.wait(lk, [&] { return kv.count(k) != 0; });
+    return kv[k];
+  }
+  bool check(const std::vector<std::string>& keys) override {
+    std::lock_guard<std::mutex> lk(mu);
+    for (auto& k : keys)
+      if (!kv.count(k)) return false;
+    return true;
+  }
+  void wait(const std::vector<std::string>& keys) override {
+    for (auto& k : keys) get(k);
+  }
+};
+
+struct Sample {
+  uint32_t a = 0;
+  std::string s;
+  std::vector<uint16_t> v;
+  template <class Ar>
+  void wire(Ar& ar) {
+    ar(a, s, v);
+  }
+};
+
+static void test_wire() {
+  // scalars raw, strings / vectors with u64 lengths, bool and optional flag as one byte, variant index u64
+  Bytes b = encode((uint32_t)0x01020304, std::string("ab"), std::vector<uint16_t>{1, 2}, true, std::optional<uint8_t>(7),
+                   std::optional<uint8_t>(), std::variant<int32_t, std::string>(std::string("z")),
+                   std::pair<uint8_t, uint8_t>(5, 6));
+  CHECK(to_hex(b) ==
+        "04030201"
+        "0200000000000000" "6162"
+        "0200000000000000" "01000200"
+        "01"
+        "01" "07"
+        "00"
+        "0100000000000000" "0100000000000000" "7a"
+        "0506");
+  uint32_t a;
+  std::string s;
+  std::vector<uint16_t> v;
+  bool flag;
+  std::optional<uint8_t> o1, o2;
+  std::variant<int32_t, std::string> var;
+  std::pair<uint8_t, uint8_t> pr;
+  decode_exact(b, a, s, v, flag, o1, o2, var, pr);
+  CHECK(a == 0x01020304 && s == "ab" && v.size() == 2 && v[1] == 2 && flag && o1 && *o1 == 7 && !o2);
+  CHECK(var.index() == 1 && std::get<1>(var) == "z" && pr.second == 6);
+  Sample in{9, "hello", {3, 4, 5}}, out;
+  decode_exact(encode(in), out);
+  CHECK(out.a == 9 && out.s == "hello" && out.v.size() == 3);
+  std::map<std::string, int32_t> m{{"k", -1}}, m2;
+  decode_exact(encode(m), m2);
+  CHECK(m2["k"] == -1);
+  bool threw = false;
+  try {
+    Bytes extra = encode((uint8_t)1, (uint8_t)2);
+    uint8_t x;
+    decode_exact(extra, x);
+  } catch (const WireError&) {
+    threw = true;
+  }
+  CHECK(threw);  // trailing bytes are an error
+  threw = false;
+  try {
+    Bytes shortb = {5, 0, 0, 0, 0, 0, 0, 0, 'a'};
+    std::string t;
+    decode_exact(shortb, t);
+  } catch (const WireError&) {
+    threw = true;
+  }
+  CHECK(threw);  // length beyond the buffer
+  CHECK(from_hex(to_hex(b)) == b);
+}
+
+static void test_mr_table() {
+  std::vector<uint8_t> buf(1000);
+  uint32_t k = MrTable::instance().add(buf.data(), buf.size());
+  uintptr_t base = (uintptr_t)buf.data();
+  CHECK(MrTable::instance().check(k, base, 1000) != nullptr);
+  CHECK(MrTable::instance().check(k, base + 999, 1) != nullptr);
+  CHECK(MrTable::instance().check(k, base + 999, 2) == nullptr);   // runs past the end
+  CHECK(MrTable::instance().check(k, base - 1, 1) == nullptr);     // starts before
+  CHECK(MrTable::instance().check(k, base, (size_t)-1) == nullptr);  // overflow
+  CHECK(MrTable::instance().check(k + 1000, base, 1) == nullptr);  // unknown key
+  MrTable::instance().remove(k);
+  CHECK(MrTable::instance().check(k, base, 1) == nullptr);
+}
+
+static void test_setup_comms(int world) {
+  MemStore store;
+  std::vector<std::thread> th;
+  std::vector<int> ok(world, 0);
+  for (int r = 0; r < world; ++r) {
+    th.emplace_back([&, r] {
+      try {
+        auto sc = SetupComms::create(store, "ringtest" + std::to_string(world), r, world, 20.0);
+        auto all = sc->allgather(std::string("rank") + std::to_string(r));
+        bool good = (int)all.size() == world;
+        for (int i = 0; i < world && good; ++i) good = all[i] == "rank" + std::to_string(i);
+        auto nums = sc->allgather((uint64_t)(r * 7));
+        for (int i = 0; i < world; ++i) good = good && nums[i] == (uint64_t)(i * 7);
+        // routed point-to-point: everyone sends to the rank two ahead (forwarded through one hop)
+        int dst = (r + 2) % world, src = (r - 2 + 2 * world) % world;
+        sc->send_to(dst, std::vector<int32_t>{r, r + 1});
+        auto got = sc->recv_from<std::vector<int32_t>>(src);
+        good = good && got.size() == 2 && got[0] == src;
+        bool threw = false;
+        sc->send_to((r + 1) % world, (uint32_t)5);
+        try {
+          sc->recv_from<std::string>((r - 1 + world) % world);  // wrong type must not be misread
+        } catch (const WireError&) {
+          threw = true;
+        }
+        good = good && threw;
+        sc->allgather((uint8_t)0);  // keep everyone alive until all messages were delivered
+        ok[r] = good;
+      } catch (const std::exception& e) {
+        fprintf(stderr, "setup comms rank %d: %s\n", r, e.what());
+      }
+    });
+  }
+  for (auto& t : th) t.join();
+  for (int r = 0; r < world; ++r) CHECK(ok[r]);
+}
+
+static void test_reduce() {
+  float a[5] = {1, 2, 3, 4, 5}, b[5] = {5, 4, 3, 2, 1}, o[5];
+  const void* srcs[2] = {a, b};
+  cpu_reduce(o, srcs, 2, 5, kDtF32, kRedAvg, 0.5, true);
+  CHECK(o[0] == 3.f && o[4] == 3.f);
+  cpu_reduce(o, srcs, 2, 5, kDtF32, kRedMax, 1, false);
+  CHECK(o[0] == 5.f && o[2] == 3.f);
+  uint16_t x[2] = {float_to_bf16(1.5f), float_to_bf16(-2.f)}, y[2] = {float_to_bf16(0.25f), float_to_bf16(8.f)}, z[2];
+  const void* s2[2] = {x, y};
+  cpu_reduce(z, s2, 2, 2, kDtBF16, kRedSum, 1, false);
+  CHECK(bf16_to_float(z[0]) == 1.75f && bf16_to_float(z[1]) == 6.f);
+  for (float f : {0.f, 1.f, -1.f, 65504.f, 1e-5f, 0.333f}) CHECK(std::fabs(f16_to_float(float_to_f16(f)) - f) <= std::fabs(f) * 1e-3f + 1e-7f);
+  int64_t i1[2] = {1LL << 40, -5}, i2[2] = {3, -7}, io[2];
+  const void* s3[2] = {i1, i2};
+  cpu_reduce(io, s3, 2, 2, kDtI64, kRedMin, 1, false);
+  CHECK(io[0] == 3 && io[1] == -7);
+}
+
+static void test_mesh_and_alloc() {
+  for (int world : {1, 2, 4, 5, 8, 33}) {
+    auto mesh = store_mesh(world, 99);
+    auto hops = store_first_hops(mesh, 0);
+    for (int d = 0; d < world; ++d) CHECK(hops[d] >= 0);
+    for (auto& adj : mesh) CHECK(adj.size() <= 4);
+  }
+  void* p = cpu_alloc(1000);
+  CHECK(p && cpu_allocator_owns(p) && ((uintptr_t)p & 63) == 0);
+  void* base;
+  size_t size;
+  CHECK(cpu_allocator_region(p, &base, &size) && size >= 1000);
+  cpu_free(p);
+  int onstack;
+  CHECK(!cpu_allocator_owns(&onstack));
+}
+
+int main() {
+  test_wire();
+  test_mr_table();
+  test_reduce();
+  test_mesh_and_alloc();
+  test_setup_comms(1);
+  test_setup_comms(2);
+  test_setup_comms(5);
+  printf("%s\n", failures ? "CORE SELFTEST FAILED" : "CORE SELFTEST OK");
+  return failures ? 1 : 0;
+}
