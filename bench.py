@@ -34,6 +34,9 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=8192)
     ap.add_argument("--backend", default="moodist", choices=["moodist", "nccl"],
                     help="process-group backend under FSDP2 (nccl = the baseline this library is compared with)")
+    ap.add_argument("--engine", default="native", choices=["native", "fsdp2"],
+                    help="native: the resident-parameter sharded engine; fsdp2: torch fully_shard per block")
+    ap.add_argument("--no-symmetric", action="store_true", help="keep gathered parameters out of the symmetric heap")
     return ap.parse_args()
 
 
@@ -52,7 +55,12 @@ def main():
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     import moodist_b200
     from moodist_b200.models.llama import LlamaConfig
-    from moodist_b200.ops.gemm import gemm_launches
+    from moodist_b200.ops.gemm import gemm_launches as _gemm_launches
+    from moodist_b200.ops.train import train_op_launches
+
+    def gemm_launches():
+        return _gemm_launches() + train_op_launches()
+
     from moodist_b200.parallel.fsdp import ShardedTrainer
     from moodist_b200.utils.clocks import ClockSampler
 
@@ -75,7 +83,7 @@ def main():
 
     cfg = LlamaConfig.llama3_8b() if args.model == "llama3-8b" else LlamaConfig.tiny()
     seq = min(args.seq_len, cfg.max_seq_len)
-    trainer = ShardedTrainer(cfg, seed=0)
+    trainer = ShardedTrainer(cfg, seed=0, engine=args.engine, symmetric_memory=not args.no_symmetric)
 
     def host_batch(i):
         g = torch.Generator().manual_seed(1000 * rank + i)
@@ -146,8 +154,9 @@ def main():
                 "global_batch": world,
                 "seq_len": seq,
                 "parallelism": f"fsdp{world}",
+                "engine": args.engine,
                 "reduce_dtype": "fp32",
-                "optimizer": "AdamW (fused)",
+                "optimizer": "AdamW, bf16 moments" + (" (flat-shard kernel)" if args.engine == "native" else " (torch fused)"),
                 "l2": "inputs larger than L2: each step streams the 16 GB of bf16 weights plus activations",
                 "timing": "CUDA events on the launching stream, max over ranks",
             },

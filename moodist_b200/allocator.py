@@ -44,6 +44,12 @@ def cuda_allocator_enabled() -> bool:
     return _enabled
 
 
+def symmetric_mem_pool() -> "torch.cuda.MemPool":
+    """A ``torch.cuda.MemPool`` backed by the symmetric heap, for ``torch.cuda.use_mem_pool``; tensors
+    allocated from it stay valid for as long as the pool object is alive."""
+    return torch.cuda.MemPool(_pluggable_allocator().allocator())
+
+
 @contextlib.contextmanager
 def symmetric_pool():
     """Allocations inside the block come from the symmetric heap; yields the ``torch.cuda.MemPool``."""

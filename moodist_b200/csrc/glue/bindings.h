@@ -12,6 +12,7 @@ using BackendClass = pybind11::class_<MoodistBackend, c10d::Backend, c10::intrus
 // ops.cc: GEMM and fused ops
 void bind_ops(pybind11::module_& m, BackendClass& backend);
 void bind_fused(pybind11::module_& m);
+void bind_train_ops(pybind11::module_& m);
 
 // store_glue.cc: TcpStore
 void bind_store(pybind11::module_& m);
@@ -28,6 +29,7 @@ void bind_allocators(pybind11::module_& m, BackendClass& backend);
 inline void bind_extras(pybind11::module_& m, BackendClass& backend) {
   bind_ops(m, backend);
   bind_fused(m);
+  bind_train_ops(m);
   bind_store(m);
   bind_queue(m, backend);
   bind_custom_op(m, backend);

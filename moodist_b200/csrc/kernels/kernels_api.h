@@ -151,6 +151,26 @@ int mb_gemm_rs(const mb_comm_t* c, uint32_t seq, const void* A, const void* B, v
 int mb_copy_cast(const void* in, void* out, size_t count, int in_dtype, int out_dtype, float scale, int use_scale,
                  void* stream);
 
+// --- training-step kernels (train_ops.cu): bf16 tensors, rows contiguous, 16-byte aligned ------------
+// Rotary embedding in place on heads [0, n_heads) of x[tokens, row_stride]; pairs are (j, j + head_dim/2),
+// position = row % seq, tables are fp32 [seq, head_dim/2]. inverse: rotate by the negative angle.
+int mb_rope_bf16(void* x, const float* cos_tab, const float* sin_tab, int64_t tokens, int seq, int n_heads,
+                 int head_dim, int64_t row_stride, int inverse, void* stream);
+// out[t, j] = silu(gu[t, j]) * gu[t, F + j]; the backward fills dgu[t, 0:2F] from dout[t, 0:F].
+int mb_swiglu_fwd_bf16(const void* gu, void* out, int64_t tokens, int F, int64_t gu_stride, int64_t out_stride,
+                       void* stream);
+int mb_swiglu_bwd_bf16(const void* gu, const void* dout, void* dgu, int64_t tokens, int F, int64_t gu_stride,
+                       int64_t dout_stride, int64_t dgu_stride, void* stream);
+// loss[row] = logsumexp(logits[row]) - logits[row, target]; lse[row] kept for the backward, which
+// overwrites logits with (softmax - onehot) * gscale[0] * inv_count.
+int mb_cross_entropy_fwd_bf16(const void* logits, const int64_t* targets, float* lse, float* loss, int64_t rows, int V,
+                              int64_t stride, int64_t ignore_index, void* stream);
+int mb_cross_entropy_bwd_bf16(void* logits, const int64_t* targets, const float* lse, const float* gscale,
+                              float inv_count, int64_t rows, int V, int64_t stride, int64_t ignore_index, void* stream);
+// AdamW (decoupled decay, bias-corrected) on n bf16 parameters with bf16 moments; grad_dtype MB_F32 or MB_BF16.
+int mb_adamw_bf16(void* p, const void* g, int grad_dtype, void* m, void* v, int64_t n, float lr, float b1, float b2,
+                  float eps, float wd, int step, float grad_scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -3,7 +3,9 @@
 The reference library has no model code (it is a communication backend); its FSDP2 benchmark target is
 a Llama-3-8B-shaped network: 32 layers, d=4096, 32 heads / 8 KV heads, SwiGLU FFN 14336, vocabulary
 128256, RoPE theta 500000, RMSNorm.  Every projection is a ``moodist_b200.ops.gemm.Linear`` so the
-matrix products of forward and backward run on the tcgen05 kernel; attention uses torch's fused SDPA.
+matrix products of forward and backward run on the tcgen05 kernel; rotary embedding, SwiGLU and the
+cross-entropy are the single-pass kernels of ``moodist_b200.ops.train``; attention uses torch's fused SDPA
+(cuDNN's sm_100 flash kernels on a B200).
 """
 
 from __future__ import annotations
@@ -15,6 +17,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from ..ops.gemm import Linear
+from ..ops.train import cross_entropy, rope_qkv_, swiglu
 
 
 @dataclass
@@ -81,10 +84,11 @@ class Attention(nn.Module):
 
     def forward(self, x, cos, sin):
         B, S, _ = x.shape
-        qkv = self.wqkv(x)
+        # q and k heads are rotated in place inside the projection's output (nothing else reads it)
+        qkv = rope_qkv_(self.wqkv(x), cos, sin, self.n_heads + self.n_kv, self.hd)
         q, k, v = qkv.split([self.n_heads * self.hd, self.n_kv * self.hd, self.n_kv * self.hd], dim=-1)
-        q = apply_rope(q.view(B, S, self.n_heads, self.hd), cos, sin).transpose(1, 2)
-        k = apply_rope(k.view(B, S, self.n_kv, self.hd), cos, sin).transpose(1, 2)
+        q = q.view(B, S, self.n_heads, self.hd).transpose(1, 2)
+        k = k.view(B, S, self.n_kv, self.hd).transpose(1, 2)
         v = v.view(B, S, self.n_kv, self.hd).transpose(1, 2)
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         return self.wo(o.transpose(1, 2).reshape(B, S, self.n_heads * self.hd))
@@ -98,8 +102,7 @@ class MLP(nn.Module):
         self.w2 = Linear(cfg.ffn_dim, cfg.dim, device=device)
 
     def forward(self, x):
-        g, u = self.w13(x).chunk(2, dim=-1)
-        return self.w2(F.silu(g) * u)
+        return self.w2(swiglu(self.w13(x)))
 
 
 class Block(nn.Module):
@@ -144,4 +147,5 @@ class Llama(nn.Module):
 
 
 def loss_fn(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
-    return F.cross_entropy(logits.float().reshape(-1, logits.shape[-1]), targets.reshape(-1))
+    """Mean token cross-entropy; on CUDA the backward overwrites ``logits`` with its gradient."""
+    return cross_entropy(logits, targets)

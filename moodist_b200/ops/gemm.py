@@ -39,11 +39,17 @@ class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w):
         ctx.save_for_backward(x, w)
+        # a sharded engine may hand the weight a slot in its flat gradient buffer: the weight-gradient
+        # GEMM then writes there directly and autograd sees no gradient for the weight
+        ctx.grad_slot = getattr(w, "_mb_grad_slot", None)
         x2 = x.reshape(-1, x.shape[-1])
         if not _rows_ok(x2):
             x2 = x2.contiguous()
-        y = gemm(x2, w)
-        return y.view(*x.shape[:-1], w.shape[0])
+        # allocate the result in its final shape: the caller may update it in place (rotary embedding,
+        # cross-entropy gradient), which autograd forbids on a view made inside a custom Function
+        y = torch.empty(*x.shape[:-1], w.shape[0], device=x.device, dtype=torch.bfloat16)
+        gemm(x2, w, out=y.view(-1, w.shape[0]))
+        return y
 
     @staticmethod
     def backward(ctx, gy):
@@ -60,7 +66,12 @@ class _Linear(torch.autograd.Function):
             gx = gemm(gy2, w, trans_b=True).view(x.shape)
         if ctx.needs_input_grad[1]:
             # dw[N, K] = dy[T, N]^T @ x[T, K]: both operands MN-major
-            gw = gemm(gy2, x2, trans_a=True, trans_b=True)
+            slot = ctx.grad_slot
+            if slot is not None and not slot.written and gy2.is_cuda:
+                gemm(gy2, x2, trans_a=True, trans_b=True, out=slot.view)
+                slot.written = True
+            else:
+                gw = gemm(gy2, x2, trans_a=True, trans_b=True)
         return gx, gw
 
 
@@ -77,6 +88,7 @@ class Linear(torch.nn.Module):
         self.in_features = in_features
         self.out_features = out_features
         self.weight = torch.nn.Parameter(torch.empty(out_features, in_features, device=device, dtype=dtype))
+        self.weight._mb_linear_weight = True  # lets a sharded engine route the weight gradient (see _Linear)
 
     def reset_parameters(self, std: float = 0.02) -> None:
         torch.nn.init.normal_(self.weight, mean=0.0, std=std)

@@ -1,14 +1,18 @@
 """Sharded data-parallel training of the Llama-shaped decoder over the moodist backend.
 
-``ShardedTrainer`` is the public training entry point: it builds the model on the local GPU, shards
-every transformer block with torch's FSDP2 ``fully_shard`` on a process group whose collectives are this
-library's sm_100a kernels (per-layer all-gather of bf16 parameters, reduce-scatter of gradients with
-fp32 accumulation and the 1/world average folded into the kernel), and exposes ``step(tokens)``, which
-takes a pinned host batch and returns the loss as a Python float.
+``ShardedTrainer`` is the public training entry point: it builds the model on the local GPU, shards it
+over a process group whose collectives are this library's sm_100a kernels, and exposes ``step(tokens)``,
+which takes a pinned host batch and returns the loss as a Python float.  Two engines:
 
-The reference ships no trainer; FSDP2 over its process group is how it is benchmarked, so the same
-construction is used here (``fully_shard`` needs all_gather_into_tensor, reduce_scatter_tensor,
-all_reduce, broadcast and barrier from the backend).
+``engine="native"`` (default)  ``moodist_b200.parallel.sharded.ShardedEngine``: gathered parameters stay
+    resident (180 GB of HBM make the second all-gather of the classic schedule pointless), gradients are
+    reduce-scattered from bf16 with fp32 accumulation, AdamW runs on the flat shard and the updated shard
+    is all-gathered in place, all per unit on a side stream under the rest of the backward pass.
+``engine="fsdp2"``  torch's ``fully_shard`` per transformer block (bf16 parameters, fp32 reduce), the
+    construction the reference is benchmarked under; needs all_gather_into_tensor,
+    reduce_scatter_tensor, all_reduce, broadcast and barrier from the backend.
+
+The reference ships no trainer of its own.
 """
 
 from __future__ import annotations
@@ -31,6 +35,8 @@ class ShardedTrainer:
         lr: float = 1e-4,
         seed: int = 0,
         reshard_after_forward: bool = True,
+        engine: str = "native",
+        symmetric_memory: bool = True,
     ):
         if not torch.cuda.is_available():
             raise RuntimeError("ShardedTrainer needs a CUDA device")
@@ -42,13 +48,28 @@ class ShardedTrainer:
         torch.manual_seed(seed)
         self.model = Llama(cfg, device=self.device)
         self.model.init_weights(seed)
-        ranks = dist.get_process_group_ranks(self.group)
-        mesh = DeviceMesh.from_group(self.group, "cuda", mesh=torch.tensor(ranks), mesh_dim_names=("dp",))
-        policy = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
-        for layer in self.model.layers:
-            fully_shard(layer, mesh=mesh, mp_policy=policy, reshard_after_forward=reshard_after_forward)
-        fully_shard(self.model, mesh=mesh, mp_policy=policy, reshard_after_forward=reshard_after_forward)
-        self.opt = torch.optim.AdamW(self.model.parameters(), lr=lr, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+        self.engine = None
+        self.opt = None
+        if engine == "native":
+            from .sharded import ShardedEngine
+
+            m = self.model
+            units = [("embed", [m.embed])]
+            units += [(f"layers.{i}", [layer]) for i, layer in enumerate(m.layers)]
+            units += [("head", [m.norm, m.lm_head])]
+            self.engine = ShardedEngine(units, group=self.group, lr=lr, betas=(0.9, 0.95), weight_decay=0.1,
+                                        symmetric_memory=symmetric_memory)
+        elif engine == "fsdp2":
+            ranks = dist.get_process_group_ranks(self.group)
+            mesh = DeviceMesh.from_group(self.group, "cuda", mesh=torch.tensor(ranks), mesh_dim_names=("dp",))
+            policy = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+            for layer in self.model.layers:
+                fully_shard(layer, mesh=mesh, mp_policy=policy, reshard_after_forward=reshard_after_forward)
+            fully_shard(self.model, mesh=mesh, mp_policy=policy, reshard_after_forward=reshard_after_forward)
+            self.opt = torch.optim.AdamW(self.model.parameters(), lr=lr, betas=(0.9, 0.95), weight_decay=0.1,
+                                         fused=True)
+        else:
+            raise ValueError(f"unknown engine {engine!r} (native or fsdp2)")
         self._tok_dev = None
 
     def step_on_device(self, tokens: torch.Tensor) -> torch.Tensor:
@@ -57,8 +78,11 @@ class ShardedTrainer:
         logits = self.model(inp)
         loss = loss_fn(logits, tgt)
         loss.backward()
-        self.opt.step()
-        self.opt.zero_grad(set_to_none=True)
+        if self.engine is not None:
+            self.engine.finish_step()
+        else:
+            self.opt.step()
+            self.opt.zero_grad(set_to_none=True)
         return loss
 
     def step(self, tokens_host: torch.Tensor) -> float:
