@@ -70,6 +70,9 @@ void bind_ops(pybind11::module_& m, BackendClass& backend) {
   m.def("gemm", &gemm, pybind11::arg("a"), pybind11::arg("b"), pybind11::arg("trans_a") = false,
         pybind11::arg("trans_b") = false, pybind11::arg("out") = pybind11::none(), pybind11::arg("out_fp32") = false,
         pybind11::arg("epilogue") = 0);
+  m.def("gemm_variant", [](int v) { mb_gemm_set_variant(v); }, pybind11::arg("variant"),
+        "0: kernel chosen by shape (two-SM cta_group::2 kernel from 256 rows up); 1: always the one-SM kernel");
+  m.def("get_gemm_variant", []() { return mb_gemm_get_variant(); });
   (void)backend;
 }
 

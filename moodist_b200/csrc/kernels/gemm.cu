@@ -112,6 +112,11 @@ int fill_params_and_maps(Params& p, CUtensorMap& ta, CUtensorMap& tb, const void
   return MB_OK;
 }
 
+bool want_pair(int M, int N);
+int gemm_pair_launch(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                     int a_mn, int b_mn, int out_fp32, int epilogue, uint32_t* status, uint64_t wait_ns,
+                     cudaStream_t stream);
+
 }  // namespace gemm
 }  // namespace mb
 
@@ -120,6 +125,9 @@ using namespace mb::gemm;
 extern "C" int mb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
                             int64_t ldc, int a_mn_major, int b_mn_major, int out_fp32, int epilogue,
                             uint32_t* status, uint64_t wait_ns, void* stream) {
+  if (want_pair(M, N))
+    return gemm_pair_launch(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, out_fp32, epilogue, status,
+                            wait_ns, static_cast<cudaStream_t>(stream));
   Params p;
   CUtensorMap ta, tb;
   int rc = fill_params_and_maps(p, ta, tb, A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, out_fp32,

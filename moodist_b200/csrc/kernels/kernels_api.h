@@ -70,6 +70,11 @@ int mb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
                  int a_mn_major, int b_mn_major, int out_fp32, int epilogue, uint32_t* status, uint64_t wait_ns,
                  void* stream);
 
+// Kernel choice of mb_gemm_bf16: 0 by shape (the two-SM cta_group::2 kernel from 256 rows up), 1 always the
+// one-SM kernel, 2 same as 0. Initial value from MOODIST_GEMM_VARIANT.
+void mb_gemm_set_variant(int v);
+int mb_gemm_get_variant(void);
+
 // --- collectives -------------------------------------------------------------------------------
 // seq: per-group collective counter (starts at 1, +1 per call, identical on every rank).
 // *_heap_off: byte offset of the tensor inside this rank's symmetric heap when it lives there (peers

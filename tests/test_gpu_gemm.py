@@ -10,10 +10,23 @@ def _ref(a, b):
     return a.float() @ b.float().t()
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 264, 136), (1024, 2048, 1024), (4096, 1536, 4096)])
+@pytest.fixture(params=[1, 0], ids=["one_sm", "by_shape"])
+def variant(request):
+    """Every GEMM test runs on the one-SM kernel and on the shape-based choice (two-SM pairs from 256 rows)."""
+    from moodist_b200._core import _C
+
+    old = _C.get_gemm_variant()
+    _C.gemm_variant(request.param)
+    yield request.param
+    _C.gemm_variant(old)
+
+
+@pytest.mark.parametrize(
+    "M,N,K", [(128, 256, 64), (200, 264, 136), (256, 256, 64), (392, 520, 200), (1024, 2048, 1024), (4096, 1536, 4096)]
+)
 @pytest.mark.parametrize("trans_a", [False, True])
 @pytest.mark.parametrize("trans_b", [False, True])
-def test_gemm_matches_fp32(M, N, K, trans_a, trans_b):
+def test_gemm_matches_fp32(M, N, K, trans_a, trans_b, variant):
     from moodist_b200.ops.gemm import gemm
 
     torch.manual_seed(M + N + K)
@@ -30,7 +43,7 @@ def test_gemm_matches_fp32(M, N, K, trans_a, trans_b):
     assert rel32 < 1e-5, rel32
 
 
-def test_gemm_silu_epilogue():
+def test_gemm_silu_epilogue(variant):
     from moodist_b200.ops.gemm import gemm
 
     a = torch.randn(512, 512, device="cuda").bfloat16()
@@ -40,7 +53,7 @@ def test_gemm_silu_epilogue():
     assert (c.float() - ref).abs().max() / ref.abs().max() < 1e-2
 
 
-def test_linear_autograd_matches_torch():
+def test_linear_autograd_matches_torch(variant):
     from moodist_b200.ops.gemm import linear
 
     torch.manual_seed(0)
