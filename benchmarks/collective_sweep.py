@@ -5,6 +5,10 @@ GPUs. Device-timed (CUDA events), max over ranks, 20 warm-up + 100 timed iterati
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29540 \
         benchmarks/collective_sweep.py --out gpurun_out/sweep8.jsonl
 
+``--impls`` may also name ``moodist_sym``: the same kernels on buffers allocated from the symmetric heap
+(``moodist_b200.allocator.symmetric_pool``, what ``enable_cuda_allocator()`` gives every tensor), which peers
+read in place instead of through the staging area.
+
 Bus bandwidth follows the usual convention: AG / RS move (n-1)/n of the gathered buffer per GPU, AR twice that.
 """
 
@@ -54,7 +58,12 @@ def main():
     torch.cuda.set_device(lr)
     dev = torch.device("cuda", lr)
     dist.init_process_group("moodist", rank=rank, world_size=world)
-    groups = {"moodist": dist.group.WORLD}
+    groups = {"moodist": dist.group.WORLD, "moodist_sym": dist.group.WORLD}
+    sym_pool = None
+    if "moodist_sym" in args.impls.split(","):
+        from moodist_b200.allocator import symmetric_mem_pool
+
+        sym_pool = symmetric_mem_pool()
     if "nccl" in args.impls.split(","):
         groups["nccl"] = dist.new_group(backend="nccl")
     dtypes = {"bf16": torch.bfloat16, "fp32": torch.float32}
@@ -71,12 +80,16 @@ def main():
             n = nbytes // es
             iters = args.iters if nbytes <= (64 << 20) else max(10, args.iters // 5)
             warm = args.warmup if nbytes <= (64 << 20) else 5
-            torch.manual_seed(rank)
-            x = (torch.rand(n, device=dev) * 2 - 1).to(dt)
-            big = (torch.rand(world * n, device=dev) * 2 - 1).to(dt) if world * nbytes <= (8 << 30) else None
-            out_small = torch.empty(n, device=dev, dtype=dt)
             for impl in args.impls.split(","):
                 g = groups[impl]
+                torch.manual_seed(rank)
+                x = (torch.rand(n, device=dev) * 2 - 1).to(dt)
+                big = (torch.rand(world * n, device=dev) * 2 - 1).to(dt) if world * nbytes <= (8 << 30) else None
+                out_small = torch.empty(n, device=dev, dtype=dt)
+                if impl == "moodist_sym":
+                    with torch.cuda.use_mem_pool(sym_pool):
+                        x, out_small = x.clone(), out_small.clone()
+                        big = big.clone() if big is not None else None
                 bar = lambda: dist.barrier(group=g)  # noqa: E731
                 for op in args.ops.split(","):
                     if big is None:
@@ -102,7 +115,7 @@ def main():
                     rows.append(row)
                     if rank == 0:
                         print(json.dumps(row), flush=True)
-            del x, big, out_small
+                del x, big, out_small
             torch.cuda.empty_cache()
     if rank == 0 and args.out:
         with open(args.out, "w") as f:

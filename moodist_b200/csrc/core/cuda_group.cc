@@ -61,6 +61,10 @@ class CudaGroupImpl final : public CudaGroup {
     comm_.max_ctas = (int)env_long("MOODIST_MAX_CTAS", 0);
     comm_.tuning = env_long("MOODIST_AG_STAGGER", 1) ? MB_TUNE_STAGGER : 0;
     push_bytes_ = (size_t)env_long("MOODIST_AG_PUSH_BYTES", 1 << 20);
+    // From this shard size up the all-gather pushes again (in two pipelined halves per CTA): posted writes
+    // fill NVLink better than read round trips, and the receiver's copy out of staging hides under the
+    // arrival of the second half. -1: large shards are pulled.
+    push_large_ = env_long("MOODIST_AG_PUSH_LARGE_BYTES", 4 << 20);
     // smallest message (bytes) for which the NVLS variant is picked automatically; -1 = never
     nvls_ar_min_ = env_long("MOODIST_NVLS_AR_MIN_BYTES", 2 << 20);
     nvls_rs_min_ = env_long("MOODIST_NVLS_RS_MIN_BYTES", -1);
@@ -176,10 +180,15 @@ class CudaGroupImpl final : public CudaGroup {
       finish_op(s);
       return;
     }
-    if (off < 0 && count * osz <= push_bytes_) off = -2;  // small shard: push it
+    const bool push = off < 0 && (count * osz <= push_bytes_ || (push_large_ >= 0 && count * osz >= (size_t)push_large_));
+    if (push) off = -2;
     size_t half = comm_.staging_bytes / 2;
     size_t piece = count;
-    if (world_ > 1 && off < 0 && count * osz > half) piece = (half / osz) & ~(size_t)63;
+    if (world_ > 1 && push && (size_t)world_ * count * osz > half) {
+      piece = (half / ((size_t)world_ * osz)) & ~(size_t)63;  // every peer's slot of a piece fits one half
+    } else if (world_ > 1 && off == -1 && count * osz > half) {
+      piece = (half / osz) & ~(size_t)63;
+    }
     for (size_t done = 0; done < count; done += piece) {
       size_t n = std::min(piece, count - done);
       uint32_t seq = next_seq(s);
@@ -306,6 +315,7 @@ class CudaGroupImpl final : public CudaGroup {
   bool have_last_ = false;
   uint32_t seq_ = 0;
   size_t push_bytes_ = 0;
+  long push_large_ = -1;
   long nvls_ar_min_ = -1, nvls_rs_min_ = -1, nvls_ag_min_ = -1, nvls_ag_max_ = -1;
   uint64_t launches_ = 0;
   void* scratch_ = nullptr;

@@ -128,6 +128,30 @@ __device__ __forceinline__ PeerInfo wait_peers_warp(const mb_comm_t& c, uint32_t
   __syncwarp();
   return r;
 }
+// Second phase of a two-bank transfer: every lane p < world whose peer pushes its data (announced mode ==
+// push_mode) waits for that peer's READY word of slice b in `bank`. Returns the per-lane result (the first
+// phase's result for lanes that had nothing to wait for).
+__device__ __forceinline__ uint32_t wait_bank_warp(const mb_comm_t& c, uint32_t seq, int b, int bank, const PeerInfo& pi,
+                                                   uint32_t push_mode) {
+  const int lane = threadIdx.x & 31;
+  uint32_t ok = pi.ok;
+  if (lane < c.world && lane != c.rank && pi.ok && pi.mode == push_mode) {
+    ok = wait_geq_sys(c.flags[c.rank] + (bank ? F_READY2 : F_READY) + lane * kMaxCtas + b, seq, c.wait_ns);
+    if (!ok) fail(c, kTimeoutReady, lane);
+  }
+  __syncwarp();
+  return ok;
+}
+// A CTA slice of `len` elements is sent in two halves (one READY bank each) when it is big enough for the
+// receiver's copy-out / reduce of the first half to hide under the arrival of the second. Same answer on
+// every rank: it depends only on the element count and the grid.
+constexpr size_t kTwoPhaseBytes = 64 << 10;
+template <typename T>
+__device__ __forceinline__ size_t first_half(size_t len) {
+  if (len * sizeof(T) < kTwoPhaseBytes) return len;
+  size_t h = len / 2;
+  return h - h % (256 / sizeof(T));  // keep the second half 256-byte aligned relative to the slice
+}
 __device__ __forceinline__ bool all_peers_ok(const PeerInfo& r) {
   return __all_sync(0xffffffffu, r.ok != 0);
 }

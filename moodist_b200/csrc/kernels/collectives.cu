@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   slice_of(count, G, b, begin, len);
   OutT* o = reinterpret_cast<OutT*>(out);
   const InT* src_local = reinterpret_cast<const InT*>(in);
+  const size_t h0 = first_half<OutT>(len);
   if (b == 0) announce(c, seq, mode == 1 ? (uint64_t)in_heap_off : 0, mode);
   if (mode == 0) {
     OutT* st = reinterpret_cast<OutT*>(stage_ptr(c, c.rank, seq));
@@ -95,16 +96,22 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     signal_ready(c, seq, b, 0, -1);
   } else if (mode == 2) {
-    for (int i = 1; i < c.world; ++i) {
-      int p = (c.rank + i) % c.world;
-      OutT* st = reinterpret_cast<OutT*>(stage_ptr(c, p, seq)) + (size_t)c.rank * count;
-      if constexpr (kCast) {
-        cta_cast_copy<InT, OutT>(st + begin, src_local + begin, len, 1.f, false);
-      } else {
-        cta_copy(st + begin, src_local + begin, len * sizeof(OutT));
+    // big slices go out in two halves, each with its own READY bank, so that the receivers copy the first
+    // half out of staging while the second is still crossing NVLink
+    for (int h = 0; h < 2; ++h) {
+      const size_t hb = h ? begin + h0 : begin, hl = h ? len - h0 : h0;
+      if (h && hl == 0) break;
+      for (int i = 1; i < c.world; ++i) {
+        int p = (c.rank + i) % c.world;
+        OutT* st = reinterpret_cast<OutT*>(stage_ptr(c, p, seq)) + (size_t)c.rank * count;
+        if constexpr (kCast) {
+          cta_cast_copy<InT, OutT>(st + hb, src_local + hb, hl, 1.f, false);
+        } else {
+          cta_copy(st + hb, src_local + hb, hl * sizeof(OutT));
+        }
       }
+      signal_ready(c, seq, b, h, -1);
     }
-    signal_ready(c, seq, b, 0, -1);
   }
   // own shard straight into place
   if constexpr (kCast) {
@@ -128,7 +135,20 @@ __global__ void __launch_bounds__(kThreads, 1)
     } else {
       src = reinterpret_cast<const OutT*>(reinterpret_cast<const uint8_t*>(c.peer[p]) + off);
     }
-    if (ok) cta_copy(o + (size_t)p * out_stride + begin, src + begin, len * sizeof(OutT));
+    // a pushed slice is complete up to h0 so far; pulled ones (modes 0, 1) are read whole
+    const size_t n = pmode == 2 ? h0 : len;
+    if (ok) cta_copy(o + (size_t)p * out_stride + begin, src + begin, n * sizeof(OutT));
+  }
+  if (h0 < len) {
+    const uint32_t ok2 = wait_bank_warp(c, seq, b, 1, pi, 2u);
+    for (int i = 0; i < c.world - 1; ++i) {
+      int p = (c.rank - 1 - (start + i) % (c.world - 1) + 2 * c.world) % c.world;
+      const bool ok = __shfl_sync(0xffffffffu, ok2, p) != 0;
+      const uint32_t pmode = __shfl_sync(0xffffffffu, pi.mode, p);
+      if (pmode != 2 || !ok) continue;
+      const OutT* src = reinterpret_cast<const OutT*>(stage_ptr(c, c.rank, seq)) + (size_t)p * count;
+      cta_copy(o + (size_t)p * out_stride + begin + h0, src + begin + h0, (len - h0) * sizeof(OutT));
+    }
   }
   exit_done(c, seq, mode == 1);
 }
@@ -148,16 +168,22 @@ __global__ void __launch_bounds__(kThreads, 1)
   const InT* x = reinterpret_cast<const InT*>(in);
   const InT* srcs[MB_MAX_RANKS];
   srcs[0] = x + (size_t)c.rank * in_stride + begin;
+  const size_t h0 = first_half<InT>(len);
   if (b == 0) announce(c, seq, direct ? (uint64_t)in_heap_off : 0, direct ? 1u : 0u);
   if (!direct) {
     // push this rank's contribution for every other owner into that owner's staging slot [rank];
     // one fence + flag round for all of them (the owners need every source before they can reduce anyway)
-    for (int i = 1; i < c.world; ++i) {
-      int p = (c.rank + i) % c.world;
-      InT* dst = reinterpret_cast<InT*>(stage_ptr(c, p, seq)) + (size_t)c.rank * count + begin;
-      cta_copy(dst, x + (size_t)p * in_stride + begin, len * sizeof(InT));
+    // two halves, two READY banks: the owners reduce the first half while the second is still arriving
+    for (int h = 0; h < 2; ++h) {
+      const size_t hb = h ? begin + h0 : begin, hl = h ? len - h0 : h0;
+      if (h && hl == 0) break;
+      for (int i = 1; i < c.world; ++i) {
+        int p = (c.rank + i) % c.world;
+        InT* dst = reinterpret_cast<InT*>(stage_ptr(c, p, seq)) + (size_t)c.rank * count + hb;
+        cta_copy(dst, x + (size_t)p * in_stride + hb, hl * sizeof(InT));
+      }
+      signal_ready(c, seq, b, h, -1);
     }
-    signal_ready(c, seq, b, 0, -1);
   }
   const PeerInfo pi = wait_peers_warp(c, seq, b, 0);
   const bool ok = all_peers_ok(pi);
@@ -172,7 +198,18 @@ __global__ void __launch_bounds__(kThreads, 1)
                 (size_t)c.rank * in_stride + begin;
     }
   }
-  if (ok) cta_reduce<InT, OutT, kOp>(reinterpret_cast<OutT*>(out) + begin, srcs, c.world, len, scale, use_scale);
+  // Peers that push (every rank that is not read in place) have delivered [0, h0) of the slice so far.
+  const bool any_pushed = __any_sync(0xffffffffu, (threadIdx.x & 31) < c.world && (threadIdx.x & 31) != c.rank &&
+                                                      pi.mode == 0u);
+  if (h0 == len || !any_pushed) {
+    if (ok) cta_reduce<InT, OutT, kOp>(reinterpret_cast<OutT*>(out) + begin, srcs, c.world, len, scale, use_scale);
+  } else {
+    if (ok) cta_reduce<InT, OutT, kOp>(reinterpret_cast<OutT*>(out) + begin, srcs, c.world, h0, scale, use_scale);
+    const bool ok2 = __all_sync(0xffffffffu, wait_bank_warp(c, seq, b, 1, pi, 0u) != 0);
+    for (int i = 0; i < c.world; ++i) srcs[i] += h0;
+    if (ok2) cta_reduce<InT, OutT, kOp>(reinterpret_cast<OutT*>(out) + begin + h0, srcs, c.world, len - h0, scale,
+                                         use_scale);
+  }
   exit_done(c, seq, direct);
 }
 

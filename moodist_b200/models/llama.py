@@ -64,6 +64,16 @@ def rope_tables(head_dim: int, seq_len: int, theta: float, device) -> tuple[torc
     return freqs.cos(), freqs.sin()
 
 
+class RopeTables:
+    """fp32 cos / sin tables handed to the blocks as one opaque object, so that wrappers which cast tensor
+    arguments to the compute dtype (FSDP2 mixed precision) leave their precision alone."""
+
+    __slots__ = ("cos", "sin")
+
+    def __init__(self, cos: torch.Tensor, sin: torch.Tensor):
+        self.cos, self.sin = cos, sin
+
+
 def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     # x: [B, S, H, D]; rotate pairs (even, odd halves layout)
     d = x.shape[-1] // 2
@@ -82,7 +92,8 @@ class Attention(nn.Module):
         self.wqkv = Linear(cfg.dim, (cfg.n_heads + 2 * cfg.n_kv_heads) * self.hd, device=device)
         self.wo = Linear(cfg.n_heads * self.hd, cfg.dim, device=device)
 
-    def forward(self, x, cos, sin):
+    def forward(self, x, rope: RopeTables):
+        cos, sin = rope.cos, rope.sin
         B, S, _ = x.shape
         # q and k heads are rotated in place inside the projection's output (nothing else reads it)
         qkv = rope_qkv_(self.wqkv(x), cos, sin, self.n_heads + self.n_kv, self.hd)
@@ -113,8 +124,8 @@ class Block(nn.Module):
         self.mlp_norm = RMSNorm(cfg.dim, cfg.norm_eps, device=device)
         self.mlp = MLP(cfg, device=device)
 
-    def forward(self, x, cos, sin):
-        x = x + self.attn(self.attn_norm(x), cos, sin)
+    def forward(self, x, rope: RopeTables):
+        x = x + self.attn(self.attn_norm(x), rope)
         return x + self.mlp(self.mlp_norm(x))
 
 
@@ -139,10 +150,10 @@ class Llama(nn.Module):
         S = tokens.shape[1]
         if self._rope is None or self._rope[0].shape[0] < S or self._rope[0].device != tokens.device:
             self._rope = rope_tables(self.cfg.dim // self.cfg.n_heads, max(S, 16), self.cfg.rope_theta, tokens.device)
-        cos, sin = self._rope
+        rope = RopeTables(*self._rope)
         x = self.embed(tokens)
         for layer in self.layers:
-            x = layer(x, cos, sin)
+            x = layer(x, rope)
         return self.lm_head(self.norm(x))
 
 

@@ -137,7 +137,7 @@ class ShardedEngine:
         if any(p.dtype != dtype for p in u.params):
             raise ValueError(f"unit {u.name}: parameters of one unit must share a dtype")
         u.full = self._alloc(u.numel, dtype, symmetric=True)
-        u.grad = self._alloc(u.numel, dtype)
+        u.grad = self._alloc(u.numel, dtype, symmetric=True)  # owners reduce straight out of the peers' buffers
         shard = u.numel // self.world
         u.exp_avg = torch.zeros(shard, dtype=dtype, device=self.device)
         u.exp_avg_sq = torch.zeros(shard, dtype=dtype, device=self.device)
