@@ -36,6 +36,8 @@ def parse_args():
                     help="process-group backend under FSDP2 (nccl = the baseline this library is compared with)")
     ap.add_argument("--engine", default="native", choices=["native", "fsdp2"],
                     help="native: the resident-parameter sharded engine; fsdp2: torch fully_shard per block")
+    ap.add_argument("--kernel-less", action="store_true",
+                    help="collectives move their bytes with DMA copies between flag kernels (no SMs taken from the GEMMs)")
     ap.add_argument("--no-symmetric", action="store_true", help="keep gathered parameters out of the symmetric heap")
     return ap.parse_args()
 
@@ -80,6 +82,8 @@ def main():
             return 0
 
     backend = moodist_b200.get_backend() if args.backend == "moodist" else _NoBackend()
+    if args.kernel_less and args.backend == "moodist":
+        backend.set_prefer_kernel_less(True)
 
     cfg = LlamaConfig.llama3_8b() if args.model == "llama3-8b" else LlamaConfig.tiny()
     seq = min(args.seq_len, cfg.max_seq_len)
@@ -155,6 +159,7 @@ def main():
                 "seq_len": seq,
                 "parallelism": f"fsdp{world}",
                 "engine": args.engine,
+                "kernel_less": bool(args.kernel_less),
                 "reduce_dtype": "fp32",
                 "optimizer": "AdamW, bf16 moments" + (" (flat-shard kernel)" if args.engine == "native" else " (torch fused)"),
                 "l2": "inputs larger than L2: each step streams the 16 GB of bf16 weights plus activations",

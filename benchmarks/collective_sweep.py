@@ -7,7 +7,8 @@ GPUs. Device-timed (CUDA events), max over ranks, 20 warm-up + 100 timed iterati
 
 ``--impls`` may also name ``moodist_sym``: the same kernels on buffers allocated from the symmetric heap
 (``moodist_b200.allocator.symmetric_pool``, what ``enable_cuda_allocator()`` gives every tensor), which peers
-read in place instead of through the staging area.
+read in place instead of through the staging area, and ``moodist_ce``: the copy-engine variant
+(``set_prefer_kernel_less(True)``), which spends no SM time on the transfer.
 
 Bus bandwidth follows the usual convention: AG / RS move (n-1)/n of the gathered buffer per GPU, AR twice that.
 """
@@ -58,7 +59,8 @@ def main():
     torch.cuda.set_device(lr)
     dev = torch.device("cuda", lr)
     dist.init_process_group("moodist", rank=rank, world_size=world)
-    groups = {"moodist": dist.group.WORLD, "moodist_sym": dist.group.WORLD}
+    groups = {"moodist": dist.group.WORLD, "moodist_sym": dist.group.WORLD, "moodist_ce": dist.group.WORLD}
+    backend = moodist_b200.get_backend()
     sym_pool = None
     if "moodist_sym" in args.impls.split(","):
         from moodist_b200.allocator import symmetric_mem_pool
@@ -82,6 +84,8 @@ def main():
             warm = args.warmup if nbytes <= (64 << 20) else 5
             for impl in args.impls.split(","):
                 g = groups[impl]
+                # moodist_ce: the copy-engine variant (DMA copies between one-warp flag kernels) from 1 MiB per rank up
+                backend.set_prefer_kernel_less(impl == "moodist_ce")
                 torch.manual_seed(rank)
                 x = (torch.rand(n, device=dev) * 2 - 1).to(dt)
                 big = (torch.rand(world * n, device=dev) * 2 - 1).to(dt) if world * nbytes <= (8 << 30) else None

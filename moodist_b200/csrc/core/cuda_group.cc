@@ -64,7 +64,12 @@ class CudaGroupImpl final : public CudaGroup {
     // From this shard size up the all-gather pushes again (in two pipelined halves per CTA): posted writes
     // fill NVLink better than read round trips, and the receiver's copy out of staging hides under the
     // arrival of the second half. -1: large shards are pulled.
-    push_large_ = env_long("MOODIST_AG_PUSH_LARGE_BYTES", 4 << 20);
+    push_large_ = env_long("MOODIST_AG_PUSH_LARGE_BYTES", 32 << 20);
+    // Copy-engine variant (DMA copies between one-warp flag kernels): taken from this many bytes per rank up
+    // when the group prefers kernel-less transfers, always when it is forced, and on its own from
+    // MOODIST_CE_AUTO_BYTES up (-1: never on its own).
+    ce_min_ = env_long("MOODIST_CE_MIN_BYTES", 1 << 20);
+    ce_auto_ = env_long("MOODIST_CE_AUTO_BYTES", -1);
     // smallest message (bytes) for which the NVLS variant is picked automatically; -1 = never
     nvls_ar_min_ = env_long("MOODIST_NVLS_AR_MIN_BYTES", 2 << 20);
     nvls_rs_min_ = env_long("MOODIST_NVLS_RS_MIN_BYTES", -1);
@@ -166,11 +171,78 @@ class CudaGroupImpl final : public CudaGroup {
     if (rc != MB_OK) fail(strf("moodist: %s: %s", what, rc_name(rc)));
   }
 
+  bool want_ce(size_t bytes) const {
+    if (world_ == 1 || !attached_ || opts_.method == 0 || opts_.method == 1) return false;
+    if (opts_.force_kernel_less == 1 || opts_.method == 2) return true;
+    if (opts_.prefer_kernel_less && bytes >= (size_t)ce_min_) return true;
+    return ce_auto_ >= 0 && bytes >= (size_t)ce_auto_;
+  }
+  uint8_t* stage_half(int r, uint32_t seq) const {
+    return (uint8_t*)comm_.stage[r] + (uint64_t)(seq & 1) * (comm_.staging_bytes / 2);
+  }
+
+  // All-gather with DMA copies: stage the shard, exchange "ready", pull every peer's staged shard straight into
+  // place. At step i every rank reads from rank+i, so each source serves one reader at a time.
+  void all_gather_ce(const uint8_t* in, uint8_t* out, size_t count, size_t esz, CUstream_st* s) {
+    const size_t half = comm_.staging_bytes / 2;
+    const size_t piece = std::min(count, (half / esz) & ~(size_t)63);
+    cudaStream_t cs = (cudaStream_t)s;
+    for (size_t done = 0; done < count; done += piece) {
+      const size_t n = std::min(piece, count - done);
+      uint32_t seq = next_seq(s);
+      run(mb_ce_phase(&comm_, seq, 0, s), "all_gather (copy engine)");
+      RT_CHECK(cudaMemcpyAsync(stage_half(rank_, seq), in + done * esz, n * esz, cudaMemcpyDeviceToDevice, cs));
+      run(mb_ce_phase(&comm_, seq, 1, s), "all_gather (copy engine)");
+      uint8_t* own = out + ((size_t)rank_ * count + done) * esz;
+      if (own != in + done * esz)
+        RT_CHECK(cudaMemcpyAsync(own, in + done * esz, n * esz, cudaMemcpyDeviceToDevice, cs));
+      for (int i = 1; i < world_; ++i) {
+        int p = (rank_ + i) % world_;
+        RT_CHECK(cudaMemcpyAsync(out + ((size_t)p * count + done) * esz, stage_half(p, seq), n * esz,
+                                 cudaMemcpyDeviceToDevice, cs));
+      }
+      run(mb_ce_phase(&comm_, seq, 2, s), "all_gather (copy engine)");
+      finish_op(s);
+      ce_copies_ += (uint64_t)world_ + 1;
+    }
+  }
+
+  // Reduce-scatter with DMA copies: push this rank's slice for owner p into slot [rank] of p's staging half,
+  // exchange "ready", then one local kernel reduces the world inputs (fp32 accumulate, scale, cast).
+  void reduce_scatter_ce(const uint8_t* in, uint8_t* out, size_t count, int idt, int odt, int op, float premul,
+                         CUstream_st* s) {
+    const size_t isz = mb_dtype_size(idt), osz = mb_dtype_size(odt);
+    const size_t half = comm_.staging_bytes / 2;
+    const size_t piece = std::min(count, (half / (isz * (size_t)world_)) & ~(size_t)63);
+    cudaStream_t cs = (cudaStream_t)s;
+    for (size_t done = 0; done < count; done += piece) {
+      const size_t n = std::min(piece, count - done);
+      uint32_t seq = next_seq(s);
+      run(mb_ce_phase(&comm_, seq, 0, s), "reduce_scatter (copy engine)");
+      for (int i = 1; i < world_; ++i) {
+        int p = (rank_ + i) % world_;
+        RT_CHECK(cudaMemcpyAsync(stage_half(p, seq) + (size_t)rank_ * n * isz, in + ((size_t)p * count + done) * isz,
+                                 n * isz, cudaMemcpyDeviceToDevice, cs));
+      }
+      run(mb_ce_phase(&comm_, seq, 1, s), "reduce_scatter (copy engine)");
+      run(mb_reduce_local(&comm_, seq, in + ((size_t)rank_ * count + done) * isz, out + done * osz, n, idt, odt, op,
+                          premul, s),
+          "reduce_scatter (copy engine)");
+      run(mb_ce_phase(&comm_, seq, 2, s), "reduce_scatter (copy engine)");
+      finish_op(s);
+      ce_copies_ += (uint64_t)world_ - 1;
+    }
+  }
+
   void all_gather(const void* in, void* out, size_t count, int idt, int odt, CUstream_st* s) override {
     std::lock_guard<std::mutex> lk(mu_);
     size_t osz = mb_dtype_size(odt), isz = mb_dtype_size(idt);
     if (!osz || !isz) fail("moodist: all_gather: unsupported dtype");
     if (count == 0) return;
+    if (idt == odt && want_ce(count * isz)) {
+      all_gather_ce((const uint8_t*)in, (uint8_t*)out, count, isz, s);
+      return;
+    }
     int64_t off = idt == odt ? heap_off(in, count * isz) : -1;
     if (idt == odt && off < 0 && world_ > 1 && want_nvls(nvls_ag_min_, count * isz) &&
         (opts_.method == 1 || nvls_ag_max_ < 0 || count * isz <= (size_t)nvls_ag_max_) &&
@@ -205,6 +277,12 @@ class CudaGroupImpl final : public CudaGroup {
     size_t osz = mb_dtype_size(odt), isz = mb_dtype_size(idt);
     if (!osz || !isz) fail("moodist: reduce_scatter: unsupported dtype");
     if (count == 0) return;
+    const bool ce_types = (idt == odt && (idt == MB_F32 || idt == MB_BF16 || idt == MB_F16)) ||
+                          (idt == MB_BF16 && odt == MB_F32) || (idt == MB_F32 && odt == MB_BF16);
+    if (ce_types && want_ce(count * isz)) {
+      reduce_scatter_ce((const uint8_t*)in, (uint8_t*)out, count, idt, odt, op, premul, s);
+      return;
+    }
     int64_t off = heap_off(in, count * isz * world_);
     size_t half = comm_.staging_bytes / 2;
     size_t piece = count;
@@ -281,9 +359,10 @@ class CudaGroupImpl final : public CudaGroup {
       tab.send_bytes[r] = send_bytes[r];
       tab.recv_off[r] = recv_off[r];
       tab.recv_bytes[r] = recv_bytes[r];
-      total = std::max<size_t>(total, send_off[r] + send_bytes[r]);
+      total = std::max<size_t>(total, recv_off[r] + recv_bytes[r]);
     }
-    int64_t off = heap_off(in, total);
+    // senders write straight into the output when it lives in the symmetric heap, else into staging
+    int64_t off = heap_off(out, total);
     uint32_t seq = next_seq(s);
     run(mb_all_to_all(&comm_, seq, in, off, out, &tab, s), "all_to_all");
     finish_op(s);
@@ -316,6 +395,8 @@ class CudaGroupImpl final : public CudaGroup {
   uint32_t seq_ = 0;
   size_t push_bytes_ = 0;
   long push_large_ = -1;
+  long ce_min_ = 1 << 20, ce_auto_ = -1;
+  uint64_t ce_copies_ = 0;
   long nvls_ar_min_ = -1, nvls_rs_min_ = -1, nvls_ag_min_ = -1, nvls_ag_max_ = -1;
   uint64_t launches_ = 0;
   void* scratch_ = nullptr;

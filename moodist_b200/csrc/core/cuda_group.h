@@ -25,7 +25,7 @@ struct GroupOptions {
   int force_kernel_less = 0;
   int num_chunks = -1;
   int chunk_size = -1;
-  int method = -1;  // -1 auto, 0 P2P kernels, 1 NVLS kernels
+  int method = -1;  // -1 auto, 0 P2P kernels, 1 NVLS kernels, 2 copy engine (DMA copies between flag kernels)
 };
 
 struct OpCounters {

@@ -341,33 +341,33 @@ __global__ void __launch_bounds__(kThreads, 1)
 // ---------------------------------------------------------------------------------------------
 // all-to-all with per-peer byte counts
 // ---------------------------------------------------------------------------------------------
+// Push protocol, addressed by the receiver: every rank tells each peer where that peer's segment has to land
+// (inside its symmetric heap when the output tensor lives there, else inside its staging half, laid out like
+// the output); senders write their segments straight from the input over NVLink (posted writes, no staging
+// on the sending side) in two halves; the last CTA of a sender's grid to finish a half raises one flag per
+// peer, so the two sides need not agree on a grid size; receivers copy each half out of staging while the
+// next one is arriving (nothing to copy when the output is in the heap).
+__device__ __forceinline__ size_t a2a_first_half(size_t bytes) {
+  if (bytes < (1u << 20)) return bytes;
+  return (bytes / 2) & ~(size_t)255;
+}
 __global__ void __launch_bounds__(kThreads, 1)
-    all_to_all_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, int64_t in_heap_off,
+    all_to_all_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, int64_t out_heap_off,
                       void* out, const __grid_constant__ mb_a2a_table_t tab) {
   const int b = blockIdx.x, G = gridDim.x;
-  const bool direct = in_heap_off >= 0;
+  const bool out_direct = out_heap_off >= 0;
   entry_wait(c, seq);
   const uint8_t* x = reinterpret_cast<const uint8_t*>(in);
   uint8_t* y = reinterpret_cast<uint8_t*>(out);
   size_t begin, len;
-  if (!direct) {
-    // stage every outgoing segment at the same offset it has in the input
-    for (int i = 1; i < c.world; ++i) {
-      int p = (c.rank + i) % c.world;
-      slice_of(tab.send_bytes[p], G, b, begin, len);
-      cta_copy(stage_ptr(c, c.rank, seq) + tab.send_off[p] + begin, x + tab.send_off[p] + begin, len);
-    }
-    signal_ready(c, seq, b, 0, -1);
-  }
   if (b == 0) {
-    // tell each peer where its segment starts (staging-relative, or heap-relative in direct mode)
     int t = threadIdx.x;
     if (t < c.world && t != c.rank) {
-      uint64_t off = direct ? (uint64_t)in_heap_off + tab.send_off[t] : tab.send_off[t];
+      uint64_t off = out_direct ? (uint64_t)out_heap_off + tab.recv_off[t] : tab.recv_off[t];
       uint32_t* a = c.flags[t] + F_ANN + ((seq & 1) * MB_MAX_RANKS + c.rank) * 4;
       a[0] = (uint32_t)off;
       a[1] = (uint32_t)(off >> 32);
-      a[2] = direct ? 1u : 0u;
+      a[2] = out_direct ? 1u : 0u;
       __threadfence_system();
       st_release_sys(a + 3, seq);
     }
@@ -375,22 +375,76 @@ __global__ void __launch_bounds__(kThreads, 1)
   // own segment
   slice_of(tab.recv_bytes[c.rank], G, b, begin, len);
   cta_copy(y + tab.recv_off[c.rank] + begin, x + tab.send_off[c.rank] + begin, len);
-  for (int i = 1; i < c.world; ++i) {
-    int p = (c.rank + i) % c.world;
-    uint64_t off;
-    uint32_t pdirect;
-    bool ok = wait_announce_warp(c, seq, p, off, pdirect);
-    const uint8_t* src;
-    if (!pdirect) {
-      ok = wait_ready_warp(c, seq, p, b, 0) && ok;
-      src = stage_ptr(c, p, seq) + off;
-    } else {
-      src = reinterpret_cast<const uint8_t*>(c.peer[p]) + off;
+  // where each peer wants its segment
+  const PeerInfo dst = [&] {
+    const int lane = threadIdx.x & 31;
+    PeerInfo r{1u, 0u, 0u, 0u};
+    if (lane < c.world && lane != c.rank) {
+      uint64_t off;
+      uint32_t aux;
+      r.ok = wait_announce(c, seq, lane, off, aux);
+      r.lo = (uint32_t)off;
+      r.hi = (uint32_t)(off >> 32);
+      r.mode = aux;
     }
-    slice_of(tab.recv_bytes[p], G, b, begin, len);
-    if (ok) cta_copy(y + tab.recv_off[p] + begin, src + begin, len);
+    __syncwarp();
+    return r;
+  }();
+  __shared__ uint32_t s_last;
+  for (int h = 0; h < 2; ++h) {
+    for (int i = 1; i < c.world; ++i) {
+      int p = (c.rank + i) % c.world;
+      const size_t h0 = a2a_first_half(tab.send_bytes[p]);
+      const size_t hb = h ? h0 : 0, hl = h ? tab.send_bytes[p] - h0 : h0;
+      const bool ok = __shfl_sync(0xffffffffu, dst.ok, p) != 0;
+      const uint32_t pdirect = __shfl_sync(0xffffffffu, dst.mode, p);
+      const uint64_t off = (uint64_t)__shfl_sync(0xffffffffu, dst.lo, p) | ((uint64_t)__shfl_sync(0xffffffffu, dst.hi, p) << 32);
+      uint8_t* d = (pdirect ? reinterpret_cast<uint8_t*>(c.peer[p]) : stage_ptr(c, p, seq)) + off;
+      slice_of(hl, G, b, begin, len);
+      if (ok && len) cta_copy(d + hb + begin, x + tab.send_off[p] + hb + begin, len);
+    }
+    // the last CTA of this grid to get here tells every peer that half h of its segment is complete
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      uint32_t* cnt = c.flags[c.rank] + F_LOCAL + 2 + h;
+      uint32_t old = atom_add_acqrel_gpu(cnt, 1u);
+      s_last = (old == (uint32_t)G - 1);
+      if (s_last) *cnt = 0;
+    }
+    __syncthreads();
+    if (s_last) {
+      int t = threadIdx.x;
+      if (t < c.world && t != c.rank) {
+        __threadfence_system();
+        st_release_sys(c.flags[t] + (h ? F_READY2 : F_READY) + c.rank * kMaxCtas, seq);
+      }
+    }
+    __syncthreads();
   }
-  exit_done(c, seq, direct);
+  // receive side
+  for (int h = 0; h < 2; ++h) {
+    uint32_t okl = 1;
+    {
+      const int lane = threadIdx.x & 31;
+      if (lane < c.world && lane != c.rank) {
+        okl = wait_geq_sys(c.flags[c.rank] + (h ? F_READY2 : F_READY) + lane * kMaxCtas, seq, c.wait_ns);
+        if (!okl) fail(c, kTimeoutReady, lane);
+      }
+      __syncwarp();
+    }
+    if (out_direct) continue;  // the segments were written in place
+    for (int i = 1; i < c.world; ++i) {
+      int p = (c.rank - i + c.world) % c.world;
+      const bool ok = __shfl_sync(0xffffffffu, okl, p) != 0;
+      const size_t h0 = a2a_first_half(tab.recv_bytes[p]);
+      const size_t hb = h ? h0 : 0, hl = h ? tab.recv_bytes[p] - h0 : h0;
+      slice_of(hl, G, b, begin, len);
+      if (ok && len)
+        cta_copy(y + tab.recv_off[p] + hb + begin, stage_ptr(c, c.rank, seq) + tab.recv_off[p] + hb + begin, len);
+    }
+  }
+  exit_done(c, seq, false);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -614,6 +668,88 @@ bool op_scale(int op, int world, float premul, float* scale, int* use_scale) {
 }
 }  // namespace
 
+// ---------------------------------------------------------------------------------------------
+// copy-engine ("kernel-less") variants: the bytes move with stream-ordered DMA copies issued by the host,
+// these one-warp kernels only run the flag protocol around them, and the reduce-scatter adds one local
+// reduction. No SM time is spent on the transfer itself, so a GEMM running next to it keeps its SMs.
+// (The reference's counterpart orders cuMemcpy2DAsync copies with IPC events, core/processgroup.cc.)
+// ---------------------------------------------------------------------------------------------
+namespace {
+__global__ void __launch_bounds__(32, 1) ce_begin_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq) {
+  entry_wait(c, seq);  // every rank has finished the op two steps back: this staging half is free everywhere
+}
+// this rank's bytes for the op are in place (its own staging half, or its slots in the peers' halves):
+// tell every peer and wait until every peer has said the same
+__global__ void __launch_bounds__(32, 1) ce_ready_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq) {
+  announce(c, seq, 0, 0u);
+  signal_ready(c, seq, 0, 0, -1);
+  (void)wait_peers_warp(c, seq, 0, 0);
+}
+__global__ void __launch_bounds__(32, 1) ce_end_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq) {
+  exit_done(c, seq, false);
+}
+// out[0..count) = op over `nsrc` local buffers (this rank's own slice and the staged slices of the peers)
+template <typename InT, typename OutT, int kOp>
+__global__ void __launch_bounds__(kThreads, 1)
+    reduce_local_kernel(const InT* s0, const InT* staged, size_t slot_stride, int rank, int world, OutT* out,
+                        size_t count, float scale, int use_scale) {
+  size_t begin, len;
+  slice_of(count, gridDim.x, blockIdx.x, begin, len);
+  const InT* srcs[MB_MAX_RANKS];
+  srcs[0] = s0 + begin;
+  int n = 1;
+  for (int p = 0; p < world; ++p)
+    if (p != rank) srcs[n++] = staged + (size_t)p * slot_stride + begin;
+  cta_reduce<InT, OutT, kOp>(out + begin, srcs, world, len, scale, use_scale);
+}
+template <typename InT, typename OutT>
+int launch_reduce_local(const void* s0, const void* staged, size_t slot_stride, int rank, int world, void* out,
+                        size_t count, int op, float scale, int use_scale, int grid, cudaStream_t s) {
+  auto a = reinterpret_cast<const InT*>(s0);
+  auto b = reinterpret_cast<const InT*>(staged);
+  auto o = reinterpret_cast<OutT*>(out);
+  switch (op) {
+    case MB_MIN: reduce_local_kernel<InT, OutT, MB_MIN><<<grid, kThreads, 0, s>>>(a, b, slot_stride, rank, world, o, count, 1.f, 0); break;
+    case MB_MAX: reduce_local_kernel<InT, OutT, MB_MAX><<<grid, kThreads, 0, s>>>(a, b, slot_stride, rank, world, o, count, 1.f, 0); break;
+    default: reduce_local_kernel<InT, OutT, MB_SUM><<<grid, kThreads, 0, s>>>(a, b, slot_stride, rank, world, o, count, scale, use_scale);
+  }
+  return check_launch();
+}
+}  // namespace
+
+extern "C" int mb_ce_phase(const mb_comm_t* c, uint32_t seq, int phase, void* stream) {
+  cudaStream_t s = MB_STREAM(stream);
+  switch (phase) {
+    case 0: ce_begin_kernel<<<1, 32, 0, s>>>(*c, seq); break;
+    case 1: ce_ready_kernel<<<1, 32, 0, s>>>(*c, seq); break;
+    case 2: ce_end_kernel<<<1, 32, 0, s>>>(*c, seq); break;
+    default: return MB_ERR_ARG;
+  }
+  return check_launch();
+}
+
+extern "C" int mb_reduce_local(const mb_comm_t* c, uint32_t seq, const void* own, void* out, size_t count,
+                               int in_dtype, int out_dtype, int op, float premul, void* stream) {
+  float scale;
+  int use_scale;
+  if (!op_scale(op, c->world, premul, &scale, &use_scale)) return MB_ERR_ARG;
+  size_t isz = dtype_size(in_dtype);
+  if (!isz) return MB_ERR_ARG;
+  const void* staged = reinterpret_cast<const uint8_t*>(c->stage[c->rank]) + (uint64_t)(seq & 1) * (c->staging_bytes >> 1);
+  int grid = pick_grid(c, count * isz, 64);
+  cudaStream_t s = MB_STREAM(stream);
+#define RL(IDT, ODT, IT, OT) \
+  if (in_dtype == IDT && out_dtype == ODT) \
+    return launch_reduce_local<IT, OT>(own, staged, count, c->rank, c->world, out, count, op, scale, use_scale, grid, s);
+  RL(MB_F32, MB_F32, float, float)
+  RL(MB_BF16, MB_BF16, __nv_bfloat16, __nv_bfloat16)
+  RL(MB_BF16, MB_F32, __nv_bfloat16, float)
+  RL(MB_F32, MB_BF16, float, __nv_bfloat16)
+  RL(MB_F16, MB_F16, __half, __half)
+#undef RL
+  return MB_ERR_ARG;
+}
+
 extern "C" int mb_reduce_scatter(const mb_comm_t* c, uint32_t seq, const void* in, int64_t in_heap_off, void* out,
                                  size_t count, size_t in_stride, int in_dtype, int out_dtype, int op, float premul,
                                  void* stream) {
@@ -680,22 +816,24 @@ extern "C" int mb_broadcast(const mb_comm_t* c, uint32_t seq, void* data, int64_
   return check_launch();
 }
 
-extern "C" int mb_all_to_all(const mb_comm_t* c, uint32_t seq, const void* in, int64_t in_heap_off, void* out,
+extern "C" int mb_all_to_all(const mb_comm_t* c, uint32_t seq, const void* in, int64_t out_heap_off, void* out,
                              const mb_a2a_table_t* tab, void* stream) {
   size_t total = 0, biggest = 0;
   for (int r = 0; r < c->world; ++r) {
-    size_t end = tab->send_off[r] + tab->send_bytes[r];
+    size_t end = tab->recv_off[r] + tab->recv_bytes[r];
     if (end > total) total = end;
     if (tab->recv_bytes[r] > biggest) biggest = tab->recv_bytes[r];
+    if (tab->send_bytes[r] > biggest) biggest = tab->send_bytes[r];
   }
   if (c->world == 1) {
     if (tab->send_bytes[0] == 0) return MB_OK;
     return mb_copy_cast((const uint8_t*)in + tab->send_off[0], (uint8_t*)out + tab->recv_off[0], tab->send_bytes[0],
                         MB_U8, MB_U8, 1.f, 0, stream);
   }
-  if (in_heap_off < 0 && total > c->staging_bytes / 2) return MB_ERR_TOO_BIG;
-  int grid = pick_grid(c, biggest);
-  all_to_all_kernel<<<grid, kThreads, 0, MB_STREAM(stream)>>>(*c, seq, in, in_heap_off, out, *tab);
+  // incoming segments are laid out in the staging half like in the output tensor
+  if (out_heap_off < 0 && total > c->staging_bytes / 2) return MB_ERR_TOO_BIG;
+  int grid = pick_grid(c, biggest);  // ranks may pick different grids: nothing in the protocol depends on it
+  all_to_all_kernel<<<grid, kThreads, 0, MB_STREAM(stream)>>>(*c, seq, in, out_heap_off, out, *tab);
   return check_launch();
 }
 

@@ -105,7 +105,9 @@ typedef struct {
   uint64_t recv_off[MB_MAX_RANKS];
   uint64_t recv_bytes[MB_MAX_RANKS];
 } mb_a2a_table_t;
-int mb_all_to_all(const mb_comm_t* c, uint32_t seq, const void* in, int64_t in_heap_off, void* out,
+// out_heap_off: byte offset of `out` inside this rank's symmetric heap (peers then write into it directly),
+// or -1: incoming segments pass through this rank's staging half.
+int mb_all_to_all(const mb_comm_t* c, uint32_t seq, const void* in, int64_t out_heap_off, void* out,
                   const mb_a2a_table_t* table, void* stream);
 
 // compile_op lowering. Every rank first stages its inputs (stage_in: local tensor -> offset in its
@@ -129,6 +131,15 @@ typedef struct {
 // stage_in / pieces are DEVICE arrays.
 int mb_gather_scatter(const mb_comm_t* c, uint32_t seq, const mb_stage_copy_t* stage_in, int num_stage,
                       const mb_piece_t* pieces, int num_pieces, size_t max_bytes, void* stream);
+
+// --- copy-engine variants: the host moves the bytes with stream-ordered DMA copies between these phases ----
+// phase 0: wait until this op's staging half is free on every rank; 1: publish "my bytes are in place" and
+// wait for every peer's; 2: publish "I am done reading" (what phase 0 of the op after next waits for).
+int mb_ce_phase(const mb_comm_t* c, uint32_t seq, int phase, void* stream);
+// out[0..count) = op(own[0..count), the world-1 peer slots of this rank's staging half for `seq`), slot p at
+// element offset p*count; fp32 accumulation, AVG / PREMUL_SUM scale and dtype conversion as in mb_reduce_scatter.
+int mb_reduce_local(const mb_comm_t* c, uint32_t seq, const void* own, void* out, size_t count, int in_dtype,
+                    int out_dtype, int op, float premul, void* stream);
 
 // --- NVLS variants (collectives_nvls.cu); need the multicast alias (mb_nvls_available) ------------------
 int mb_nvls_available(const mb_comm_t* c);

@@ -53,6 +53,26 @@ def _cuda_collectives(rank, world, port):
     dist.all_to_all_single(out, inp, [int(x) for x in splits[:, rank]], [int(x) for x in splits[rank]])
     ref = torch.cat([torch.full((int(splits[s, rank]), H), s * 100 + rank, dtype=torch.bfloat16) for s in range(world)])
     assert torch.equal(out.cpu(), ref)
+    # very uneven splits (the ranks end up with different grid sizes, segments above the two-half threshold
+    # next to empty ones), the output once in ordinary memory and once in the symmetric heap
+    from moodist_b200.allocator import symmetric_mem_pool
+
+    pool = symmetric_mem_pool()
+    for it, rows in enumerate([[0, 3, 40000, 1], [70000, 0, 5, 12345], [17, 17, 17, 17]]):
+        sp = torch.zeros(world, world, dtype=torch.long)
+        for s_ in range(world):
+            for d in range(world):
+                sp[s_, d] = rows[(s_ * world + d + it) % len(rows)]
+        inp = torch.cat([torch.full((int(sp[rank, d]), H), rank * 10 + d, dtype=torch.bfloat16) for d in range(world)]).to(dev)
+        ref = torch.cat([torch.full((int(sp[s_, rank]), H), s_ * 10 + rank, dtype=torch.bfloat16) for s_ in range(world)])
+        for symmetric in (False, True):
+            if symmetric:
+                with torch.cuda.use_mem_pool(pool):
+                    out = torch.zeros(int(sp[:, rank].sum()), H, dtype=torch.bfloat16, device=dev)
+            else:
+                out = torch.zeros(int(sp[:, rank].sum()), H, dtype=torch.bfloat16, device=dev)
+            dist.all_to_all_single(out, inp, [int(x) for x in sp[:, rank]], [int(x) for x in sp[rank]])
+            assert torch.equal(out.cpu(), ref), ("uneven all_to_all", it, symmetric)
     dist.barrier()
     import moodist_b200
 
@@ -103,6 +123,51 @@ def _nvls_variants(rank, world, port):
 
 def test_nvls_variants_2gpu():
     run_ranks(_nvls_variants, 2, timeout=240, env={"MOODIST_DEVICE_TIMEOUT_MS": 5000})
+
+
+def _copy_engine_variants(rank, world, port):
+    """The copy-engine variants (DMA copies between one-warp flag kernels) against the seeded oracle, mixed
+    with kernel collectives so that sequence numbers and staging halves interleave."""
+    dist = init_moodist(rank, world, port, device="cuda")
+    import moodist_b200
+
+    dev = torch.device("cuda", rank)
+    pg = moodist_b200.get_backend()
+    for it, (dtype, n) in enumerate([(torch.bfloat16, 1 << 20), (torch.float32, 300_000), (torch.bfloat16, 1 << 23),
+                                     (torch.float16, 65536 + 8)]):
+        pg.set_prefer_kernel_less(it % 2 == 0)
+        pg._set_option("method", 2 if it % 2 else -1)  # odd rounds force the copy engine through `method`
+        g = torch.Generator().manual_seed(77 + it)
+        full = (torch.rand(world, n, generator=g) * 2 - 1).to(dtype)
+        ag = torch.empty(world * n, device=dev, dtype=dtype)
+        dist.all_gather_into_tensor(ag, full[rank].to(dev).contiguous())
+        assert torch.equal(ag.cpu().view(world, n), full), ("ce all_gather", dtype, n)
+        # in place: the input is the rank's slice of the output
+        ag2 = torch.zeros(world * n, device=dev, dtype=dtype)
+        ag2.view(world, n)[rank].copy_(full[rank])
+        dist.all_gather_into_tensor(ag2, ag2.view(world, n)[rank])
+        assert torch.equal(ag2.cpu().view(world, n), full), ("ce all_gather in place", dtype, n)
+        allin = (torch.rand(world, world, n, generator=g) * 2 - 1).to(dtype)
+        out = torch.empty(n, device=dev, dtype=dtype)
+        dist.reduce_scatter_tensor(out, allin[rank].reshape(-1).to(dev), op=dist.ReduceOp.AVG)
+        ref = allin[:, rank].float().mean(0)
+        torch.testing.assert_close(out.float().cpu(), ref, rtol=2e-2, atol=2e-2)
+        if dtype == torch.bfloat16:
+            out32 = torch.empty(n, device=dev, dtype=torch.float32)
+            pg.reduce_scatter_cast(out32, allin[rank].reshape(-1).to(dev), int(dist.ReduceOp.SUM), 1.0)
+            torch.testing.assert_close(out32.cpu(), allin[:, rank].float().sum(0), rtol=1e-5, atol=1e-5)
+        pg._set_option("method", -1)
+        pg.set_prefer_kernel_less(False)
+        t = torch.ones(4096, device=dev)
+        dist.all_reduce(t)  # a kernel collective in between
+        assert bool((t == world).all())
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_copy_engine_variants_2gpu():
+    run_ranks(_copy_engine_variants, 2, timeout=240, env={"MOODIST_DEVICE_TIMEOUT_MS": 5000})
 
 
 def _absent_rank(rank, world, port):
