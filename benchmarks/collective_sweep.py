@@ -7,8 +7,9 @@ GPUs. Device-timed (CUDA events), max over ranks, 20 warm-up + 100 timed iterati
 
 ``--impls`` may also name ``moodist_sym``: the same kernels on buffers allocated from the symmetric heap
 (``moodist_b200.allocator.symmetric_pool``, what ``enable_cuda_allocator()`` gives every tensor), which peers
-read in place instead of through the staging area, and ``moodist_ce``: the copy-engine variant
-(``set_prefer_kernel_less(True)``), which spends no SM time on the transfer.
+read in place instead of through the staging area, and the forced kernel families ``moodist_p2p`` (peer
+loads / stores), ``moodist_nvls`` (multimem through NVSwitch) and ``moodist_ce`` (DMA copies between
+one-warp flag kernels, no SM time spent on the transfer); ``moodist`` is the library's own choice.
 
 Bus bandwidth follows the usual convention: AG / RS move (n-1)/n of the gathered buffer per GPU, AR twice that.
 """
@@ -59,7 +60,9 @@ def main():
     torch.cuda.set_device(lr)
     dev = torch.device("cuda", lr)
     dist.init_process_group("moodist", rank=rank, world_size=world)
-    groups = {"moodist": dist.group.WORLD, "moodist_sym": dist.group.WORLD, "moodist_ce": dist.group.WORLD}
+    groups = {k: dist.group.WORLD for k in ("moodist", "moodist_sym", "moodist_ce", "moodist_p2p", "moodist_nvls")}
+    # forced kernel families, for the variant table (moodist_b200.utils.tuning): -1 lets the library choose
+    methods = {"moodist_p2p": 0, "moodist_nvls": 1, "moodist_ce": 2}
     backend = moodist_b200.get_backend()
     sym_pool = None
     if "moodist_sym" in args.impls.split(","):
@@ -84,8 +87,8 @@ def main():
             warm = args.warmup if nbytes <= (64 << 20) else 5
             for impl in args.impls.split(","):
                 g = groups[impl]
-                # moodist_ce: the copy-engine variant (DMA copies between one-warp flag kernels) from 1 MiB per rank up
-                backend.set_prefer_kernel_less(impl == "moodist_ce")
+                if impl.startswith("moodist"):
+                    backend._set_option("method", methods.get(impl, -1))
                 torch.manual_seed(rank)
                 x = (torch.rand(n, device=dev) * 2 - 1).to(dt)
                 big = (torch.rand(world * n, device=dev) * 2 - 1).to(dt) if world * nbytes <= (8 << 30) else None

@@ -10,6 +10,8 @@
 #include "kernels/kernels_api.h"
 #include "log.h"
 #include "symm_heap.h"
+#include "topology.h"
+#include "wire.h"
 
 namespace moodist {
 namespace {
@@ -83,6 +85,7 @@ class CudaGroupImpl final : public CudaGroup {
     comm_.status = (uint32_t*)dptr;
     // MOODIST_FORCE_STAGING=1 gives a one-rank group its staging area too, so the fused kernels can be run
     // (and profiled) on a single GPU
+    if (world > 1) check_topology(store, key, rank, world, device);
     if (world > 1 || env_flag("MOODIST_FORCE_STAGING")) {
       size_t staging = (size_t)env_long("MOODIST_STAGING_MB", 1024) << 20;
       heap_ = &SymmHeap::instance(device);
@@ -111,9 +114,55 @@ class CudaGroupImpl final : public CudaGroup {
     if (status_host_) cudaFreeHost((void*)status_host_);
   }
 
+  // Every rank publishes which machine and which physical GPU it runs on; a group whose ranks cannot address
+  // each other's memory (several machines, two ranks on one GPU, a pair without peer access) is refused here
+  // with the reason, before any memory is exchanged.
+  void check_topology(KVStore& store, const std::string& key, int rank, int world, int device) {
+    char pci[32] = {0};
+    if (cudaDeviceGetPCIBusId(pci, sizeof(pci), device) != cudaSuccess) pci[0] = 0;
+    const NodeTopology& local = local_topology();
+    store.set(key + "/topo/" + std::to_string(rank), encode(local.node_id, std::string(pci)));
+    std::vector<std::string> nodes(world), pcis(world);
+    for (int r = 0; r < world; ++r) {
+      std::vector<uint8_t> v = store.get(key + "/topo/" + std::to_string(r));
+      decode_exact(v, nodes[r], pcis[r]);
+    }
+    // physical index of each rank's GPU in this machine's table (ranks elsewhere: -1)
+    std::vector<int> devs(world, -1);
+    for (int r = 0; r < world; ++r) {
+      if (nodes[r] != nodes[rank]) continue;
+      std::string want = pcis[r];
+      for (auto& ch : want) ch = (char)tolower((unsigned char)ch);
+      bool found = false;
+      for (auto& g : local.gpus) {
+        // CUDA prints a 4-digit PCI domain, NVML an 8-digit one
+        if (!want.empty() && g.pci_bus_id.size() >= want.size() &&
+            g.pci_bus_id.compare(g.pci_bus_id.size() - want.size(), want.size(), want) == 0) {
+          devs[r] = g.index;
+          found = true;
+        }
+      }
+      if (!found) {
+        // no NVML table: still tell two ranks on one GPU apart by bus id
+        for (int q = 0; q < r; ++q)
+          if (nodes[q] == nodes[r] && pcis[q] == pcis[r] && !pcis[r].empty())
+            fail(strf("moodist: ranks %d and %d both use the GPU at %s; every rank of a CUDA group needs its own GPU",
+                      q, r, pcis[r].c_str()));
+        devs[r] = 1000 + r;  // distinct placeholder outside the table
+      }
+    }
+    GroupTopology g = make_group_topology(rank, nodes, devs, local);
+    if (!g.kernels_usable) fail("moodist: CUDA group cannot be formed: " + g.why_not);
+    numa_node_ = -1;
+    for (auto& gi : local.gpus)
+      if (gi.index == devs[rank]) numa_node_ = gi.numa_node;
+    if (numa_node_ < 0 && pci[0]) numa_node_ = numa_node_of_pci(pci);
+  }
+
   int rank() const override { return rank_; }
   int world() const override { return world_; }
   int device() const override { return device_; }
+  int numa_node() const override { return numa_node_; }
   bool has_nvls() const override { return comm_.mc_stage != nullptr; }
   GroupOptions& options() override { return opts_; }
   const void* comm_struct() const override { return &comm_; }
@@ -396,6 +445,7 @@ class CudaGroupImpl final : public CudaGroup {
   size_t push_bytes_ = 0;
   long push_large_ = -1;
   long ce_min_ = 1 << 20, ce_auto_ = -1;
+  int numa_node_ = -1;
   uint64_t ce_copies_ = 0;
   long nvls_ar_min_ = -1, nvls_rs_min_ = -1, nvls_ag_min_ = -1, nvls_ag_max_ = -1;
   uint64_t launches_ = 0;

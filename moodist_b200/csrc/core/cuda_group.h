@@ -43,6 +43,7 @@ class CudaGroup {
   virtual int world() const = 0;
   virtual int device() const = 0;
   virtual bool has_nvls() const = 0;
+  virtual int numa_node() const = 0;  // memory node of this rank's GPU, -1 when unknown
   virtual GroupOptions& options() = 0;
 
   virtual void all_gather(const void* in, void* out, size_t count, int in_dtype, int out_dtype, CUstream_st* s) = 0;

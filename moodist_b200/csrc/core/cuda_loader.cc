@@ -75,6 +75,7 @@ const NvmlApi& nvml() {
     N(nvmlDeviceGetNvLinkRemotePciInfo_v2)
     N(nvmlDeviceGetNumaNodeId)
     N(nvmlDeviceGetCount_v2)
+    N(nvmlDeviceGetPciInfo_v3)
 #undef N
     if (g_nvml.nvmlInit_v2 && g_nvml.nvmlInit_v2() == 0) g_nvml.loaded = true;
   });

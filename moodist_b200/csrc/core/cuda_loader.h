@@ -85,6 +85,7 @@ struct NvmlApi {
   int (*nvmlDeviceGetNvLinkRemotePciInfo_v2)(void*, unsigned, void*) = nullptr;
   int (*nvmlDeviceGetNumaNodeId)(void*, unsigned*) = nullptr;
   int (*nvmlDeviceGetCount_v2)(unsigned*) = nullptr;
+  int (*nvmlDeviceGetPciInfo_v3)(void*, void*) = nullptr;
   bool loaded = false;
 };
 const NvmlApi& nvml();

@@ -3,6 +3,8 @@
 // mb_cuda_alloc / mb_cuda_free hooks of the core library (moodist_b200/allocator.py); the reference
 // subclasses CUDACachingAllocator::CUDAAllocator instead (wrapper/allocator_wrapper.cc:14-199), an interface
 // that changes between torch releases.
+#include "core/numa.h"
+#include "core/topology.h"
 #include <c10/core/Allocator.h>
 #include <c10/core/CPUAllocator.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -75,6 +77,37 @@ void bind_allocators(pybind11::module_& m, BackendClass& backend) {
   m.def("cpu_allocator_debug", [] { return cpu_allocator_debug(); });
   m.def("cpu_allocator_owns", [](const at::Tensor& t) { return cpu_allocator_owns(t.data_ptr()); });
   m.def("cuda_copy", &cuda_copy, pybind11::arg("dst"), pybind11::arg("src"));
+  // what NVML says about this machine: GPUs, NVLink / PCIe reachability between them, NUMA nodes
+  m.def("topology", [] {
+    const NodeTopology& t = local_topology();
+    pybind11::dict d;
+    d["node_id"] = t.node_id;
+    d["nvswitch"] = t.nvswitch;
+    d["all_p2p"] = t.all_p2p;
+    pybind11::list gpus;
+    for (auto& g : t.gpus) {
+      pybind11::dict e;
+      e["index"] = g.index;
+      e["pci_bus_id"] = g.pci_bus_id;
+      e["numa_node"] = g.numa_node;
+      e["nvlinks_up"] = g.nvlinks_up;
+      e["nvlinks_to_switch"] = g.nvlinks_to_switch;
+      gpus.append(e);
+    }
+    d["gpus"] = gpus;
+    static const char* names[] = {"none", "pcie", "nvlink", "self"};
+    pybind11::list links;
+    for (auto& row : t.link) {
+      pybind11::list r;
+      for (auto k : row) r.append(names[(int)k]);
+      links.append(r);
+    }
+    d["links"] = links;
+    d["text"] = t.describe();
+    return d;
+  });
+  m.def("numa_cpus", [](int node) { return cpus_of_numa_node(node); });
+  m.def("bind_thread_to_numa_node", [](int node) { return bind_thread_to_numa_node(node); });
   // profiling is per group in the engine; the module-level switch applies to every live group
   backend.def("enable_profiling", [](c10::intrusive_ptr<MoodistBackend> self, bool on) {
     pybind11::gil_scoped_release nogil;

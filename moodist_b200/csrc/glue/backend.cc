@@ -1,5 +1,7 @@
 #include "backend.h"
 
+#include "core/numa.h"
+
 #include <ATen/cuda/CUDAEvent.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
@@ -181,6 +183,11 @@ CudaGroup& MoodistBackend::cudaGroup(int device) {
   if (!cuda_) {
     MOODIST_TRANSLATE(cuda_ = CudaGroup::create(*kv_, name_, rank_, size_, device);)
     cuda_->options() = opts_;
+    // the host engine thread (if it exists already) moves next to the GPU's memory node
+    if (host_ && cuda_->numa_node() >= 0) {
+      int node = cuda_->numa_node();
+      host_->run_on_engine([node] { bind_thread_to_numa_node(node); });
+    }
   }
   TORCH_CHECK(cuda_->device() == device, "moodist: this process group is bound to cuda:", cuda_->device(),
               " but got a tensor on cuda:", device);
@@ -191,6 +198,10 @@ HostGroup& MoodistBackend::hostGroup() {
   std::lock_guard<std::mutex> lk(mu_);
   if (!host_) {
     MOODIST_TRANSLATE(host_ = HostGroup::create(*kv_, name_, rank_, size_);)
+    if (cuda_ && cuda_->numa_node() >= 0) {
+      int node = cuda_->numa_node();
+      host_->run_on_engine([node] { bind_thread_to_numa_node(node); });
+    }
   }
   return *host_;
 }

@@ -1,0 +1,133 @@
+"""Variant table from measured bus bandwidth.
+
+The collectives have several kernel families per operation (peer loads/stores, NVLS multimem through
+NVSwitch, copy-engine DMA) and size thresholds between them.  The thresholds compiled into the library were
+measured on one 8 x B200 NVSwitch machine; this module re-derives them from a sweep on the machine at hand:
+
+    torchrun ... benchmarks/collective_sweep.py --impls moodist_p2p,moodist_nvls,moodist_ce,nccl --out sweep.jsonl
+    python -m moodist_b200.utils.tuning sweep.jsonl            # prints the table and the settings
+    eval "$(python -m moodist_b200.utils.tuning sweep.jsonl --export)"   # MOODIST_* variables for the next run
+
+``apply(settings)`` puts the variables into ``os.environ`` (before the process group is created).  The
+reference picks its algorithm per call from fixed rules in ``core/processgroup.cc``; it has no measured table.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import sys
+from collections import defaultdict
+
+FAMILIES = {"moodist_p2p": "p2p", "moodist_nvls": "nvls", "moodist_ce": "ce"}
+
+
+def load_sweep(path: str) -> list[dict]:
+    rows = []
+    with open(path) as f:
+        for line in f:
+            line = line.strip()
+            if line.startswith("{"):
+                rows.append(json.loads(line))
+    return rows
+
+
+def variant_table(rows: list[dict], dtype: str = "bf16") -> dict[str, list[dict]]:
+    """Per operation, per message size: time of every measured family and the fastest one."""
+    by = defaultdict(dict)
+    for r in rows:
+        if r.get("dtype") != dtype or r["impl"] not in FAMILIES:
+            continue
+        by[(r["op"], r["bytes_per_rank"])][FAMILIES[r["impl"]]] = r["us"]
+    table = defaultdict(list)
+    for (op, nbytes), times in sorted(by.items()):
+        best = min(times, key=times.get)
+        table[op].append({"bytes": nbytes, "best": best, "us": times})
+    return dict(table)
+
+
+def _first_size_from_which(entries: list[dict], family: str) -> int:
+    """Smallest size such that `family` is the fastest at it and at every larger measured size (-1: none)."""
+    start = -1
+    for e in entries:
+        if e["best"] == family:
+            if start < 0:
+                start = e["bytes"]
+        else:
+            start = -1
+    return start
+
+
+def _window(entries: list[dict], family: str) -> tuple[int, int]:
+    """Longest run of consecutive sizes at which `family` is fastest, as (first, last) bytes; (-1, -1) if none."""
+    best = (-1, -1)
+    run = None
+    for e in entries + [{"bytes": None, "best": None}]:
+        if e["best"] == family:
+            run = (run[0], e["bytes"]) if run else (e["bytes"], e["bytes"])
+        elif run:
+            if best[0] < 0 or (run[1] / run[0]) > (best[1] / best[0]):
+                best = run
+            run = None
+    return best
+
+
+def settings_from(table: dict[str, list[dict]]) -> dict[str, int]:
+    """MOODIST_* thresholds that reproduce the table's choices."""
+    out: dict[str, int] = {}
+    ag = table.get("ag", [])
+    if ag:
+        lo, hi = _window(ag, "nvls")
+        out["MOODIST_NVLS_AG_MIN_BYTES"] = lo
+        out["MOODIST_NVLS_AG_MAX_BYTES"] = hi if lo >= 0 else -1
+    rs = table.get("rs_sum", table.get("rs_avg", []))
+    if rs:
+        out["MOODIST_NVLS_RS_MIN_BYTES"] = _first_size_from_which(rs, "nvls")
+    ar = table.get("ar", [])
+    if ar:
+        out["MOODIST_NVLS_AR_MIN_BYTES"] = _first_size_from_which(ar, "nvls")
+    # one copy-engine threshold for all operations: the largest of the per-operation ones, so that no
+    # operation is moved to DMA copies below the size where they win
+    ce = [_first_size_from_which(t, "ce") for t in (ag, rs) if t]
+    out["MOODIST_CE_AUTO_BYTES"] = max(ce) if ce and all(c >= 0 for c in ce) else -1
+    return out
+
+
+def apply(settings: dict[str, int]) -> None:
+    """Set the variables for this process; call before ``init_process_group``."""
+    for k, v in settings.items():
+        os.environ[k] = str(int(v))
+
+
+def format_table(table: dict[str, list[dict]]) -> str:
+    lines = []
+    for op, entries in table.items():
+        lines.append(f"{op}:")
+        for e in entries:
+            times = "  ".join(f"{k} {v:9.1f} us" for k, v in sorted(e["us"].items()))
+            lines.append(f"  {e['bytes']:>11}  best {e['best']:<5} {times}")
+    return "\n".join(lines)
+
+
+def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    export = "--export" in argv
+    paths = [a for a in argv if not a.startswith("--")]
+    if len(paths) != 1:
+        print(__doc__)
+        return 2
+    table = variant_table(load_sweep(paths[0]))
+    settings = settings_from(table)
+    if export:
+        for k, v in settings.items():
+            print(f"export {k}={v}")
+    else:
+        print(format_table(table))
+        print()
+        for k, v in settings.items():
+            print(f"{k}={v}")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

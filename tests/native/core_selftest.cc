@@ -12,6 +12,8 @@
 #include "core/cpu_allocator.h"
 #include "core/cpu_reduce.h"
 #include "core/log.h"
+#include "core/numa.h"
+#include "core/topology.h"
 #include "core/setup_comms.h"
 #include "core/store.h"
 #include "core/tcp_transport.h"
@@ -200,8 +202,83 @@ static void test_mesh_and_alloc() {
   CHECK(!cpu_allocator_owns(&onstack));
 }
 
+// A recorded machine instead of NVML: `n` GPUs; with `nvswitch` every GPU has 18 links that end in a switch,
+// otherwise GPUs 0-1 and 2-3 are joined by direct links and the rest only by PCIe; `no_p2p` breaks one pair.
+struct FakeProbe : TopologyProbe {
+  int n;
+  bool nvswitch;
+  int broken_a = -1, broken_b = -1;
+  FakeProbe(int n_, bool sw) : n(n_), nvswitch(sw) {}
+  int device_count() override { return n; }
+  bool pci_bus_id(int d, std::string* out) override {
+    char buf[32];
+    snprintf(buf, sizeof(buf), "00000000:%02X:00.0", 0x1b + d * 0x10);
+    *out = buf;
+    return true;
+  }
+  int numa_node(int d) override { return d < n / 2 ? 0 : 1; }
+  bool link_up(int d, int l) override { return nvswitch ? l < 18 : (d < 4 && l < 4); }
+  bool link_remote(int d, int l, std::string* pci) override {
+    if (nvswitch) {
+      *pci = "00000000:05:00.0";  // a switch, not in the GPU table
+      return true;
+    }
+    (void)l;
+    return pci_bus_id(d ^ 1, pci);
+  }
+  int p2p_ok(int a, int b) override {
+    return !((a == broken_a && b == broken_b) || (a == broken_b && b == broken_a));
+  }
+};
+
+static void test_topology() {
+  FakeProbe sw(8, true);
+  NodeTopology t = discover_topology(sw);
+  CHECK(t.gpus.size() == 8 && t.nvswitch && t.all_p2p);
+  CHECK(t.gpus[3].nvlinks_up == 18 && t.gpus[3].nvlinks_to_switch == 18 && t.gpus[5].numa_node == 1);
+  CHECK(t.gpus[1].pci_bus_id == "00000000:2b:00.0");
+  CHECK(t.link[0][7] == LinkKind::NvLink && t.link[2][2] == LinkKind::Self);
+  NodeTopology back = NodeTopology::decode(t.encode());
+  CHECK(back.describe() == t.describe());
+
+  FakeProbe pcie(6, false);
+  NodeTopology p = discover_topology(pcie);
+  CHECK(!p.nvswitch && p.all_p2p);
+  CHECK(p.link[0][1] == LinkKind::NvLink && p.link[2][3] == LinkKind::NvLink);
+  CHECK(p.link[0][2] == LinkKind::Pcie && p.link[4][5] == LinkKind::Pcie);
+  CHECK(p.gpus[0].nvlinks_up == 4 && p.gpus[0].nvlinks_to_switch == 0 && p.gpus[5].nvlinks_up == 0);
+
+  FakeProbe broken(4, true);
+  broken.broken_a = 1;
+  broken.broken_b = 2;
+  NodeTopology b = discover_topology(broken);
+  CHECK(!b.all_p2p && !b.nvswitch && b.link[1][2] == LinkKind::None && b.link[0][3] == LinkKind::NvLink);
+
+  // groups
+  std::vector<std::string> one(4, t.node_id);
+  GroupTopology g = make_group_topology(2, one, {0, 1, 2, 3}, t);
+  CHECK(g.single_node && g.kernels_usable && g.local_ranks.size() == 4);
+  g = make_group_topology(0, one, {0, 1, 1, 3}, t);
+  CHECK(!g.kernels_usable && g.why_not.find("share GPU 1") != std::string::npos);
+  g = make_group_topology(0, one, {0, 1, 2, 3}, b);
+  CHECK(!g.kernels_usable && g.why_not.find("cannot address") != std::string::npos);
+  std::vector<std::string> two = {t.node_id, t.node_id, "other-machine", "other-machine"};
+  g = make_group_topology(1, two, {0, 1, -1, -1}, t);
+  CHECK(!g.single_node && g.num_nodes == 2 && !g.kernels_usable && g.local_ranks.size() == 2);
+
+  // NUMA text parsing and the (possibly trivial) layout of this host
+  auto cpus = parse_cpu_list("0-3,8,10-11\n");
+  CHECK(cpus.size() == 7 && cpus[4] == 8 && cpus[6] == 11);
+  CHECK(parse_cpu_list("").empty() && parse_cpu_list("x").empty());
+  CHECK(numa_node_count() >= 1);
+  CHECK(!read_boot_id().empty());
+  CHECK(numa_node_of_pci("ffff:ff:1f.7") == -1);
+  CHECK(!bind_thread_to_numa_node(100000));
+}
+
 int main() {
   test_wire();
+  test_topology();
   test_mr_table();
   test_reduce();
   test_mesh_and_alloc();

@@ -37,3 +37,13 @@ def test_engine_selftest(tmp_path, world, n):
     exe = _build("engine_selftest", tmp_path)
     r = subprocess.run([exe, str(world), str(n)], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "ENGINE SELFTEST OK" in r.stdout, r.stdout + r.stderr
+
+
+def test_topology_binding_on_any_host():
+    """The binding answers on hosts without NVML too (an empty GPU table and this machine's boot id)."""
+    from moodist_b200._core import _C
+
+    t = _C.topology()
+    assert t["node_id"] and isinstance(t["gpus"], list) and len(t["links"]) == len(t["gpus"])
+    assert "GPU(s)" in t["text"]
+    assert isinstance(_C.numa_cpus(0), list)
