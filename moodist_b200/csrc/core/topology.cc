@@ -199,7 +199,7 @@ NodeTopology discover_topology(TopologyProbe& probe) {
         continue;
       }
       int ok = probe.p2p_ok(a, b);
-      if (ok <= 0) {
+      if (ok == 0) {  // an explicit "no"; when the machine does not answer (-1) the pair is not ruled out
         t.all_p2p = false;
         t.nvswitch = false;
         continue;
