@@ -33,7 +33,40 @@ enum PairStatus : uint32_t {
   kTimeoutPairEpilogue = 0x113,
 };
 
-template <bool kAMn, bool kBMn, typename OutT>
+// Walk order of the fused variants over 256-row pair tiles (same idea as tile_map of the one-SM kernel).
+// row_in_shard: first row of the tile inside its shard of the gathered operand (gather only).
+template <bool kGatherWait, bool kScatterOut>
+__device__ __forceinline__ void pair_tile_map(const Params& p, int t, int& tm, int& tn, int& shard, int& row_in_shard) {
+  shard = 0;
+  row_in_shard = 0;
+  if constexpr (kGatherWait) {
+    const int other = p.gather_on_b ? p.tiles_m : p.tiles_n;
+    const int blocks = p.shard_rows / kPairBM;  // BN == kPairBM: both gathered extents are 256 rows per tile
+    const int per_shard = blocks * other;
+    const int si = t / per_shard, within = t - si * per_shard;
+    shard = (p.first_shard - si + 2 * p.num_shards) % p.num_shards;
+    const int blk = within / other, o = within - blk * other;
+    if (p.gather_on_b) {
+      tn = shard * blocks + blk;
+      tm = o;
+    } else {
+      tm = shard * blocks + blk;
+      tn = o;
+    }
+    row_in_shard = blk * kPairBM;
+  } else if constexpr (kScatterOut) {
+    const int blocks = p.scatter_rows / kPairBM;
+    const int per_shard = blocks * p.tiles_n;
+    const int si = t / per_shard, within = t - si * per_shard;
+    shard = (p.first_shard + 1 + si) % p.num_shards;
+    tm = shard * blocks + within / p.tiles_n;
+    tn = within % p.tiles_n;
+  } else {
+    tile_coords(p, t, tm, tn);
+  }
+}
+
+template <bool kAMn, bool kBMn, typename OutT, bool kGatherWait = false, bool kScatterOut = false>
 __device__ __forceinline__ void gemm_pair_body(const Params& p, const CUtensorMap* tmap_a, const CUtensorMap* tmap_b,
                                                uint8_t* smem_raw) {
   uint32_t raw = smem_u32(smem_raw);
@@ -77,7 +110,7 @@ __device__ __forceinline__ void gemm_pair_body(const Params& p, const CUtensorMa
     tmem_relinquish_pair();
   }
   tc_fence_before_sync();
-  __syncthreads();
+  body_sync();
   cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
@@ -88,10 +121,23 @@ __device__ __forceinline__ void gemm_pair_body(const Params& p, const CUtensorMa
       uint32_t it = 0;
       bool ok = true;
       for (int t = pair; t < num_tiles && ok; t += stride) {
-        int tm, tn;
-        tile_coords(p, t, tm, tn);
+        int tm, tn, shard, row_in_shard;
+        pair_tile_map<kGatherWait, kScatterOut>(p, t, tm, tn, shard, row_in_shard);
         const int row_a = tm * kPairBM + (int)cta_rank * BM;     // this CTA's 128 rows of A
         const int row_b = tn * BN + (int)cta_rank * (BN / 2);    // this CTA's 128 rows (N) of B
+        if constexpr (kGatherWait) {
+          // the 128 gathered rows this CTA loads may span several arrival sub-chunks
+          const int r0 = row_in_shard + (int)cta_rank * BM;
+          const int first = r0 / p.sub_rows, last = (r0 + BM - 1) / p.sub_rows;
+          for (int f = first; f <= last && ok; ++f) {
+            if (!wait_geq_sys(p.ready + shard * p.subs_per_shard + f, p.epoch, p.wait_ns)) {
+              report(p, kTimeoutGather);
+              ok = false;
+            }
+          }
+          if (!ok) break;
+          fence_proxy_async_all();  // the rows were written by ordinary stores; TMA reads them next
+        }
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           int s = it % kPairStages;
           uint32_t ph = (it / kPairStages) & 1;
@@ -168,8 +214,8 @@ __device__ __forceinline__ void gemm_pair_body(const Params& p, const CUtensorMa
     uint32_t local_tile = 0;
     bool ok = true;
     for (int t = pair; t < num_tiles && ok; t += stride, ++local_tile) {
-      int tm, tn;
-      tile_coords(p, t, tm, tn);
+      int tm, tn, shard, row_in_shard;
+      pair_tile_map<kGatherWait, kScatterOut>(p, t, tm, tn, shard, row_in_shard);
       uint32_t acc = local_tile & 1;
       uint32_t acc_ph = (local_tile >> 1) & 1;
       if (!mbar_wait(&acc_full[acc], acc_ph, p.wait_ns)) {
@@ -179,7 +225,13 @@ __device__ __forceinline__ void gemm_pair_body(const Params& p, const CUtensorMa
       }
       tc_fence_after_sync();
       const int row0 = tm * kPairBM + (int)cta_rank * BM + q * 32;
-      OutT* cbase = reinterpret_cast<OutT*>(p.C) + (int64_t)row0 * p.ldc;
+      OutT* cbase;
+      if constexpr (kScatterOut) {
+        const int owner = (tm * kPairBM) / p.scatter_rows;  // scatter_rows is a multiple of 256 here
+        cbase = reinterpret_cast<OutT*>(p.scatter_dst[owner]) + (int64_t)(row0 - owner * p.scatter_rows) * p.ldc;
+      } else {
+        cbase = reinterpret_cast<OutT*>(p.C) + (int64_t)row0 * p.ldc;
+      }
       uint8_t* patch = epi_patch + (warp - 2) * kEpiPatchBytes;
       const uint32_t taddr = tmem_base + acc * kAccCols + ((uint32_t)(q * 32) << 16);
       constexpr int kColsPerPass = 128 / (int)sizeof(OutT);
@@ -228,11 +280,21 @@ __device__ __forceinline__ void gemm_pair_body(const Params& p, const CUtensorMa
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+      if constexpr (kScatterOut) {
+        // this warp's 32 rows are on their way: one arrival on the owner's counter of their 128-row block
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int owner = (tm * kPairBM) / p.scatter_rows;
+          const int blk = (tm * kPairBM + (int)cta_rank * BM - owner * p.scatter_rows) / BM;
+          red_add_release_sys(p.scatter_cnt[owner] + blk, 1u);
+        }
+      }
     }
     if (!ok && lane == 0) *abort_flag = 1;
   }
 
-  __syncthreads();
+  body_sync();
   if (*abort_flag) {
     // a wait ran out somewhere in this CTA: give copies that may still be in flight towards this CTA's
     // shared memory time to land before it is released

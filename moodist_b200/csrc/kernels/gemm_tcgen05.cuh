@@ -83,6 +83,10 @@ struct Params {
   int scatter_rows;          // output rows per owner (multiple of BM)
 };
 
+// Barrier over the 192 threads that run the tile loop (named barrier 1). In the plain GEMM kernels that is
+// the whole CTA; the fused all-gather kernel has four more warps that move data and must not be waited for.
+__device__ __forceinline__ void body_sync() { asm volatile("bar.sync 1, 192;" ::: "memory"); }
+
 // The status word may be host-mapped memory, so no atomics: first writer (nearly) wins.
 __device__ __forceinline__ void report(const Params& p, uint32_t code) {
   volatile uint32_t* s = p.status;
@@ -106,8 +110,9 @@ __device__ __forceinline__ void tile_coords(const Params& p, int t, int& tm, int
 //  scatter: tiles owned by other ranks first (rank+1, rank+2, ...), this rank's own rows last, so remote
 //           partial sums are on the wire while the local ones are still being computed.
 template <bool kGatherWait, bool kScatterOut>
-__device__ __forceinline__ void tile_map(const Params& p, int t, int& tm, int& tn, int& flag) {
+__device__ __forceinline__ void tile_map(const Params& p, int t, int& tm, int& tn, int& flag, int* nflags = nullptr) {
   flag = 0;
+  if (nflags) *nflags = 1;
   if constexpr (kGatherWait) {
     const int ext = p.gather_on_b ? BN : BM;
     const int other = p.gather_on_b ? p.tiles_m : p.tiles_n;
@@ -123,7 +128,10 @@ __device__ __forceinline__ void tile_map(const Params& p, int t, int& tm, int& t
       tm = shard * blocks + blk;
       tn = o;
     }
-    flag = shard * p.subs_per_shard + (blk * ext) / p.sub_rows;
+    // the tile's rows of the gathered operand may span several arrival sub-chunks
+    const int first = (blk * ext) / p.sub_rows, last = (blk * ext + ext - 1) / p.sub_rows;
+    flag = shard * p.subs_per_shard + first;
+    if (nflags) *nflags = last - first + 1;
   } else if constexpr (kScatterOut) {
     const int blocks = p.scatter_rows / BM;
     const int per_shard = blocks * p.tiles_n;
@@ -179,7 +187,7 @@ __device__ __forceinline__ void gemm_body(const Params& p, const CUtensorMap* tm
     tmem_relinquish();
   }
   tc_fence_before_sync();
-  __syncthreads();
+  body_sync();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
 
@@ -189,14 +197,16 @@ __device__ __forceinline__ void gemm_body(const Params& p, const CUtensorMap* tm
       uint32_t it = 0;  // k-blocks issued so far
       bool ok = true;
       for (int t = cta; t < num_tiles && ok; t += stride) {
-        int tm, tn, flag;
-        tile_map<kGatherWait, kScatterOut>(p, t, tm, tn, flag);
+        int tm, tn, flag, nflags;
+        tile_map<kGatherWait, kScatterOut>(p, t, tm, tn, flag, &nflags);
         if constexpr (kGatherWait) {
-          if (!wait_geq_sys(p.ready + flag, p.epoch, p.wait_ns)) {  // written by peers: system scope
-            report(p, kTimeoutGather);
-            ok = false;
-            break;
+          for (int f = 0; f < nflags && ok; ++f) {
+            if (!wait_geq_sys(p.ready + flag + f, p.epoch, p.wait_ns)) {  // written by peers: system scope
+              report(p, kTimeoutGather);
+              ok = false;
+            }
           }
+          if (!ok) break;
           fence_proxy_async_all();  // the landed rows were written by ordinary stores; TMA reads them next
         }
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
@@ -368,7 +378,7 @@ __device__ __forceinline__ void gemm_body(const Params& p, const CUtensorMap* tm
   }
 
   tc_fence_before_sync();
-  __syncthreads();
+  body_sync();
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
