@@ -63,15 +63,19 @@ class CudaGroupImpl final : public CudaGroup {
     comm_.max_ctas = (int)env_long("MOODIST_MAX_CTAS", 0);
     comm_.tuning = env_long("MOODIST_AG_STAGGER", 1) ? MB_TUNE_STAGGER : 0;
     push_bytes_ = (size_t)env_long("MOODIST_AG_PUSH_BYTES", 1 << 20);
-    // From this shard size up the all-gather pushes again (in two pipelined halves per CTA): posted writes
-    // fill NVLink better than read round trips, and the receiver's copy out of staging hides under the
-    // arrival of the second half. -1: large shards are pulled.
-    push_large_ = env_long("MOODIST_AG_PUSH_LARGE_BYTES", 32 << 20);
+    // Pushing large shards (two pipelined halves per CTA) beat the pull on 2 GPUs from 32 MiB up (447 vs 421 GB/s)
+    // but lost on 8 (456-499 vs 557-597 GB/s: seven incoming write streams per GPU plus the copy out of
+    // staging), so it stays off unless asked for.
+    push_large_ = env_long("MOODIST_AG_PUSH_LARGE_BYTES", -1);
     // Copy-engine variant (DMA copies between one-warp flag kernels): taken from this many bytes per rank up
     // when the group prefers kernel-less transfers, always when it is forced, and on its own from
     // MOODIST_CE_AUTO_BYTES up (-1: never on its own).
     ce_min_ = env_long("MOODIST_CE_MIN_BYTES", 1 << 20);
-    ce_auto_ = env_long("MOODIST_CE_AUTO_BYTES", -1);
+    // measured on 8 GPUs: the DMA all-gather reaches 612-683 GB/s from 64 MiB per rank up (pull kernel 557-597,
+    // NCCL 600-664); the DMA reduce-scatter (544 GB/s) stays behind the kernel (605-637), so only the all-gather
+    // switches on its own
+    ce_auto_ = env_long("MOODIST_CE_AUTO_BYTES", 48 << 20);
+    ce_auto_rs_ = env_long("MOODIST_CE_AUTO_RS_BYTES", -1);
     // smallest message (bytes) for which the NVLS variant is picked automatically; -1 = never
     nvls_ar_min_ = env_long("MOODIST_NVLS_AR_MIN_BYTES", 2 << 20);
     nvls_rs_min_ = env_long("MOODIST_NVLS_RS_MIN_BYTES", -1);
@@ -220,11 +224,11 @@ class CudaGroupImpl final : public CudaGroup {
     if (rc != MB_OK) fail(strf("moodist: %s: %s", what, rc_name(rc)));
   }
 
-  bool want_ce(size_t bytes) const {
+  bool want_ce(size_t bytes, long auto_min) const {
     if (world_ == 1 || !attached_ || opts_.method == 0 || opts_.method == 1) return false;
     if (opts_.force_kernel_less == 1 || opts_.method == 2) return true;
     if (opts_.prefer_kernel_less && bytes >= (size_t)ce_min_) return true;
-    return ce_auto_ >= 0 && bytes >= (size_t)ce_auto_;
+    return auto_min >= 0 && bytes >= (size_t)auto_min;
   }
   uint8_t* stage_half(int r, uint32_t seq) const {
     return (uint8_t*)comm_.stage[r] + (uint64_t)(seq & 1) * (comm_.staging_bytes / 2);
@@ -288,7 +292,7 @@ class CudaGroupImpl final : public CudaGroup {
     size_t osz = mb_dtype_size(odt), isz = mb_dtype_size(idt);
     if (!osz || !isz) fail("moodist: all_gather: unsupported dtype");
     if (count == 0) return;
-    if (idt == odt && want_ce(count * isz)) {
+    if (idt == odt && want_ce(count * isz, ce_auto_)) {
       all_gather_ce((const uint8_t*)in, (uint8_t*)out, count, isz, s);
       return;
     }
@@ -328,7 +332,7 @@ class CudaGroupImpl final : public CudaGroup {
     if (count == 0) return;
     const bool ce_types = (idt == odt && (idt == MB_F32 || idt == MB_BF16 || idt == MB_F16)) ||
                           (idt == MB_BF16 && odt == MB_F32) || (idt == MB_F32 && odt == MB_BF16);
-    if (ce_types && want_ce(count * isz)) {
+    if (ce_types && want_ce(count * isz, ce_auto_rs_)) {
       reduce_scatter_ce((const uint8_t*)in, (uint8_t*)out, count, idt, odt, op, premul, s);
       return;
     }
@@ -444,7 +448,7 @@ class CudaGroupImpl final : public CudaGroup {
   uint32_t seq_ = 0;
   size_t push_bytes_ = 0;
   long push_large_ = -1;
-  long ce_min_ = 1 << 20, ce_auto_ = -1;
+  long ce_min_ = 1 << 20, ce_auto_ = -1, ce_auto_rs_ = -1;
   int numa_node_ = -1;
   uint64_t ce_copies_ = 0;
   long nvls_ar_min_ = -1, nvls_rs_min_ = -1, nvls_ag_min_ = -1, nvls_ag_max_ = -1;

@@ -359,7 +359,14 @@ extern "C" int mb_gemm_rs(const mb_comm_t* c, uint32_t seq, const void* A, const
   if (M % (world * BM) != 0 || N % 8 != 0 || K % 8 != 0) return MB_ERR_ARG;
   const int rows = M / world;
   if (rows / BM > 128) return MB_ERR_TOO_BIG;
-  const bool pair = fused_pair_enabled() && rows % kPairBM == 0;
+  // On 8 GPUs the pair loop made this kernel slower (1.16 ms against 1.04 ms for the tensor-parallel MLP shape:
+  // the MMA issuer waits for the remote-store epilogues of both CTAs before it may reuse an accumulator), on 2
+  // GPUs faster (3.6 against 4.2 ms); it is opt-in: MOODIST_FUSED_PAIR_RS=1.
+  static const bool rs_pair = [] {
+    const char* e = getenv("MOODIST_FUSED_PAIR_RS");
+    return e && e[0] == '1';
+  }();
+  const bool pair = rs_pair && fused_pair_enabled() && rows % kPairBM == 0;
   const uint64_t slot_bytes = (uint64_t)rows * N * 2;
   if (slot_bytes * world > c->staging_bytes / 2) return MB_ERR_TOO_BIG;
   Params p{};

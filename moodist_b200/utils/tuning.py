@@ -86,10 +86,11 @@ def settings_from(table: dict[str, list[dict]]) -> dict[str, int]:
     ar = table.get("ar", [])
     if ar:
         out["MOODIST_NVLS_AR_MIN_BYTES"] = _first_size_from_which(ar, "nvls")
-    # one copy-engine threshold for all operations: the largest of the per-operation ones, so that no
-    # operation is moved to DMA copies below the size where they win
-    ce = [_first_size_from_which(t, "ce") for t in (ag, rs) if t]
-    out["MOODIST_CE_AUTO_BYTES"] = max(ce) if ce and all(c >= 0 for c in ce) else -1
+    # DMA copies: one threshold per operation (they win for all-gather long before they do for reduce-scatter)
+    if ag:
+        out["MOODIST_CE_AUTO_BYTES"] = _first_size_from_which(ag, "ce")
+    if rs:
+        out["MOODIST_CE_AUTO_RS_BYTES"] = _first_size_from_which(rs, "ce")
     return out
 
 
