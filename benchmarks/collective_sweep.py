@@ -3,7 +3,7 @@ bf16 and fp32 buffers, powers of two from 4 KiB to 1 GiB per rank, moodist kerne
 GPUs. Device-timed (CUDA events), max over ranks, 20 warm-up + 100 timed iterations by default.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29540 \
-        benchmarks/collective_sweep.py --out gpurun_out/sweep8.jsonl
+        benchmarks/collective_sweep.py --out sweep8.jsonl
 
 ``--impls`` may also name ``moodist_sym``: the same kernels on buffers allocated from the symmetric heap
 (``moodist_b200.allocator.symmetric_pool``, what ``enable_cuda_allocator()`` gives every tensor), which peers

@@ -112,6 +112,38 @@ void adamw_(at::Tensor p, const at::Tensor& g, at::Tensor m, at::Tensor v, doubl
       "adamw");
 }
 
+// returns (y, rstd)
+std::tuple<at::Tensor, at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, double eps) {
+  need_bf16_rows(x, "rmsnorm");
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kBFloat16 && w.is_contiguous() && w.numel() == x.size(1),
+              "moodist rmsnorm: bf16 weight of the row length required");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor y = at::empty({x.size(0), x.size(1)}, x.options());
+  at::Tensor rstd = at::empty({x.size(0)}, x.options().dtype(at::kFloat));
+  run(mb_rmsnorm_fwd_bf16(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), x.size(0), (int)x.size(1),
+                          x.stride(0), y.stride(0), (float)eps, cur_stream()),
+      "rmsnorm");
+  return {y, rstd};
+}
+
+// returns (dx, dw)
+std::tuple<at::Tensor, at::Tensor> rmsnorm_bwd(const at::Tensor& x, const at::Tensor& w, const at::Tensor& dy,
+                                               const at::Tensor& rstd) {
+  need_bf16_rows(x, "rmsnorm backward");
+  need_bf16_rows(dy, "rmsnorm backward");
+  TORCH_CHECK(dy.sizes() == x.sizes() && rstd.numel() == x.size(0) && rstd.scalar_type() == at::kFloat,
+              "moodist rmsnorm backward: shape mismatch");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor dx = at::empty({x.size(0), x.size(1)}, x.options());
+  at::Tensor dw = at::empty({x.size(1)}, x.options());
+  at::Tensor part = at::empty({(int64_t)mb_rmsnorm_bwd_parts(x.size(0)), x.size(1)}, x.options().dtype(at::kFloat));
+  run(mb_rmsnorm_bwd_bf16(x.data_ptr(), w.data_ptr(), dy.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
+                          part.data_ptr<float>(), dw.data_ptr(), x.size(0), (int)x.size(1), x.stride(0), dy.stride(0),
+                          dx.stride(0), cur_stream()),
+      "rmsnorm backward");
+  return {dx, dw};
+}
+
 }  // namespace
 
 void bind_train_ops(pybind11::module_& m) {
@@ -123,6 +155,9 @@ void bind_train_ops(pybind11::module_& m) {
   m.def("cross_entropy_fwd", &cross_entropy_fwd, py::arg("logits"), py::arg("targets"), py::arg("ignore_index") = -100);
   m.def("cross_entropy_bwd_", &cross_entropy_bwd_);
   m.def("adamw_", &adamw_);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rmsnorm_max_dim", [] { return mb_rmsnorm_max_dim(); });
 }
 
 }  // namespace moodist

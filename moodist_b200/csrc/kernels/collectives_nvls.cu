@@ -6,7 +6,7 @@
 //                    to every rank -> copy out
 //   reduce-scatter : stage input -> ld_reduce own chunk -> scale / cast -> out
 //   all-gather     : multimem.st own shard to every rank's staging -> copy out
-// The reference has no NVLS path (SURVEY §5.8); P2P kernels in collectives.cu are the fallback wherever a
+// The reference has no NVLS path; P2P kernels in collectives.cu are the fallback wherever a
 // multicast object cannot be created.
 #include <cuda_runtime.h>
 

@@ -14,7 +14,7 @@
 //     up: fp32 accumulation over the ranks' slots, optional scale, bf16 (or fp32) result.
 //
 // No TMA instruction touches another GPU's memory and no load uses cluster multicast: remote data moves
-// with ordinary ld/st only. The reference has neither op (it has no GEMM); BASELINE asks for them.
+// with ordinary ld/st only. The reference has neither op (it has no GEMM at all).
 #include "coll.cuh"
 #include "gemm_pair_tcgen05.cuh"
 

@@ -183,6 +183,15 @@ int mb_cross_entropy_fwd_bf16(const void* logits, const int64_t* targets, float*
                               int64_t stride, int64_t ignore_index, void* stream);
 int mb_cross_entropy_bwd_bf16(void* logits, const int64_t* targets, const float* lse, const float* gscale,
                               float inv_count, int64_t rows, int V, int64_t stride, int64_t ignore_index, void* stream);
+// RMSNorm over the last dimension (D a multiple of 8, at most mb_rmsnorm_max_dim()): y = x * rstd * w with rstd saved
+// per row; the backward gives dx and dw (partial sums per CTA in `dw_partial`, mb_rmsnorm_bwd_parts(rows) x D fp32).
+int mb_rmsnorm_max_dim(void);
+int mb_rmsnorm_bwd_parts(int64_t rows);
+int mb_rmsnorm_fwd_bf16(const void* x, const void* w, void* y, float* rstd, int64_t rows, int D, int64_t x_stride,
+                        int64_t y_stride, float eps, void* stream);
+int mb_rmsnorm_bwd_bf16(const void* x, const void* w, const void* dy, const float* rstd, void* dx, float* dw_partial,
+                        void* dw, int64_t rows, int D, int64_t x_stride, int64_t dy_stride, int64_t dx_stride,
+                        void* stream);
 // AdamW (decoupled decay, bias-corrected) on n bf16 parameters with bf16 moments; grad_dtype MB_F32 or MB_BF16.
 int mb_adamw_bf16(void* p, const void* g, int grad_dtype, void* m, void* v, int64_t n, float lr, float b1, float b2,
                   float eps, float wd, int step, float grad_scale, void* stream);

@@ -250,6 +250,159 @@ __global__ void adamw_kernel(__nv_bfloat16* __restrict__ p, const GradT* __restr
   }
 }
 
+// ---- RMSNorm ---------------------------------------------------------------------------------------
+// y = x * rsqrt(mean(x^2) + eps) * w, one CTA of 256 threads per row (forward) or per stripe of rows (backward).
+// A thread owns the same 8-element column groups in every row (groups tid, tid + 256, ...; at most kMaxGroups),
+// so the weight and the weight-gradient partial sums stay in registers across rows.
+constexpr int kNormThreads = 256;
+constexpr int kMaxGroups = 4;  // D <= 256 * 8 * 4 = 8192
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // red may still be read from the previous call
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < kNormThreads / 32 ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+
+template <int kG>
+__global__ void __launch_bounds__(kNormThreads)
+    rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                       __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int64_t rows, int D, int64_t x_stride,
+                       int64_t y_stride, float eps) {
+  __shared__ float red[kNormThreads / 32];
+  const int groups = D / 8;
+  float fw[kG][8];
+#pragma unroll
+  for (int g = 0; g < kG; ++g) {
+    const int col = (threadIdx.x + g * kNormThreads) * 8;
+    if (threadIdx.x + g * kNormThreads < groups) unpack8(*reinterpret_cast<const bf16x8*>(w + col), fw[g]);
+  }
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    float fx[kG][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int g = 0; g < kG; ++g) {
+      const int col = (threadIdx.x + g * kNormThreads) * 8;
+      if (threadIdx.x + g * kNormThreads < groups) {
+        unpack8(*reinterpret_cast<const bf16x8*>(x + r * x_stride + col), fx[g]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss += fx[g][k] * fx[g][k];
+      }
+    }
+    ss = block_sum(ss, red);
+    const float rs = rsqrtf(ss / (float)D + eps);
+    if (threadIdx.x == 0) rstd[r] = rs;
+#pragma unroll
+    for (int g = 0; g < kG; ++g) {
+      const int col = (threadIdx.x + g * kNormThreads) * 8;
+      if (threadIdx.x + g * kNormThreads < groups) {
+        float o[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = fx[g][k] * rs * fw[g][k];
+        *reinterpret_cast<bf16x8*>(y + r * y_stride + col) = pack8(o);
+      }
+    }
+  }
+}
+
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)),  dw_partial[cta] = sum over the CTA's rows of dy * xhat
+template <int kG>
+__global__ void __launch_bounds__(kNormThreads)
+    rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                       const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd,
+                       __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int64_t rows, int D,
+                       int64_t x_stride, int64_t dy_stride, int64_t dx_stride) {
+  __shared__ float red[kNormThreads / 32];
+  const int groups = D / 8;
+  float fw[kG][8], acc[kG][8];
+#pragma unroll
+  for (int g = 0; g < kG; ++g) {
+    const int col = (threadIdx.x + g * kNormThreads) * 8;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[g][k] = 0.f;
+    if (threadIdx.x + g * kNormThreads < groups) unpack8(*reinterpret_cast<const bf16x8*>(w + col), fw[g]);
+  }
+  // the next row's operands are requested before the current row's block-wide reduction, so their latency
+  // hides behind it
+  bf16x8 px[kG], pd[kG];
+  auto fetch = [&](int64_t r) {
+#pragma unroll
+    for (int g = 0; g < kG; ++g) {
+      const int col = (threadIdx.x + g * kNormThreads) * 8;
+      if (threadIdx.x + g * kNormThreads < groups) {
+        px[g] = *reinterpret_cast<const bf16x8*>(x + r * x_stride + col);
+        pd[g] = *reinterpret_cast<const bf16x8*>(dy + r * dy_stride + col);
+      }
+    }
+  };
+  if ((int64_t)blockIdx.x < rows) fetch(blockIdx.x);
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float rs = rstd[r];
+    float xh[kG][8], gw[kG][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int g = 0; g < kG; ++g) {
+      if (threadIdx.x + g * kNormThreads < groups) {
+        float fx[8], fd[8];
+        unpack8(px[g], fx);
+        unpack8(pd[g], fd);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          xh[g][k] = fx[k] * rs;
+          gw[g][k] = fd[k] * fw[g][k];
+          dot += gw[g][k] * xh[g][k];
+          acc[g][k] += fd[k] * xh[g][k];
+        }
+      }
+    }
+    if (r + gridDim.x < rows) fetch(r + gridDim.x);
+    dot = block_sum(dot, red) / (float)D;
+#pragma unroll
+    for (int g = 0; g < kG; ++g) {
+      const int col = (threadIdx.x + g * kNormThreads) * 8;
+      if (threadIdx.x + g * kNormThreads < groups) {
+        float o[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = rs * (gw[g][k] - xh[g][k] * dot);
+        *reinterpret_cast<bf16x8*>(dx + r * dx_stride + col) = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < kG; ++g) {
+    const int col = (threadIdx.x + g * kNormThreads) * 8;
+    if (threadIdx.x + g * kNormThreads < groups) {
+      float* o = dw_partial + (int64_t)blockIdx.x * D + col;
+      *reinterpret_cast<float4*>(o) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+      *reinterpret_cast<float4*>(o + 4) = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
+    }
+  }
+}
+
+// dw[c] = sum over `parts` rows of dw_partial[:, c]. One CTA per 32 columns: eight warps stride over the
+// rows (128-byte coalesced reads), then combine through shared memory.
+__global__ void __launch_bounds__(256)
+    rmsnorm_dw_kernel(const float* __restrict__ dw_partial, __nv_bfloat16* __restrict__ dw, int parts, int D) {
+  __shared__ float sm[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
+  float s = 0.f;
+  if (c < D) {
+    for (int p = ty; p < parts; p += 8) s += dw_partial[(int64_t)p * D + c];
+  }
+  sm[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < D) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += sm[k][tx];
+    dw[c] = __float2bfloat16(t);
+  }
+}
+
 inline int grid_for(int64_t work_items, int threads) {
   int64_t g = (work_items + threads - 1) / threads;
   if (g < 1) g = 1;
@@ -337,5 +490,51 @@ extern "C" int mb_adamw_bf16(void* p, const void* g, int grad_dtype, void* m, vo
   } else {
     return MB_ERR_ARG;
   }
+  return check_launch();
+}
+
+extern "C" int mb_rmsnorm_max_dim(void) { return kNormThreads * 8 * kMaxGroups; }
+extern "C" int mb_rmsnorm_bwd_parts(int64_t rows) {
+  int64_t g = rows < 148 * 8 ? rows : 148 * 8;
+  return (int)(g < 1 ? 1 : g);
+}
+
+extern "C" int mb_rmsnorm_fwd_bf16(const void* x, const void* w, void* y, float* rstd, int64_t rows, int D,
+                                   int64_t x_stride, int64_t y_stride, float eps, void* stream) {
+  if (rows <= 0) return MB_OK;
+  if (D <= 0 || D % 8 || D > kNormThreads * 8 * kMaxGroups) return MB_ERR_ARG;
+  if (!aligned16(x) || !aligned16(w) || !aligned16(y) || x_stride % 8 || y_stride % 8) return MB_ERR_ALIGN;
+  int64_t grid = rows < (1 << 20) ? rows : (1 << 20);  // one row per CTA: every load of the row is in flight at once
+  const int need = (D / 8 + kNormThreads - 1) / kNormThreads;  // column groups per thread
+#define FWD(G)                                                                         \
+  rmsnorm_fwd_kernel<G><<<(unsigned)grid, kNormThreads, 0, MB_STREAM(stream)>>>(       \
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w), \
+      reinterpret_cast<__nv_bfloat16*>(y), rstd, rows, D, x_stride, y_stride, eps)
+  if (need <= 1) FWD(1); else if (need <= 2) FWD(2); else FWD(4);
+#undef FWD
+  return check_launch();
+}
+
+// dw_partial: fp32 scratch of mb_rmsnorm_bwd_parts(rows) x D elements
+extern "C" int mb_rmsnorm_bwd_bf16(const void* x, const void* w, const void* dy, const float* rstd, void* dx,
+                                   float* dw_partial, void* dw, int64_t rows, int D, int64_t x_stride,
+                                   int64_t dy_stride, int64_t dx_stride, void* stream) {
+  if (rows <= 0) return MB_OK;
+  if (D <= 0 || D % 8 || D > kNormThreads * 8 * kMaxGroups) return MB_ERR_ARG;
+  if (!aligned16(x) || !aligned16(w) || !aligned16(dy) || !aligned16(dx) || !aligned16(dw_partial) || x_stride % 8 ||
+      dy_stride % 8 || dx_stride % 8)
+    return MB_ERR_ALIGN;
+  const int parts = mb_rmsnorm_bwd_parts(rows);
+  const int need = (D / 8 + kNormThreads - 1) / kNormThreads;
+#define BWD(G)                                                                                  \
+  rmsnorm_bwd_kernel<G><<<parts, kNormThreads, 0, MB_STREAM(stream)>>>(                         \
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w),     \
+      reinterpret_cast<const __nv_bfloat16*>(dy), rstd, reinterpret_cast<__nv_bfloat16*>(dx), dw_partial, rows, D, \
+      x_stride, dy_stride, dx_stride)
+  if (need <= 1) BWD(1); else if (need <= 2) BWD(2); else BWD(4);
+#undef BWD
+  if (check_launch()) return MB_ERR_LAUNCH;
+  rmsnorm_dw_kernel<<<(D + 31) / 32, 256, 0, MB_STREAM(stream)>>>(dw_partial, reinterpret_cast<__nv_bfloat16*>(dw),
+                                                                   parts, D);
   return check_launch();
 }

@@ -17,7 +17,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from ..ops.gemm import Linear
-from ..ops.train import cross_entropy, rope_qkv_, swiglu
+from ..ops.train import cross_entropy, rms_norm, rope_qkv_, swiglu
 
 
 @dataclass
@@ -54,7 +54,7 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(dim, device=device, dtype=dtype))
 
     def forward(self, x):
-        return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
+        return rms_norm(x, self.weight, self.eps)
 
 
 def rope_tables(head_dim: int, seq_len: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:

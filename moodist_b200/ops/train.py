@@ -5,6 +5,7 @@
 ``cross_entropy`` mean token cross-entropy over bf16 logits; the backward overwrites the logits with their
                   gradient, so no fp32 copy of the ``[tokens, vocab]`` matrix is ever made
 ``adamw_``        AdamW over a flat bf16 parameter shard with bf16 moments (gradient fp32 or bf16)
+``rms_norm``      RMSNorm over the last dimension; the backward produces dx and dw in one pass over dy and x
 
 On CUDA tensors these always run the kernels of ``csrc/kernels/train_ops.cu``.  CPU tensors take plain
 PyTorch arithmetic so the sharded engine's host-side logic can be exercised on ``gloo`` ranks.
@@ -152,6 +153,38 @@ def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int
     if not logits.is_contiguous():
         logits = logits.contiguous()
     return _CrossEntropy.apply(logits, targets, ignore_index)
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1 or (x2.stride(0) * 2) % 16:
+            x2 = x2.contiguous()
+        _count()
+        y, rstd = _C.rmsnorm_fwd(x2, w, eps)
+        ctx.save_for_backward(x2, w, rstd)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, rstd = ctx.saved_tensors
+        d2 = dy.reshape(-1, dy.shape[-1])
+        if d2.stride(-1) != 1 or (d2.stride(0) * 2) % 16:
+            d2 = d2.contiguous()
+        _count(2)
+        dx, dw = _C.rmsnorm_bwd(x2, w, d2, rstd)
+        return dx.view(dy.shape), dw, None
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """``x * rsqrt(mean(x^2, -1) + eps) * weight``; bf16 CUDA tensors whose last dimension is a multiple of 8
+    (up to 8192) run the single-pass kernels, anything else ``torch.nn.functional.rms_norm``."""
+    d = x.shape[-1]
+    if (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and d % 8 == 0
+            and d <= _C.rmsnorm_max_dim() and weight.is_contiguous()):
+        return _RMSNorm.apply(x, weight, eps)
+    return F.rms_norm(x, (d,), weight, eps)
 
 
 def adamw_(p, g, m, v, lr: float, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.1, step: int = 1,

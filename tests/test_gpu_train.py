@@ -53,6 +53,27 @@ def test_swiglu_kernel_forward_backward():
     torch.testing.assert_close(gu.grad.float(), g32.grad, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("rows,D", [(5, 256), (777, 4096), (300, 8192), (64, 1000)])
+def test_rmsnorm_kernel_forward_backward(rows, D):
+    from moodist_b200.ops.train import rms_norm
+
+    torch.manual_seed(rows + D)
+    x = (torch.randn(3, rows, D, device="cuda") * 2).bfloat16().requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16().requires_grad_(True)
+    y = rms_norm(x, w, 1e-5)
+    x32 = x.detach().float().requires_grad_(True)
+    w32 = w.detach().float().requires_grad_(True)
+    ref = F.rms_norm(x32, (D,), w32, 1e-5)
+    torch.testing.assert_close(y.float(), ref, rtol=1e-2, atol=1e-2)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    ref.backward(dy.float())
+    torch.testing.assert_close(x.grad.float(), x32.grad, rtol=2e-2, atol=2e-2)
+    # dw sums 3 * rows products: compare relative to its magnitude
+    rel = (w.grad.float() - w32.grad).abs().max() / w32.grad.abs().max()
+    assert rel < 2e-2, rel
+
+
 @pytest.mark.parametrize("rows,V", [(37, 1000), (513, 128256), (16, 1003)])
 def test_cross_entropy_kernel(rows, V):
     from moodist_b200._core import _C
