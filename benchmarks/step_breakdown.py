@@ -4,7 +4,8 @@ layers (full width, vocabulary and sequence length), from torch.profiler on one 
     python benchmarks/step_breakdown.py --layers 4 --engine native
 
 Prints the CUDA-event time of a step without the profiler first (the number to quote), then the table of
-kernels sorted by device time (shares only: a profiler is attached for that step).
+kernels sorted by device time (shares only: a profiler is attached for that step). With ``--no-profiler`` only
+the timing runs, e.g. under ``ncu --metrics gpu__time_duration.sum`` for a launch list.
 """
 
 from __future__ import annotations
@@ -30,6 +31,8 @@ def main():
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--engine", default="native", choices=["native", "fsdp2"])
     ap.add_argument("--rows", type=int, default=40)
+    ap.add_argument("--no-profiler", action="store_true",
+                    help="only time the steps (for runs under an external profiler such as ncu's launch list)")
     args = ap.parse_args()
     torch.cuda.set_device(0)
     dist.init_process_group("moodist", init_method=f"tcp://127.0.0.1:{free_port()}", rank=0, world_size=1)
@@ -47,6 +50,9 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     print(f"{args.layers} layers, engine {args.engine}: {e0.elapsed_time(e1) / 2:.2f} ms/step (CUDA events, no profiler)")
+    if args.no_profiler:
+        dist.destroy_process_group()
+        return
     with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
         tr.step_on_device(toks[5])
         torch.cuda.synchronize()
