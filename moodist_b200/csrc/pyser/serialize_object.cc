@@ -26,7 +26,9 @@
 #include <Python.h>
 
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
+#include <new>
 #include <stdexcept>
 #include <string>
 #include <unordered_map>
@@ -101,9 +103,87 @@ void init_strings() {
 }
 
 // ------------------------------------------------------------------------------------------------
+// Output bytes: a plain growing buffer (no zero-fill on growth, no per-byte capacity check beyond one compare).
+class ByteBuf {
+ public:
+  ByteBuf() = default;
+  ByteBuf(const ByteBuf&) = delete;
+  ByteBuf& operator=(const ByteBuf&) = delete;
+  ~ByteBuf() { free(data_); }
+  size_t size() const { return size_; }
+  uint8_t* data() { return data_; }
+  uint8_t& operator[](size_t i) { return data_[i]; }
+  void reserve(size_t n) {
+    if (n > cap_) grow(n);
+  }
+  void push_back(uint8_t b) {
+    if (size_ == cap_) grow(size_ + 1);
+    data_[size_++] = b;
+  }
+  void append(const void* p, size_t n) {
+    if (size_ + n > cap_) grow(size_ + n);
+    memcpy(data_ + size_, p, n);
+    size_ += n;
+  }
+
+ private:
+  void grow(size_t need) {
+    size_t cap = cap_ ? cap_ * 2 : 256;
+    while (cap < need) cap *= 2;
+    void* p = realloc(data_, cap);
+    if (!p) throw std::bad_alloc();
+    data_ = static_cast<uint8_t*>(p);
+    cap_ = cap;
+  }
+  uint8_t* data_ = nullptr;
+  size_t size_ = 0, cap_ = 0;
+};
+
+// Identity memo: object address -> offset of its first encoding. Open addressing with linear probing in a
+// power-of-two table kept at most half full; one multiply to hash, no allocation per entry.
+class PtrMap {
+ public:
+  PtrMap() { rehash(1024); }
+  // returns {slot value reference, true if the key was inserted now}
+  std::pair<size_t*, bool> try_emplace(PyObject* key, size_t value) {
+    if ((count_ + 1) * 2 > keys_.size()) rehash(keys_.size() * 2);
+    size_t i = index(key);
+    while (keys_[i]) {
+      if (keys_[i] == key) return {&vals_[i], false};
+      i = (i + 1) & mask_;
+    }
+    keys_[i] = key;
+    vals_[i] = value;
+    ++count_;
+    return {&vals_[i], true};
+  }
+
+ private:
+  size_t index(PyObject* key) const {
+    return (size_t)(((uint64_t)(uintptr_t)key >> 4) * 0x9E3779B97F4A7C15ull >> shift_);
+  }
+  void rehash(size_t n) {
+    std::vector<PyObject*> ok;
+    std::vector<size_t> ov;
+    ok.swap(keys_);
+    ov.swap(vals_);
+    keys_.assign(n, nullptr);
+    vals_.assign(n, 0);
+    mask_ = n - 1;
+    shift_ = 64 - __builtin_ctzll(n);
+    count_ = 0;
+    for (size_t j = 0; j < ok.size(); ++j)
+      if (ok[j]) try_emplace(ok[j], ov[j]);
+  }
+  std::vector<PyObject*> keys_;
+  std::vector<size_t> vals_;
+  size_t mask_ = 0, count_ = 0;
+  int shift_ = 0;
+};
+
 class Packer {
  public:
-  std::vector<uint8_t> out;
+  ByteBuf out;
 
   void pack(PyObject* obj) {
     if (obj == Py_None) return byte(T_NONE);
@@ -118,11 +198,11 @@ class Packer {
       return;
     }
     // everything below is memoised by identity
-    auto [it, fresh] = memo_.try_emplace(obj, out.size());
+    auto [slot, fresh] = memo_.try_emplace(obj, out.size());
     if (!fresh) {
-      out[it->second] |= 0x80;
+      out[*slot] |= 0x80;
       byte(T_OFFSET);
-      u64(it->second);
+      u64(*slot);
       return;
     }
     if (depth_ > 2000) {
@@ -135,15 +215,12 @@ class Packer {
   }
 
  private:
-  std::unordered_map<PyObject*, size_t> memo_;
+  PtrMap memo_;
   std::vector<Ref> keepalive_;  // temporaries (reduce results) must outlive the memo entries that point at them
   int depth_ = 0;
 
   void byte(uint8_t b) { out.push_back(b); }
-  void raw(const void* p, size_t n) {
-    const uint8_t* b = static_cast<const uint8_t*>(p);
-    out.insert(out.end(), b, b + n);
-  }
+  void raw(const void* p, size_t n) { out.append(p, n); }
   void u64(uint64_t v) { raw(&v, 8); }
 
   void pack_int(int64_t v) {
