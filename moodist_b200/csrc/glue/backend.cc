@@ -566,6 +566,27 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::barrier(const c10d::BarrierOption
   return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::BARRIER, std::vector<at::Tensor>{});
 }
 
+c10::intrusive_ptr<c10d::Work> MoodistBackend::send(std::vector<at::Tensor>& tensors, int dstRank, int tag) {
+  TORCH_CHECK(tensors.size() == 1, "moodist: send takes one tensor");
+  TORCH_CHECK(dstRank >= 0 && dstRank < size_ && dstRank != rank_, "moodist: send: bad destination rank ", dstRank);
+  at::Tensor t = tensors[0];
+  check_contig(t, "send tensor");
+  at::Tensor host = t.is_cuda() ? t.cpu() : t;  // .cpu() synchronises with the producing stream
+  MOODIST_TRANSLATE(hostGroup().send(host.data_ptr(), (size_t)host.nbytes(), dstRank, (uint32_t)tag);)
+  return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::SEND, tensors);
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::recv(std::vector<at::Tensor>& tensors, int srcRank, int tag) {
+  TORCH_CHECK(tensors.size() == 1, "moodist: recv takes one tensor");
+  TORCH_CHECK(srcRank >= 0 && srcRank < size_ && srcRank != rank_, "moodist: recv: bad source rank ", srcRank);
+  at::Tensor t = tensors[0];
+  check_contig(t, "recv tensor");
+  at::Tensor host = t.is_cuda() ? at::empty(t.sizes(), t.options().device(at::kCPU).pinned_memory(true)) : t;
+  MOODIST_TRANSLATE(hostGroup().recv(host.data_ptr(), (size_t)host.nbytes(), srcRank, (uint32_t)tag);)
+  if (t.is_cuda()) t.copy_(host);  // blocking copy from pinned memory: `host` may be released afterwards
+  return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::RECV, tensors);
+}
+
 void MoodistBackend::cudaBarrier() {
   int dev = cuda_ ? cuda_->device() : (int)c10::cuda::current_device();
   c10::cuda::CUDAGuard guard((c10::DeviceIndex)dev);

@@ -79,6 +79,10 @@ class MoodistBackend final : public c10d::Backend {
   c10::intrusive_ptr<c10d::Work> alltoall(std::vector<at::Tensor>& outputs, std::vector<at::Tensor>& inputs,
                                           const c10d::AllToAllOptions& opts = c10d::AllToAllOptions()) override;
   c10::intrusive_ptr<c10d::Work> barrier(const c10d::BarrierOptions& opts = c10d::BarrierOptions()) override;
+  // point-to-point through the host engine (CUDA tensors are staged through host memory): enough for
+  // control traffic and pipeline hand-offs, not a bandwidth path
+  c10::intrusive_ptr<c10d::Work> send(std::vector<at::Tensor>& tensors, int dstRank, int tag) override;
+  c10::intrusive_ptr<c10d::Work> recv(std::vector<at::Tensor>& tensors, int srcRank, int tag) override;
 
   // ---- moodist-specific surface (reference: wrapper/module.cc:836-849) ----
   std::string moodistName() const { return name_; }

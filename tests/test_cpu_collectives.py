@@ -92,3 +92,36 @@ def _odd_sizes(rank, world, port):
 
 def test_cpu_odd_sizes_and_stress():
     run_ranks(_odd_sizes, 2, timeout=120)
+
+
+def _send_recv(rank, world, port):
+    dist = init_moodist(rank, world, port)
+    # a ring of point-to-point messages with tags, two in flight per pair, different sizes
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    a = torch.arange(1000, dtype=torch.float32) + rank
+    b = torch.full((3, 7), rank, dtype=torch.int64)
+    ra, rb = torch.empty(1000), torch.empty(3, 7, dtype=torch.int64)
+    if rank % 2 == 0:
+        dist.send(a, nxt, tag=1)
+        dist.send(b, nxt, tag=2)
+        dist.recv(rb, prv, tag=2)  # received out of send order: matched by tag
+        dist.recv(ra, prv, tag=1)
+    else:
+        dist.recv(rb, prv, tag=2)
+        dist.recv(ra, prv, tag=1)
+        dist.send(a, nxt, tag=1)
+        dist.send(b, nxt, tag=2)
+    assert torch.equal(ra, torch.arange(1000, dtype=torch.float32) + prv)
+    assert torch.equal(rb, torch.full((3, 7), prv, dtype=torch.int64))
+    # non-blocking forms
+    reqs = [dist.isend(a * 2, nxt, tag=9), dist.irecv(ra, prv, tag=9)]
+    for r in reqs:
+        r.wait()
+    assert torch.equal(ra, (torch.arange(1000, dtype=torch.float32) + prv) * 2)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_send_recv_ring():
+    run_ranks(_send_recv, 2, timeout=120)
+    run_ranks(_send_recv, 4, timeout=120)
