@@ -160,3 +160,64 @@ def test_errors():
         moodist.deserialize(torch.tensor([0, 0], dtype=torch.uint8))  # trailing bytes
     with pytest.raises(TypeError):
         moodist.deserialize(torch.zeros(2))
+
+
+def test_roundtrip_property_based():
+    """Randomly generated nested objects survive serialize -> deserialize unchanged, shared references stay shared."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    import moodist_b200 as moodist
+
+    scalars = st.one_of(
+        st.none(), st.booleans(), st.integers(min_value=-(2**80), max_value=2**80),
+        st.floats(allow_nan=False), st.text(max_size=40), st.binary(max_size=40),
+    )
+    hashable = st.one_of(st.integers(), st.text(max_size=10), st.booleans(), st.none(),
+                         st.tuples(st.integers(), st.text(max_size=5)))
+    objects = st.recursive(
+        scalars,
+        lambda inner: st.one_of(
+            st.lists(inner, max_size=6), st.tuples(inner, inner), st.dictionaries(hashable, inner, max_size=6),
+            st.frozensets(hashable, max_size=5), st.sets(hashable, max_size=5),
+        ),
+        max_leaves=40,
+    )
+
+    @settings(max_examples=300, deadline=None)
+    @given(objects)
+    def check(obj):
+        back = moodist.deserialize(moodist.serialize(obj))
+        assert back == obj and type(back) is type(obj)
+        shared = [obj, obj, (obj,)]
+        b2 = moodist.deserialize(moodist.serialize(shared))
+        assert b2 == shared
+        if isinstance(obj, (list, dict, set)):
+            assert b2[0] is b2[1] and b2[2][0] is b2[0]
+
+    check()
+
+
+def test_truncated_and_corrupt_input_raise():
+    """Every prefix of a valid encoding and random byte flips either raise a Python exception or decode to some
+    object; none may crash the process."""
+    import random
+
+    import moodist_b200 as moodist
+
+    obj = {"a": [1, 2.5, "x" * 20, b"bytes", (None, True)], "b": {1, 2, 3}, "c": 2**70, "d": [[], {}, ()]}
+    blob = bytes(moodist.serialize(obj).numpy().tobytes() if hasattr(moodist.serialize(obj), "numpy") else moodist.serialize(obj))
+    for cut in range(len(blob)):
+        try:
+            moodist.deserialize(blob[:cut])
+        except Exception:
+            pass
+    rng = random.Random(0)
+    for _ in range(500):
+        b = bytearray(blob)
+        for _ in range(rng.randint(1, 3)):
+            b[rng.randrange(len(b))] = rng.randrange(256)
+        try:
+            moodist.deserialize(bytes(b))
+        except Exception:
+            pass
