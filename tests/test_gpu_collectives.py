@@ -170,6 +170,28 @@ def test_copy_engine_variants_2gpu():
     run_ranks(_copy_engine_variants, 2, timeout=240, env={"MOODIST_DEVICE_TIMEOUT_MS": 5000})
 
 
+def _cuda_send_recv(rank, world, port):
+    dist = init_moodist(rank, world, port, device="cuda")
+    dev = torch.device("cuda", rank)
+    peer = 1 - rank
+    a = (torch.arange(100_000, device=dev, dtype=torch.float32) + rank).bfloat16()
+    got = torch.empty_like(a)
+    if rank == 0:
+        dist.send(a, peer, tag=3)
+        dist.recv(got, peer, tag=4)
+    else:
+        dist.recv(got, peer, tag=3)
+        dist.send(a, peer, tag=4)
+    want = (torch.arange(100_000, device=dev, dtype=torch.float32) + peer).bfloat16()
+    assert torch.equal(got, want)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_cuda_send_recv_2gpu():
+    run_ranks(_cuda_send_recv, 2, timeout=120)
+
+
 def _absent_rank(rank, world, port):
     """A device wait that runs out returns a status instead of hanging: rank 1 never launches."""
     import time
