@@ -30,7 +30,6 @@ from dataclasses import dataclass, field
 
 import torch
 import torch.distributed as dist
-from torch import nn
 
 from ..ops.train import adamw_
 

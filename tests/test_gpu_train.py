@@ -1,7 +1,6 @@
 """Training kernels (rotary embedding, SwiGLU, cross-entropy, AdamW) against fp32 PyTorch references of the
 same ops, and the sharded engine on GPUs against a single-process AdamW on rank-averaged gradients."""
 
-import copy
 
 import pytest
 import torch
