@@ -76,6 +76,7 @@ class CudaGroupImpl final : public CudaGroup {
     // switches on its own
     ce_auto_ = env_long("MOODIST_CE_AUTO_BYTES", 48 << 20);
     ce_auto_rs_ = env_long("MOODIST_CE_AUTO_RS_BYTES", -1);
+    ar_compose_ = env_long("MOODIST_AR_COMPOSE_BYTES", -1);
     // smallest message (bytes) for which the NVLS variant is picked automatically; -1 = never
     nvls_ar_min_ = env_long("MOODIST_NVLS_AR_MIN_BYTES", 2 << 20);
     nvls_rs_min_ = env_long("MOODIST_NVLS_RS_MIN_BYTES", -1);
@@ -289,6 +290,9 @@ class CudaGroupImpl final : public CudaGroup {
 
   void all_gather(const void* in, void* out, size_t count, int idt, int odt, CUstream_st* s) override {
     std::lock_guard<std::mutex> lk(mu_);
+    all_gather_locked(in, out, count, idt, odt, s);
+  }
+  void all_gather_locked(const void* in, void* out, size_t count, int idt, int odt, CUstream_st* s) {
     size_t osz = mb_dtype_size(odt), isz = mb_dtype_size(idt);
     if (!osz || !isz) fail("moodist: all_gather: unsupported dtype");
     if (count == 0) return;
@@ -327,6 +331,10 @@ class CudaGroupImpl final : public CudaGroup {
   void reduce_scatter(const void* in, void* out, size_t count, int idt, int odt, int op, float premul,
                       CUstream_st* s) override {
     std::lock_guard<std::mutex> lk(mu_);
+    reduce_scatter_locked(in, out, count, idt, odt, op, premul, s);
+  }
+  void reduce_scatter_locked(const void* in, void* out, size_t count, int idt, int odt, int op, float premul,
+                             CUstream_st* s) {
     size_t osz = mb_dtype_size(odt), isz = mb_dtype_size(idt);
     if (!osz || !isz) fail("moodist: reduce_scatter: unsupported dtype");
     if (count == 0) return;
@@ -364,6 +372,19 @@ class CudaGroupImpl final : public CudaGroup {
     size_t sz = mb_dtype_size(dt);
     if (!sz) fail("moodist: all_reduce: unsupported dtype");
     if (count == 0) return;
+    // Large buffers, opt-in (MOODIST_AR_COMPOSE_BYTES): the reduce-scatter kernel into this rank's slice of `out`,
+    // then the (DMA) all-gather in place. From the 8-GPU sweep's parts (reduce-scatter 605-614 GB/s, DMA all-gather
+    // 612-683 GB/s) this should give 609-638 GB/s bus bandwidth against 574-586 for the NVLS kernel; it stays
+    // off until that is measured as a whole.
+    if (ar_compose_ >= 0 && world_ > 1 && count * sz >= (size_t)ar_compose_ && count % (size_t)world_ == 0 &&
+        ((count / world_) * sz) % 16 == 0 && (op == MB_SUM || op == MB_AVG || op == MB_PREMUL_SUM) &&
+        (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+      const size_t chunk = count / world_;
+      uint8_t* mine = (uint8_t*)out + (size_t)rank_ * chunk * sz;
+      reduce_scatter_locked(in, mine, chunk, dt, dt, op, premul, s);
+      all_gather_locked(mine, out, chunk, dt, dt, s);
+      return;
+    }
     size_t half = comm_.staging_bytes / 2;
     size_t oneshot_max = (size_t)env_long("MOODIST_AR_ONESHOT_BYTES", 2 << 20);
     // two-shot needs 2*world*chunk bytes of the half; keep pieces well inside
@@ -448,7 +469,7 @@ class CudaGroupImpl final : public CudaGroup {
   uint32_t seq_ = 0;
   size_t push_bytes_ = 0;
   long push_large_ = -1;
-  long ce_min_ = 1 << 20, ce_auto_ = -1, ce_auto_rs_ = -1;
+  long ce_min_ = 1 << 20, ce_auto_ = -1, ce_auto_rs_ = -1, ar_compose_ = -1;
   int numa_node_ = -1;
   uint64_t ce_copies_ = 0;
   long nvls_ar_min_ = -1, nvls_rs_min_ = -1, nvls_ag_min_ = -1, nvls_ag_max_ = -1;

@@ -166,6 +166,28 @@ def _copy_engine_variants(rank, world, port):
     dist.destroy_process_group()
 
 
+def _composed_all_reduce(rank, world, port):
+    """MOODIST_AR_COMPOSE_BYTES: all-reduce as reduce-scatter kernel + in-place all-gather, in and out of place."""
+    dist = init_moodist(rank, world, port, device="cuda")
+    dev = torch.device("cuda", rank)
+    for dtype, n, op in [(torch.bfloat16, 1 << 20, dist.ReduceOp.SUM), (torch.float32, 3 << 19, dist.ReduceOp.AVG),
+                         (torch.bfloat16, 64 << 20, dist.ReduceOp.SUM), (torch.float32, 1000, dist.ReduceOp.SUM)]:
+        g = torch.Generator().manual_seed(5)
+        full = (torch.rand(world, n, generator=g) * 2 - 1).to(dtype)
+        t = full[rank].to(dev)
+        dist.all_reduce(t, op=op)
+        ref = full.float().sum(0) / (world if op == dist.ReduceOp.AVG else 1)
+        torch.testing.assert_close(t.float().cpu(), ref, rtol=2e-2, atol=2e-2)
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_composed_all_reduce_2gpu():
+    run_ranks(_composed_all_reduce, 2, timeout=240, env={"MOODIST_AR_COMPOSE_BYTES": 1 << 20,
+                                                         "MOODIST_DEVICE_TIMEOUT_MS": 5000})
+
+
 def test_copy_engine_variants_2gpu():
     run_ranks(_copy_engine_variants, 2, timeout=240, env={"MOODIST_DEVICE_TIMEOUT_MS": 5000})
 
