@@ -1,6 +1,8 @@
 // Stand-alone checks of the torch-free core: wire format golden bytes, the registered-memory table,
 // the bootstrap ring (ranks as threads), the store mesh, and the CPU reduce loops.
+#include <algorithm>
 #include <cmath>
+#include <cstring>
 #include <condition_variable>
 #include <cstdio>
 #include <map>
@@ -10,6 +12,7 @@
 #include <variant>
 
 #include "core/cpu_allocator.h"
+#include "core/compile_plan.h"
 #include "core/cpu_reduce.h"
 #include "core/log.h"
 #include "core/numa.h"
@@ -276,8 +279,125 @@ static void test_topology() {
   CHECK(!bind_thread_to_numa_node(100000));
 }
 
+// Random N-d redistributions: the global tensor is cut into input boxes one way and output boxes another way
+// (random cuts per dimension, boxes dealt to ranks at random, some inputs replicated); executing every rank's
+// pieces on byte buffers must reproduce the global tensor in every output box, each element written once.
+static void test_planner_random() {
+  uint64_t seed = 12345;
+  auto rnd = [&](uint64_t n) {
+    seed = seed * 6364136223846793005ull + 1442695040888963407ull;
+    return (seed >> 33) % n;
+  };
+  auto cuts = [&](int64_t extent) {
+    std::vector<int64_t> c{0};
+    int parts = 1 + (int)rnd(3);
+    for (int i = 1; i < parts; ++i) c.push_back(1 + (int64_t)rnd((uint64_t)extent - 1 > 0 ? extent - 1 : 1));
+    c.push_back(extent);
+    std::sort(c.begin(), c.end());
+    c.erase(std::unique(c.begin(), c.end()), c.end());
+    return c;
+  };
+  for (int iter = 0; iter < 200; ++iter) {
+    const int nd = 1 + (int)rnd(4), world = 1 + (int)rnd(4);
+    const size_t esz = (size_t[]){1, 2, 4, 8}[rnd(4)];
+    std::vector<int64_t> shape(nd);
+    int64_t total = 1;
+    for (auto& d : shape) {
+      d = 1 + (int64_t)rnd(9);
+      total *= d;
+    }
+    auto boxes_of = [&](bool replicate) {
+      std::vector<std::vector<int64_t>> c;
+      for (int d = 0; d < nd; ++d) c.push_back(cuts(shape[d]));
+      std::vector<BoxSpec> out;
+      std::vector<size_t> idx(nd, 0);
+      while (true) {
+        BoxSpec b;
+        b.rank = (int)rnd(world);
+        for (int d = 0; d < nd; ++d) {
+          b.offset.push_back(c[d][idx[d]]);
+          b.shape.push_back(c[d][idx[d] + 1] - c[d][idx[d]]);
+        }
+        out.push_back(b);
+        if (replicate && rnd(4) == 0) {  // the same data also lives on another rank
+          BoxSpec r = b;
+          r.rank = (int)rnd(world);
+          out.push_back(r);
+        }
+        int d = nd - 1;
+        while (d >= 0 && ++idx[d] + 1 >= c[d].size()) idx[d--] = 0;
+        if (d < 0) break;
+      }
+      return out;
+    };
+    std::vector<BoxSpec> ins = boxes_of(true), outs = boxes_of(false);
+    // global tensor: element i holds bytes derived from i
+    std::vector<uint8_t> global((size_t)total * esz);
+    for (size_t i = 0; i < global.size(); ++i) global[i] = (uint8_t)(i * 131 + 7);
+    auto strides = [&](const std::vector<int64_t>& sh) {
+      std::vector<int64_t> st(sh.size(), 1);
+      for (int d = (int)sh.size() - 2; d >= 0; --d) st[d] = st[d + 1] * sh[d + 1];
+      return st;
+    };
+    auto fill_box = [&](const BoxSpec& b) {  // the box's contents as a contiguous local tensor
+      std::vector<uint8_t> buf((size_t)b.numel() * esz);
+      auto gst = strides(shape), lst = strides(b.shape);
+      for (int64_t e = 0; e < b.numel(); ++e) {
+        int64_t rem = e, g = 0;
+        for (int d = 0; d < nd; ++d) {
+          int64_t i = rem / lst[d];
+          rem -= i * lst[d];
+          g += (b.offset[d] + i) * gst[d];
+        }
+        memcpy(&buf[(size_t)e * esz], &global[(size_t)g * esz], esz);
+      }
+      return buf;
+    };
+    // per rank: its input tensors in plan order
+    std::vector<std::vector<std::vector<uint8_t>>> in_bufs(world);
+    for (auto& b : ins) in_bufs[b.rank].push_back(fill_box(b));
+    for (int r = 0; r < world; ++r) {
+      RedistributionPlan plan = plan_redistribution(shape, esz, ins, outs, r, world);
+      std::vector<std::vector<uint8_t>> out_bufs;
+      std::vector<std::vector<uint8_t>> written;
+      for (auto& b : plan.outputs[r]) {
+        out_bufs.emplace_back((size_t)b.numel() * esz, 0xEE);
+        written.emplace_back((size_t)b.numel() * esz, 0);
+      }
+      for (auto& pc : plan.pieces) {
+        CHECK(pc.src_rank >= 0 && pc.src_rank < world && pc.src_input < (int)in_bufs[pc.src_rank].size());
+        const auto& src = in_bufs[pc.src_rank][pc.src_input];
+        auto& dst = out_bufs[pc.dst_output];
+        for (uint64_t row = 0; row < pc.rows; ++row) {
+          uint64_t so = pc.src_offset + row * pc.src_pitch, dof = pc.dst_offset + row * pc.dst_pitch;
+          CHECK(so + pc.row_bytes <= src.size() && dof + pc.row_bytes <= dst.size());
+          if (so + pc.row_bytes > src.size() || dof + pc.row_bytes > dst.size()) return;
+          memcpy(&dst[dof], &src[so], pc.row_bytes);
+          for (uint64_t k = 0; k < pc.row_bytes; ++k) ++written[pc.dst_output][dof + k];
+        }
+      }
+      for (size_t j = 0; j < plan.outputs[r].size(); ++j) {
+        CHECK(out_bufs[j] == fill_box(plan.outputs[r][j]));
+        bool once = true;
+        for (uint8_t w : written[j]) once = once && w == 1;
+        CHECK(once);  // every byte written exactly once, replicated inputs included
+      }
+    }
+  }
+  // an output element nobody holds is an error
+  bool threw = false;
+  try {
+    BoxSpec in{0, {0}, {4}}, out{0, {0}, {8}};
+    plan_redistribution({8}, 4, {in}, {out}, 0, 1);
+  } catch (const std::exception&) {
+    threw = true;
+  }
+  CHECK(threw);
+}
+
 int main() {
   test_wire();
+  test_planner_random();
   test_topology();
   test_mr_table();
   test_reduce();
