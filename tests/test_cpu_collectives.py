@@ -69,7 +69,7 @@ def _collectives(rank, world, port, n):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,n", [(2, 1 << 20), (3, 12345), (1, 100)])
+@pytest.mark.parametrize("world,n", [(2, 1 << 20), (3, 12345), (1, 100), (8, 4097)])
 def test_cpu_collectives(world, n):
     run_ranks(_collectives, world, n, timeout=120)
 
