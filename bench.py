@@ -140,6 +140,24 @@ def main():
 
     tokens_per_step = world * seq
     value = tokens_per_step / (ms_per_step / 1e3)
+
+    def roofline():
+        """Model FLOPs per GPU and step against the measured cuBLAS rate of this pool (extra information only)."""
+        try:
+            hd = cfg.dim // cfg.n_heads
+            per_layer = cfg.dim * (cfg.n_heads + 2 * cfg.n_kv_heads) * hd + cfg.n_heads * hd * cfg.dim + 3 * cfg.dim * cfg.ffn_dim
+            matmul_params = cfg.n_layers * per_layer + cfg.vocab_size * cfg.dim
+            flops = 6.0 * matmul_params * seq + cfg.n_layers * 3.5 * 2.0 * seq * seq * cfg.dim  # causal attention, fwd + bwd
+            out = {"model_tflop_per_gpu_step": flops / 1e12, "achieved_tflops_per_gpu": flops / 1e12 / (ms_per_step / 1e3)}
+            peaks = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
+            if os.path.exists(peaks):
+                with open(peaks) as f:
+                    pk = json.load(f)
+                out["frac_of_measured_sustained_bf16"] = out["achieved_tflops_per_gpu"] / float(pk["bf16_tflops_sustained"])
+            return out
+        except Exception as e:  # never let the extra block break the result line
+            return {"error": str(e)}
+
     if rank == 0:
         out = {
             "metric": "FSDP2 Llama-3-8B training throughput",
@@ -179,6 +197,7 @@ def main():
             },
             "gpu_launches": int(launches),
             "final_loss": last,
+            "roofline": roofline(),
         }
         print(json.dumps(out))
     dist.barrier()
