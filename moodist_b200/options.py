@@ -2,7 +2,8 @@
 
 Option names are the reference's (``py/moodist/options.py:8-113``): ``prefer_kernel_less`` and
 ``force_kernel_less`` (bool), ``num_chunks``, ``chunk_size`` and ``method`` (int, ``None`` = automatic).
-Here ``method`` selects the kernel variant (0 = P2P kernels, 1 = NVLS multimem kernels).
+Here ``method`` selects the kernel family (0 = peer load/store kernels, 1 = NVLS multimem kernels, 2 = DMA copies
+between one-warp flag kernels).
 
     pg.options().method = 1
     with pg.options(prefer_kernel_less=True, num_chunks=2):
