@@ -406,20 +406,16 @@ class HostRedistributionImpl final : public HostRedistribution {
         if (pc.src_rank == p.rank) continue;
         const RemoteInput& ri = c.remote[pc.src_rank].at(pc.src_input);
         uint8_t* d = (uint8_t*)c.outputs[pc.dst_output] + pc.dst_offset;
-        bool contiguous = pc.rows == 1 || (pc.src_pitch == pc.row_bytes && pc.dst_pitch == pc.row_bytes);
-        uint64_t nreads = contiguous ? 1 : pc.rows;
-        uint64_t len = contiguous ? pc.rows * pc.row_bytes : pc.row_bytes;
-        for (uint64_t k = 0; k < nreads; ++k) {
-          ++c.reads_pending;
-          g_.post_read(pc.src_rank, d + k * pc.dst_pitch, len, ri.rkey, ri.addr + pc.src_offset + k * pc.src_pitch,
-                       [this, call](bool ok) {
-                         auto it = calls_state_.find(call);
-                         if (it == calls_state_.end()) return;
-                         if (!ok) it->second.failed = true;
-                         --it->second.reads_pending;
-                         progress(call);
-                       });
-        }
+        // a strided piece is one request: the peer streams the runs back to back, they are scattered on arrival
+        ++c.reads_pending;
+        g_.post_read_strided(pc.src_rank, d, pc.rows, pc.row_bytes, pc.dst_pitch, ri.rkey, ri.addr + pc.src_offset,
+                             pc.src_pitch, [this, call](bool ok) {
+                               auto it = calls_state_.find(call);
+                               if (it == calls_state_.end()) return;
+                               if (!ok) it->second.failed = true;
+                               --it->second.reads_pending;
+                               progress(call);
+                             });
       }
     }
     if (c.reads_pending > 0) return;

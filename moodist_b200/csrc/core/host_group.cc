@@ -340,6 +340,10 @@ class HostGroupImpl final : public HostGroup {
                  std::function<void(bool ok)> done) override {
     transport_.post_read(src, local, bytes, rkey, (uintptr_t)raddr, std::move(done));
   }
+  void post_read_strided(int src, void* local, uint64_t rows, size_t row_bytes, size_t dst_pitch, uint32_t rkey,
+                         uint64_t raddr, size_t src_pitch, std::function<void(bool ok)> done) override {
+    transport_.post_read_strided(src, local, rows, row_bytes, dst_pitch, rkey, (uintptr_t)raddr, src_pitch, std::move(done));
+  }
 
   bool in_error() const override { return error_state_.load(); }
   std::string error_text() const override {

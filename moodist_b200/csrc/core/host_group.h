@@ -89,6 +89,10 @@ class HostGroup {
   // One-sided read of a peer's registered memory (engine thread only). Register with MrTable.
   virtual void post_read(int src, void* local, size_t bytes, uint32_t rkey, uint64_t raddr,
                          std::function<void(bool ok)> done) = 0;
+  // The same for `rows` runs of `row_bytes` bytes, `src_pitch` apart at the peer, `dst_pitch` apart locally:
+  // one request, one reply.
+  virtual void post_read_strided(int src, void* local, uint64_t rows, size_t row_bytes, size_t dst_pitch, uint32_t rkey,
+                                 uint64_t raddr, size_t src_pitch, std::function<void(bool ok)> done) = 0;
 
   // ---- health ----
   virtual bool in_error() const = 0;

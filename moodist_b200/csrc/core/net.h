@@ -82,7 +82,10 @@ class Conn : public std::enable_shared_from_this<Conn> {
   bool closed_ = false, want_write_ = false, connecting_ = false;
   std::deque<Out> out_;
   size_t queued_ = 0;
-  Bytes inbuf_;
+  // receive buffer: raw storage (never zero-filled on growth) with `in_len_` valid bytes at its start
+  std::unique_ptr<uint8_t[]> in_mem_;
+  size_t in_cap_ = 0, in_len_ = 0;
+  int cork_ = 0;  // while > 0, send*() only queue; uncork() flushes (one writev for a header and its payload)
   uint8_t* direct_dst_ = nullptr;
   size_t direct_left_ = 0;
   std::function<void()> direct_done_;
@@ -92,6 +95,12 @@ class Conn : public std::enable_shared_from_this<Conn> {
   std::deque<int> received_fds_;
 
  public:
+  // Between cork() and the matching uncork() nothing is written to the socket; uncork() sends everything queued
+  // with as few system calls as possible. Calls nest.
+  void cork() { ++cork_; }
+  void uncork() {
+    if (cork_ > 0 && --cork_ == 0 && !connecting_ && !closed_) flush();
+  }
   // fds received with SCM_RIGHTS, in arrival order
   int take_fd() {
     if (received_fds_.empty()) return -1;

@@ -258,8 +258,10 @@ void TcpTransport::send_record(int peer, Bytes header, const void* payload, size
     p.backlog.push_back(Peer::Queued{std::move(header), payload, n, std::move(keep)});
     return;
   }
+  p.conn->cork();  // header and payload leave in one writev
   p.conn->send_frame(header);
   if (n) p.conn->send_ref(payload, n, std::move(keep));
+  p.conn->uncork();
   bytes_sent_ += header.size() + 8 + n;
 }
 
@@ -288,6 +290,30 @@ void TcpTransport::post_read(int dst, void* local, size_t bytes, uint32_t rkey, 
   uint64_t index = next_index_++;
   pending_[index] = Pending{std::move(done), local, bytes};
   send_record(dst, encode((uint8_t)kMsgRead, index, rkey, (uint64_t)raddr, (uint64_t)bytes), nullptr, 0, nullptr);
+}
+
+void TcpTransport::post_read_strided(int dst, void* local, uint64_t rows, size_t row_bytes, size_t dst_pitch, uint32_t rkey,
+                                     uintptr_t raddr, size_t src_pitch, Done done) {
+  if (rows <= 1 || (src_pitch == row_bytes && dst_pitch == row_bytes)) {
+    post_read(dst, local, (size_t)rows * row_bytes, rkey, raddr, std::move(done));
+    return;
+  }
+  if (dst == rank_) {
+    uint64_t span = (rows - 1) * (uint64_t)src_pitch + row_bytes;
+    uint8_t* s = (uint8_t*)MrTable::instance().check(rkey, raddr, span);
+    if (s)
+      for (uint64_t r = 0; r < rows; ++r) memcpy((uint8_t*)local + r * dst_pitch, s + r * src_pitch, row_bytes);
+    if (done) done(s != nullptr);
+    return;
+  }
+  uint64_t index = next_index_++;
+  Pending pend{std::move(done), local, (size_t)rows * row_bytes};
+  pend.rows = rows;
+  pend.row_bytes = row_bytes;
+  pend.dst_pitch = dst_pitch;
+  pending_[index] = std::move(pend);
+  send_record(dst, encode((uint8_t)kMsgReadStrided, index, rkey, (uint64_t)raddr, rows, (uint64_t)row_bytes, (uint64_t)src_pitch),
+              nullptr, 0, nullptr);
 }
 
 void TcpTransport::post_send(int dst, Bytes payload) {
@@ -378,6 +404,29 @@ void TcpTransport::handle_record(int peer, Reader& r) {
       send_record(peer, encode((uint8_t)kMsgReadSuccess, index, (uint64_t)bytes), src, bytes, nullptr);
       break;
     }
+    case kMsgReadStrided: {
+      uint64_t index, raddr, rows, row_bytes, src_pitch;
+      uint32_t rkey;
+      r(index, rkey, raddr, rows, row_bytes, src_pitch);
+      // the span the request touches, with overflow checks: (rows - 1) * src_pitch + row_bytes
+      uint64_t span = 0, total = 0;
+      bool bad = rows == 0 || row_bytes == 0 || __builtin_mul_overflow(rows - 1, src_pitch, &span) ||
+                 __builtin_add_overflow(span, row_bytes, &span) || __builtin_mul_overflow(rows, row_bytes, &total);
+      uint8_t* src = bad ? nullptr : (uint8_t*)MrTable::instance().check(rkey, (uintptr_t)raddr, span);
+      if (!src) {
+        log_error("tcp transport: rank %d strided read outside registered memory (key %u)", peer, rkey);
+        send_record(peer, encode((uint8_t)kMsgCompletionError, index), nullptr, 0, nullptr);
+        break;
+      }
+      Peer& q = *peers_[peer];
+      if (!q.ready || !q.conn || !q.conn->open()) break;  // the requester is gone
+      q.conn->cork();  // header and every run leave in as few writev calls as possible
+      q.conn->send_frame(encode((uint8_t)kMsgReadSuccess, index, total));
+      for (uint64_t k = 0; k < rows; ++k) q.conn->send_ref(src + k * src_pitch, (size_t)row_bytes, nullptr);
+      q.conn->uncork();
+      bytes_sent_ += total;
+      break;
+    }
     case kMsgReadSuccess: {
       uint64_t index, bytes;
       r(index, bytes);
@@ -392,10 +441,42 @@ void TcpTransport::handle_record(int peer, Reader& r) {
         bytes_recv_ += bytes;
         if (pend.done) pend.done(true);
       };
-      if (bytes == 0)
+      if (bytes == 0) {
         finish();
-      else
+      } else if (pend.rows <= 1) {
         p.conn->read_into(pend.local, bytes, finish);
+      } else {
+        // scatter the reply: one run at a time, each completion arms the next
+        struct Scatter {
+          std::shared_ptr<Conn> conn;
+          uint8_t* base;
+          uint64_t rows, k = 0;
+          size_t row_bytes, pitch;
+          std::function<void()> finish;
+          std::function<void()> step;
+        };
+        auto sc = std::make_shared<Scatter>();
+        sc->conn = p.conn;
+        sc->base = (uint8_t*)pend.local;
+        sc->rows = pend.rows;
+        sc->row_bytes = pend.row_bytes;
+        sc->pitch = pend.dst_pitch;
+        sc->finish = finish;
+        std::weak_ptr<Scatter> weak = sc;
+        sc->step = [weak] {
+          auto s = weak.lock();
+          if (!s) return;
+          if (++s->k == s->rows) {
+            auto fin = std::move(s->finish);
+            fin();
+            return;
+          }
+          auto keep = s;
+          s->conn->read_into(s->base + s->k * s->pitch, s->row_bytes, [keep] { keep->step(); });
+        };
+        auto keep = sc;
+        p.conn->read_into(sc->base, sc->row_bytes, [keep] { keep->step(); });
+      }
       break;
     }
     default:

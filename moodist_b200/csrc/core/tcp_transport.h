@@ -32,6 +32,9 @@ enum TcpMsg : uint8_t {
   kMsgSend = 4,
   kMsgRead = 5,
   kMsgReadSuccess = 6,
+  // extension (not in the reference's record set): one request for `rows` runs of `row_bytes` bytes that lie
+  // `src_pitch` apart; answered by one ReadSuccess whose payload is the runs back to back
+  kMsgReadStrided = 7,
 };
 
 // Process-global registered-memory table (reference: MrManager, core/rdma_tcp.cc:17-65).
@@ -71,6 +74,9 @@ class TcpTransport {
                   std::shared_ptr<void> keep = nullptr);
   // One-sided read of a peer's registered region into local memory.
   void post_read(int dst, void* local, size_t bytes, uint32_t rkey, uintptr_t raddr, Done done);
+  // rows x row_bytes from raddr + r * src_pitch into local + r * dst_pitch, one request and one reply
+  void post_read_strided(int dst, void* local, uint64_t rows, size_t row_bytes, size_t dst_pitch, uint32_t rkey,
+                         uintptr_t raddr, size_t src_pitch, Done done);
   // Two-sided message.
   void post_send(int dst, Bytes payload);
 
@@ -99,6 +105,8 @@ class TcpTransport {
     Done done;
     void* local = nullptr;
     size_t bytes = 0;
+    uint64_t rows = 1;        // > 1: the reply is scattered, row_bytes at a time, dst_pitch apart
+    size_t row_bytes = 0, dst_pitch = 0;
   };
   std::unordered_map<uint64_t, Pending> pending_;
   uint64_t bytes_sent_ = 0, bytes_recv_ = 0;
