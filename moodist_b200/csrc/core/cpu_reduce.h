@@ -4,6 +4,8 @@
 // PREMUL_SUM are folded into the final pass as a scale instead of a separate multiply over the output.
 #pragma once
 
+#include <type_traits>
+
 #include <cstddef>
 #include <cstdint>
 #include <cstring>
@@ -108,24 +110,44 @@ struct Traits<F16> {
   static void store(uint16_t* p, Acc v) { *p = float_to_f16(v); }
 };
 
+// Blocked, source-outer loops with the operation hoisted out of them, so that the compiler vectorises each pass;
+// a block's sources are all read before anything is stored, which keeps in-place use (out aliasing a source) valid.
 template <typename Tag, typename Elem>
 void reduce_typed(void* out, const void* const* srcs, int nsrc, size_t n, int op, double scale, bool use_scale) {
   using Tr = Traits<Tag>;
   using Acc = typename Tr::Acc;
+  constexpr size_t kBlock = 2048;
   Elem* o = static_cast<Elem*>(out);
-  for (size_t i = 0; i < n; ++i) {
-    Acc a = Tr::load(static_cast<const Elem*>(srcs[0]) + i);
+  Acc acc[kBlock];
+  for (size_t base = 0; base < n; base += kBlock) {
+    const size_t m = n - base < kBlock ? n - base : kBlock;
+    const Elem* s0 = static_cast<const Elem*>(srcs[0]) + base;
+    for (size_t i = 0; i < m; ++i) acc[i] = Tr::load(s0 + i);
     for (int r = 1; r < nsrc; ++r) {
-      Acc b = Tr::load(static_cast<const Elem*>(srcs[r]) + i);
-      if (op == kRedMin)
-        a = b < a ? b : a;
-      else if (op == kRedMax)
-        a = b > a ? b : a;
-      else
-        a = (Acc)(a + b);
+      const Elem* sr = static_cast<const Elem*>(srcs[r]) + base;
+      if (op == kRedMin) {
+        for (size_t i = 0; i < m; ++i) {
+          Acc b = Tr::load(sr + i);
+          acc[i] = b < acc[i] ? b : acc[i];
+        }
+      } else if (op == kRedMax) {
+        for (size_t i = 0; i < m; ++i) {
+          Acc b = Tr::load(sr + i);
+          acc[i] = b > acc[i] ? b : acc[i];
+        }
+      } else {
+        for (size_t i = 0; i < m; ++i) acc[i] = (Acc)(acc[i] + Tr::load(sr + i));
+      }
     }
-    if (use_scale) a = (Acc)(a * scale);
-    Tr::store(o + i, a);
+    if (use_scale) {
+      if constexpr (std::is_floating_point_v<Acc>) {
+        const Acc sc = (Acc)scale;
+        for (size_t i = 0; i < m; ++i) acc[i] *= sc;
+      } else {
+        for (size_t i = 0; i < m; ++i) acc[i] = (Acc)(acc[i] * scale);
+      }
+    }
+    for (size_t i = 0; i < m; ++i) Tr::store(o + base + i, acc[i]);
   }
 }
 }  // namespace detail

@@ -147,16 +147,49 @@ class HostGroupImpl final : public HostGroup {
     submit_and_wait(w);
   }
 
+  // Receive / intermediate buffers of the collectives: reused across calls (a fresh multi-megabyte vector per
+  // call costs its zero-fill and a page fault per 4 KiB). The buffer goes back to the pool when the last
+  // reference (the call, or a completion still running on the engine thread) lets go of it.
+  std::shared_ptr<Bytes> scratch(size_t bytes) {
+    std::unique_ptr<Bytes> buf;
+    std::shared_ptr<ScratchPool> pool = scratch_pool_;  // the deleter keeps the pool alive, not the group
+    {
+      std::lock_guard<std::mutex> lk(pool->mu);
+      auto& free = pool->free;
+      for (size_t i = 0; i < free.size(); ++i) {
+        if (free[i]->size() >= bytes) {
+          buf = std::move(free[i]);
+          free.erase(free.begin() + i);
+          break;
+        }
+      }
+      if (!buf && !free.empty()) {  // all too small: let one of them grow instead of keeping both
+        buf = std::move(free.back());
+        free.pop_back();
+      }
+    }
+    if (!buf) buf = std::make_unique<Bytes>();
+    if (buf->size() < bytes) buf->resize(bytes);
+    Bytes* raw = buf.release();
+    return std::shared_ptr<Bytes>(raw, [pool](Bytes* b) {
+      std::lock_guard<std::mutex> lk(pool->mu);
+      if (pool->free.size() < 4)
+        pool->free.emplace_back(b);
+      else
+        delete b;
+    });
+  }
+
   void reduce_scatter(const void* in, void* out, size_t count, int dtype, int op, double premul) override {
     size_t esz = cpu_dtype_size(dtype);
     if (!esz) fail("moodist: reduce_scatter: unsupported dtype for CPU tensors");
     check_op(op);
     size_t chunk = count * esz;
     const uint8_t* x = static_cast<const uint8_t*>(in);
-    auto tmp = std::make_shared<Bytes>(chunk * world_);
+    auto tmp = scratch(chunk * world_);
     auto w = new_work(kOpReduceScatterCpu, "reduce_scatter");
     w->recv_base = tmp->data();
-    w->recv_size = tmp->size();
+    w->recv_size = chunk * world_;
     w->expect_in = (uint64_t)chunk * (world_ - 1);
     for (int p = 0; p < world_; ++p)
       if (p != rank_) w->outs.push_back({p, x + (size_t)p * chunk, chunk, (uint64_t)rank_ * chunk});
@@ -186,9 +219,9 @@ class HostGroupImpl final : public HostGroup {
     size_t chunk = (count + world_ - 1) / world_;
     size_t padded = chunk * world_;
     if (padded == count) {
-      Bytes mine(chunk * esz);
-      reduce_scatter(in, mine.data(), chunk, dtype, op, premul);
-      all_gather(mine.data(), out, chunk * esz);
+      auto mine = scratch(chunk * esz);
+      reduce_scatter(in, mine->data(), chunk, dtype, op, premul);
+      all_gather(mine->data(), out, chunk * esz);
       return;
     }
     Bytes pin(padded * esz, 0), pout(padded * esz), mine(chunk * esz);
@@ -720,6 +753,11 @@ class HostGroupImpl final : public HostGroup {
   int rank_, world_;
   Poller poller_;
   TcpTransport transport_;
+  struct ScratchPool {
+    std::mutex mu;
+    std::vector<std::unique_ptr<Bytes>> free;
+  };
+  std::shared_ptr<ScratchPool> scratch_pool_ = std::make_shared<ScratchPool>();
   std::thread thread_;
   std::atomic<bool> stop_{false}, mesh_ready_{false}, error_state_{false}, busy_{false}, shutdown_started_{false};
   mutable std::mutex error_mu_;
