@@ -1,6 +1,13 @@
 """Headline benchmark: FSDP2 training throughput (tokens/s) of a Llama-3-8B-shaped decoder, bf16
 parameters with fp32 gradient reduction, 1 sequence x 8192 tokens per GPU, over the moodist backend.
 
+The default schedule is the re-gather one: parameters sharded by rows at rest, each block's weights gathered
+for its forward and again for its backward, the gathers of the QKV and gate/up weights fused into their GEMM
+kernels, gradients reduce-scattered per weight under the backward pass (`--schedule resident` keeps the
+gathered parameters on every GPU instead). With more than one GPU the run first checks every collective
+against a CPU oracle (`selfcheck`) and, after the timed region, measures the same model over NCCL twice
+(`vs_nccl`): this repository's engine on the nccl backend, and torch's `fully_shard` on the nccl backend.
+
     python bench.py --gpus 1 --steps 5 --warmup 3
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port P \
         bench.py --gpus 8 --steps 5 --warmup 3
@@ -39,6 +46,14 @@ def parse_args():
     ap.add_argument("--kernel-less", action="store_true",
                     help="collectives move their bytes with DMA copies between flag kernels (no SMs taken from the GEMMs)")
     ap.add_argument("--no-symmetric", action="store_true", help="keep gathered parameters out of the symmetric heap")
+    ap.add_argument("--schedule", default="regather", choices=["regather", "resident"],
+                    help="regather: sharded at rest, per-block gathers (FSDP2); resident: gathered parameters stay")
+    ap.add_argument("--no-fused", action="store_true", help="regather schedule without the all-gather GEMM")
+    ap.add_argument("--no-selfcheck", action="store_true", help="skip the collectives-against-CPU-oracle check (N > 1)")
+    ap.add_argument("--no-nccl-arms", action="store_true", help="skip the two NCCL comparison runs after the timed region")
+    ap.add_argument("--exposed", action="store_true",
+                    help="after the timed steps, run two more with CUDA events around every wait of the compute stream "
+                         "for the side stream and report the sum per step")
     return ap.parse_args()
 
 
@@ -60,8 +75,10 @@ def main():
     from moodist_b200.ops.gemm import gemm_launches as _gemm_launches
     from moodist_b200.ops.train import train_op_launches
 
+    from moodist_b200.ops.fused import fused_launches
+
     def gemm_launches():
-        return _gemm_launches() + train_op_launches()
+        return _gemm_launches() + train_op_launches() + fused_launches()
 
     from moodist_b200.parallel.fsdp import ShardedTrainer
     from moodist_b200.utils.clocks import ClockSampler
@@ -87,7 +104,19 @@ def main():
 
     cfg = LlamaConfig.llama3_8b() if args.model == "llama3-8b" else LlamaConfig.tiny()
     seq = min(args.seq_len, cfg.max_seq_len)
-    trainer = ShardedTrainer(cfg, seed=0, engine=args.engine, symmetric_memory=not args.no_symmetric)
+
+    selfcheck = None
+    if world > 1 and args.backend == "moodist" and not args.no_selfcheck:
+        from moodist_b200.utils.selfcheck import run_selfcheck
+
+        selfcheck = run_selfcheck(device=dev)
+        if not selfcheck["ok"]:
+            if rank == 0:
+                print(json.dumps({"selfcheck": selfcheck, "error": "collectives disagree with the CPU oracle"}))
+            raise SystemExit(3)
+
+    trainer = ShardedTrainer(cfg, seed=0, engine=args.engine, symmetric_memory=not args.no_symmetric,
+                             schedule=args.schedule, fused=not args.no_fused)
 
     def host_batch(i):
         g = torch.Generator().manual_seed(1000 * rank + i)
@@ -141,6 +170,64 @@ def main():
     tokens_per_step = world * seq
     value = tokens_per_step / (ms_per_step / 1e3)
 
+    fused_calls = getattr(trainer.engine, "fused_calls", 0) if trainer.engine is not None else 0
+    exposed = None
+    if args.exposed and trainer.engine is not None and hasattr(trainer.engine, "exposed_events"):
+        trainer.engine.exposed_events = []
+        for i in range(2):
+            trainer.step_on_device(dev_batches[args.warmup + i % args.steps])
+        trainer.engine.wait()
+        exposed = {"ms_per_step": trainer.engine.exposed_ms() / 2,
+                   "what": "time the compute stream waited for gathers / buffers of the side stream (CUDA events)"}
+        trainer.engine.exposed_events = None
+    op_stats = backend.stats(True) if args.backend == "moodist" and hasattr(backend, "stats") else None
+
+    # ---- the same model over NCCL, in this process, after the timed region ----
+    def nccl_arm(engine, schedule):
+        """tokens/s of `engine` over an nccl group of the same ranks (same steps, warm-up and timing rules)."""
+        g = dist.new_group(backend="nccl", device_id=dev)
+        t = ShardedTrainer(cfg, group=g, seed=0, engine=engine, schedule=schedule, symmetric_memory=False)
+        for i in range(args.warmup):
+            t.step_on_device(dev_batches[i])
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(args.steps):
+            t.step_on_device(dev_batches[args.warmup + i])
+        if t.engine is not None:
+            t.engine.wait()
+        b.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        m = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float32)
+        dist.all_reduce(m, op=dist.ReduceOp.MAX)
+        del t
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        return tokens_per_step / (m.item() / args.steps / 1e3)
+
+    vs_nccl = None
+    if world > 1 and args.backend == "moodist" and not args.no_nccl_arms:
+        vs_nccl = {}
+        del trainer
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        for key, (eng, sched) in {"same_engine_nccl": ("native", args.schedule), "torch_fsdp2_nccl": ("fsdp2", "regather")}.items():
+            try:
+                tps = nccl_arm(eng, sched)
+                vs_nccl[key + "_tokens_per_s"] = tps
+                vs_nccl["ratio_vs_" + key] = value / tps
+            except Exception as e:  # the headline stands without the comparison
+                vs_nccl[key + "_error"] = f"{type(e).__name__}: {e}"[:300]
+        vs_nccl["note"] = ("same steps / warm-up / timing; same_engine = this repository's model and sharding engine "
+                           "with nccl collectives (nothing fused); torch_fsdp2 = torch fully_shard per block, bf16 "
+                           "parameters and fp32 reduce, torch fused AdamW with the moments in bf16 like the engine's")
+
     def roofline():
         """Model FLOPs per GPU and step against the measured cuBLAS rate of this pool (extra information only)."""
         try:
@@ -160,7 +247,8 @@ def main():
 
     if rank == 0:
         out = {
-            "metric": "FSDP2 Llama-3-8B training throughput",
+            "metric": ("FSDP2 Llama-3-8B training throughput" if args.engine == "fsdp2" or args.schedule == "regather"
+                       else "ZeRO-2 (resident parameters) Llama-3-8B training throughput"),
             "value": value,
             "unit": "tokens/s",
             "n_gpus": world,
@@ -181,6 +269,9 @@ def main():
                 "seq_len": seq,
                 "parallelism": f"fsdp{world}",
                 "engine": args.engine,
+                "schedule": ("torch fully_shard" if args.engine == "fsdp2" else args.schedule),
+                "fused_all_gather_gemm": bool(fused_calls > 0),
+                "fused_all_gather_gemm_calls": int(fused_calls),
                 "kernel_less": bool(args.kernel_less),
                 "reduce_dtype": "fp32",
                 "optimizer": "AdamW, bf16 moments" + (" (flat-shard kernel)" if args.engine == "native" else " (torch fused)"),
@@ -199,6 +290,14 @@ def main():
             "final_loss": last,
             "roofline": roofline(),
         }
+        if selfcheck is not None:
+            out["selfcheck"] = selfcheck
+        if vs_nccl is not None:
+            out["vs_nccl"] = vs_nccl
+        if exposed is not None:
+            out["exposed_wait"] = exposed
+        if op_stats:
+            out["collective_stats"] = op_stats
         print(json.dumps(out))
     dist.barrier()
     dist.destroy_process_group()

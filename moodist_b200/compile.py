@@ -52,46 +52,51 @@ def _shard_box(dtensor) -> dict:
     return {"offset": offset, "shape": local}
 
 
+def _adopt(holder, key, value, what):
+    """Record the global shape / dtype the first DTensor brings; later ones must agree."""
+    if holder.get(key) is None:
+        holder[key] = value
+    elif holder[key] != value:
+        raise ValueError(f"compile_op: DTensors disagree on the global {what}: {holder[key]} here, {value} there")
+
+
 def _normalise(specs, holder):
     if specs is None:
         return None
     out = []
     for x in specs:
         if _is_dtensor(x):
-            shape, dtype = tuple(x.shape), x.dtype
-            if holder.get("shape") is None:
-                holder["shape"] = shape
-            elif tuple(holder["shape"]) != shape:
-                raise ValueError(f"All DTensors must have the same global shape, got {holder['shape']} and {shape}")
-            if holder.get("dtype") is None:
-                holder["dtype"] = dtype
-            elif holder["dtype"] != dtype:
-                raise ValueError(f"All DTensors must have the same dtype, got {holder['dtype']} and {dtype}")
+            _adopt(holder, "shape", tuple(x.shape), "shape")
+            _adopt(holder, "dtype", x.dtype, "dtype")
             out.append(_shard_box(x))
         else:
             out.append(x)
     return out
 
 
-def _check(specs, ndim):
+def _int_list(box, field, ndim, where):
+    if field not in box:
+        raise ValueError(f"compile_op: {where} has no '{field}' entry")
+    values = box[field]
+    if not isinstance(values, (tuple, list)):
+        raise TypeError(f"compile_op: '{field}' of {where} is a {type(values).__name__}; a list or tuple of ints is needed")
+    if len(values) != ndim:
+        raise ValueError(f"compile_op: '{field}' of {where} has {len(values)} entries for a {ndim}-d tensor")
+    for i, v in enumerate(values):
+        if not isinstance(v, int) or isinstance(v, bool):
+            raise TypeError(f"compile_op: {field}[{i}] of {where} is a {type(v).__name__}, not an int")
+    return tuple(values)
+
+
+def _check(specs, ndim, side):
     if not isinstance(specs, (tuple, list)):
-        raise TypeError(f"inputs/outputs must be a tuple or list, got {type(specs).__name__}")
+        raise TypeError(f"compile_op: {side} is a {type(specs).__name__}; pass a list of boxes (or None)")
     boxes = []
-    for x in specs:
-        if not isinstance(x, dict):
-            raise TypeError(f"each input/output spec must be a dict, got {type(x).__name__}")
-        for n in ("offset", "shape"):
-            if n not in x:
-                raise ValueError(f"'{n}' is missing for an input or output")
-            v = x[n]
-            if not isinstance(v, (tuple, list)):
-                raise TypeError(f"'{n}' must be a tuple or list, got {type(v).__name__}")
-            if len(v) != ndim:
-                raise ValueError(f"expected '{n}' with {ndim} dimensions, but got {len(v)}")
-            for i, z in enumerate(v):
-                if not isinstance(z, int):
-                    raise TypeError(f"{n}[{i}] must be an int, got {type(z).__name__}")
-        boxes.append((tuple(x["offset"]), tuple(x["shape"])))
+    for index, box in enumerate(specs):
+        where = f"{side}[{index}]"
+        if not isinstance(box, dict):
+            raise TypeError(f"compile_op: {where} is a {type(box).__name__}; a box is a dict with 'offset' and 'shape'")
+        boxes.append((_int_list(box, "offset", ndim, where), _int_list(box, "shape", ndim, where)))
     return tuple(boxes)
 
 
@@ -106,7 +111,7 @@ def _backend_of(group):
                 continue
             if hasattr(b, "compile_op_full"):
                 return b
-    raise RuntimeError(f"moodist.compile_op needs a moodist process group, got {type(group)}")
+    raise RuntimeError(f"compile_op: {type(group).__name__} is not a moodist process group")
 
 
 def compile_op(group, shape=None, dtype=None, inputs=None, outputs=None):
@@ -122,20 +127,19 @@ def compile_op(group, shape=None, dtype=None, inputs=None, outputs=None):
     inputs = _normalise(inputs, holder)
     outputs = _normalise(outputs, holder)
     shape, dtype = holder["shape"], holder["dtype"]
-    if shape is None:
-        raise ValueError("shape must be provided or derivable from DTensors")
-    if dtype is None:
-        raise ValueError("dtype must be provided or derivable from DTensors")
+    if shape is None or dtype is None:
+        missing = "shape" if shape is None else "dtype"
+        raise ValueError(f"compile_op: give the global {missing}, or pass DTensors that carry it")
     if not isinstance(dtype, torch.dtype):
-        raise TypeError(f"dtype must be a torch.dtype, got {type(dtype).__name__}")
+        raise TypeError(f"compile_op: dtype is a {type(dtype).__name__}, not a torch.dtype")
     shape = tuple(shape)
     for i, x in enumerate(shape):
-        if not isinstance(x, int):
-            raise TypeError(f"shape[{i}] must be an int, got {type(x).__name__}")
+        if not isinstance(x, int) or isinstance(x, bool):
+            raise TypeError(f"compile_op: shape[{i}] is a {type(x).__name__}, not an int")
     if inputs is not None:
-        inputs = _check(inputs, len(shape))
+        inputs = _check(inputs, len(shape), "inputs")
     if outputs is not None:
-        outputs = _check(outputs, len(shape))
+        outputs = _check(outputs, len(shape), "outputs")
 
     queue = _queues.get(pg)
     if queue is None:
@@ -148,9 +152,9 @@ def compile_op(group, shape=None, dtype=None, inputs=None, outputs=None):
     for _ in range(pg.size()):
         source_rank, nshape, ndtype, ninput, noutput = queue.get_object()
         if tuple(nshape) != shape:
-            raise ValueError(f"moodist.compile_op: Ranks specified different shapes: {shape} vs {nshape}")
+            raise ValueError(f"compile_op: rank {source_rank} describes a {tuple(nshape)} tensor, this rank a {shape} one")
         if ndtype != str(dtype):
-            raise ValueError(f"moodist.compile_op: Ranks specified different dtypes: {dtype} vs {ndtype}")
+            raise ValueError(f"compile_op: rank {source_rank} describes {ndtype} data, this rank {dtype}")
         for o, s in ninput or ():
             all_inputs.append((source_rank, list(o), list(s)))
         for o, s in noutput or ():

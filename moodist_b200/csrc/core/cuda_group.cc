@@ -5,7 +5,10 @@
 #include <algorithm>
 #include <atomic>
 #include <cstring>
+#include <fstream>
+#include <map>
 #include <mutex>
+#include <sstream>
 
 #include "kernels/kernels_api.h"
 #include "log.h"
@@ -49,6 +52,75 @@ std::string status_text(uint32_t st) {
   return strf("moodist: collective failed on the device: %s (code 0x%x, peer rank %u)", what, code, peer);
 }
 
+}  // namespace
+
+// MOODIST_VARIANT_TABLE names a JSON file {"<world size>": {"MOODIST_...": <integer>, ...}, ...} written by
+// `python -m moodist_b200.utils.tuning sweep.jsonl --table FILE` from a sweep on the machine at hand. Only this
+// shape is understood: one object of objects of integers.
+std::map<std::string, long> load_variant_table(const std::string& path, int world) {
+  std::map<std::string, long> out;
+  std::ifstream f(path);
+  if (!f) {
+    log_error("MOODIST_VARIANT_TABLE: cannot read %s; built-in thresholds stay", path.c_str());
+    return out;
+  }
+  std::stringstream ss;
+  ss << f.rdbuf();
+  const std::string t = ss.str();
+  size_t i = 0;
+  auto skip = [&] { while (i < t.size() && (isspace((unsigned char)t[i]) || t[i] == ',')) ++i; };
+  auto str = [&](std::string& v) {
+    skip();
+    if (i >= t.size() || t[i] != '"') return false;
+    size_t e = t.find('"', i + 1);
+    if (e == std::string::npos) return false;
+    v = t.substr(i + 1, e - i - 1);
+    i = e + 1;
+    return true;
+  };
+  auto expect = [&](char ch) {
+    skip();
+    if (i < t.size() && t[i] == ch) {
+      ++i;
+      return true;
+    }
+    return false;
+  };
+  bool ok = expect('{');
+  const std::string want = std::to_string(world);
+  while (ok) {
+    std::string key;
+    if (!str(key)) break;
+    ok = expect(':') && expect('{');
+    while (ok) {
+      std::string name;
+      if (!str(name)) break;
+      if (!expect(':')) {
+        ok = false;
+        break;
+      }
+      skip();
+      char* end = nullptr;
+      long v = strtol(t.c_str() + i, &end, 10);
+      if (end == t.c_str() + i) {
+        ok = false;
+        break;
+      }
+      i = (size_t)(end - t.c_str());
+      if (key == want) out[name] = v;
+    }
+    ok = ok && expect('}');
+  }
+  if (!ok) {
+    log_error("MOODIST_VARIANT_TABLE: %s is not {\"world\": {\"NAME\": integer}}; built-in thresholds stay",
+              path.c_str());
+    out.clear();
+  }
+  return out;
+}
+
+namespace {
+
 class CudaGroupImpl final : public CudaGroup {
  public:
   CudaGroupImpl(KVStore& store, const std::string& key, int rank, int world, int device)
@@ -62,27 +134,30 @@ class CudaGroupImpl final : public CudaGroup {
     comm_.wait_ns = (uint64_t)env_long("MOODIST_DEVICE_TIMEOUT_MS", 30000) * 1000000ull;
     comm_.max_ctas = (int)env_long("MOODIST_MAX_CTAS", 0);
     comm_.tuning = env_long("MOODIST_AG_STAGGER", 1) ? MB_TUNE_STAGGER : 0;
-    push_bytes_ = (size_t)env_long("MOODIST_AG_PUSH_BYTES", 1 << 20);
+    if (const char* tp = getenv("MOODIST_VARIANT_TABLE"); tp && *tp) table_ = load_variant_table(tp, world);
+    stats_every_ = (int)env_long("MOODIST_STATS_SAMPLE", 64);
+    push_bytes_ = (size_t)threshold("MOODIST_AG_PUSH_BYTES", 1 << 20);
     // Pushing large shards (two pipelined halves per CTA) beat the pull on 2 GPUs from 32 MiB up (447 vs 421 GB/s)
     // but lost on 8 (456-499 vs 557-597 GB/s: seven incoming write streams per GPU plus the copy out of
     // staging), so it stays off unless asked for.
-    push_large_ = env_long("MOODIST_AG_PUSH_LARGE_BYTES", -1);
+    push_large_ = threshold("MOODIST_AG_PUSH_LARGE_BYTES", -1);
     // Copy-engine variant (DMA copies between one-warp flag kernels): taken from this many bytes per rank up
     // when the group prefers kernel-less transfers, always when it is forced, and on its own from
     // MOODIST_CE_AUTO_BYTES up (-1: never on its own).
-    ce_min_ = env_long("MOODIST_CE_MIN_BYTES", 1 << 20);
+    ce_min_ = threshold("MOODIST_CE_MIN_BYTES", 1 << 20);
     // measured on 8 GPUs: the DMA all-gather reaches 612-683 GB/s from 64 MiB per rank up (pull kernel 557-597,
     // NCCL 600-664); the DMA reduce-scatter (544 GB/s) stays behind the kernel (605-637), so only the all-gather
     // switches on its own
-    ce_auto_ = env_long("MOODIST_CE_AUTO_BYTES", 48 << 20);
-    ce_auto_rs_ = env_long("MOODIST_CE_AUTO_RS_BYTES", -1);
-    ar_compose_ = env_long("MOODIST_AR_COMPOSE_BYTES", -1);
+    ce_auto_ = threshold("MOODIST_CE_AUTO_BYTES", 48 << 20);
+    ce_auto_rs_ = threshold("MOODIST_CE_AUTO_RS_BYTES", -1);
+    ar_compose_ = threshold("MOODIST_AR_COMPOSE_BYTES", -1);
     // smallest message (bytes) for which the NVLS variant is picked automatically; -1 = never
-    nvls_ar_min_ = env_long("MOODIST_NVLS_AR_MIN_BYTES", 2 << 20);
-    nvls_rs_min_ = env_long("MOODIST_NVLS_RS_MIN_BYTES", -1);
+    nvls_ar_min_ = threshold("MOODIST_NVLS_AR_MIN_BYTES", 2 << 20);
+    nvls_rs_min_ = threshold("MOODIST_NVLS_RS_MIN_BYTES", -1);
     // measured on 8 GPUs: the multimem.st all-gather wins between 32 KiB and ~2 MiB per rank, the P2P pull above
-    nvls_ag_min_ = env_long("MOODIST_NVLS_AG_MIN_BYTES", 32 << 10);
-    nvls_ag_max_ = env_long("MOODIST_NVLS_AG_MAX_BYTES", 3 << 20);
+    nvls_ag_min_ = threshold("MOODIST_NVLS_AG_MIN_BYTES", 32 << 10);
+    nvls_ag_max_ = threshold("MOODIST_NVLS_AG_MAX_BYTES", 3 << 20);
+    ar_oneshot_ = threshold("MOODIST_AR_ONESHOT_BYTES", 2 << 20);
     RT_CHECK(cudaHostAlloc((void**)&status_host_, 64, cudaHostAllocMapped));
     memset((void*)status_host_, 0, 64);
     void* dptr = nullptr;
@@ -113,6 +188,11 @@ class CudaGroupImpl final : public CudaGroup {
   ~CudaGroupImpl() override {
     cudaSetDevice(device_);
     cudaDeviceSynchronize();
+    for (auto& [name, st] : stats_)
+      for (auto& pr : st.pending) {
+        cudaEventDestroy(pr.first);
+        cudaEventDestroy(pr.second);
+      }
     if (attached_) heap_->detach_group(key_);
     if (order_) cudaEventDestroy(order_);
     if (scratch_) cudaFree(scratch_);
@@ -209,6 +289,86 @@ class CudaGroupImpl final : public CudaGroup {
     }
   }
 
+  // A threshold comes from the environment when the variable is set, else from the measured table loaded at
+  // group creation (MOODIST_VARIANT_TABLE), else from the built-in value.
+  long threshold(const char* name, long dflt) const {
+    if (getenv(name)) return env_long(name, dflt);
+    auto it = table_.find(name);
+    return it == table_.end() ? dflt : it->second;
+  }
+
+  // ---- per-op counters: calls, bytes, kernel family chosen, and device time of every k-th call ----
+  struct Stat {
+    uint64_t calls = 0, bytes = 0, timed = 0;
+    double us = 0;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending;
+  };
+  class OpScope {
+   public:
+    OpScope(CudaGroupImpl* g, const char* op, const char* variant, size_t bytes, CUstream_st* s) : g_(g), s_(s) {
+      st_ = &g->stats_[std::string(op) + "/" + variant];
+      st_->calls++;
+      st_->bytes += bytes;
+      if (g->stats_every_ > 0 && st_->calls % (uint64_t)g->stats_every_ == 1 && st_->pending.size() < 64) {
+        if (cudaEventCreate(&a_) == cudaSuccess && cudaEventCreate(&b_) == cudaSuccess) {
+          timed_ = true;
+          // the ordering wait that next_seq may add belongs to the op's cost as its caller sees it
+          cudaEventRecord(a_, (cudaStream_t)s);
+        }
+      }
+    }
+    ~OpScope() {
+      if (timed_) {
+        cudaEventRecord(b_, (cudaStream_t)s_);
+        st_->pending.emplace_back(a_, b_);
+      }
+    }
+
+   private:
+    CudaGroupImpl* g_;
+    Stat* st_;
+    CUstream_st* s_;
+    cudaEvent_t a_ = nullptr, b_ = nullptr;
+    bool timed_ = false;
+  };
+  void drain(Stat& st, bool wait) {
+    auto it = st.pending.begin();
+    while (it != st.pending.end()) {
+      if (wait) cudaEventSynchronize(it->second);
+      float ms = 0;
+      if (cudaEventQuery(it->second) == cudaSuccess && cudaEventElapsedTime(&ms, it->first, it->second) == cudaSuccess) {
+        st.us += ms * 1e3;
+        st.timed++;
+        cudaEventDestroy(it->first);
+        cudaEventDestroy(it->second);
+        it = st.pending.erase(it);
+      } else {
+        ++it;
+      }
+    }
+  }
+  std::vector<OpStat> stats(bool wait) override {
+    std::lock_guard<std::mutex> lk(mu_);
+    std::vector<OpStat> out;
+    for (auto& [name, st] : stats_) {
+      drain(st, wait);
+      out.push_back(OpStat{name, st.calls, st.bytes, st.timed, st.us});
+    }
+    return out;
+  }
+  void note_op(const char* op, const char* variant, size_t bytes) override {
+    std::lock_guard<std::mutex> lk(mu_);
+    Stat& st = stats_[std::string(op) + "/" + variant];
+    st.calls++;
+    st.bytes += bytes;
+  }
+
+  void note(const char* op, const char* variant, size_t bytes) {  // mu_ held
+    Stat& st = stats_[std::string(op) + "/" + variant];
+    st.calls++;
+    st.bytes += bytes;
+  }
+
   int64_t heap_off(const void* p, size_t bytes) const {
     if (!heap_ || opts_.force_kernel_less == 2) return -1;
     return heap_->offset_of(p, bytes);
@@ -292,32 +452,40 @@ class CudaGroupImpl final : public CudaGroup {
     std::lock_guard<std::mutex> lk(mu_);
     all_gather_locked(in, out, count, idt, odt, s);
   }
+  // Which kernel family runs, and into how many pieces a call is split, depends only on values every rank
+  // shares (element count, dtypes, group options, thresholds): ranks that decided differently would launch
+  // kernels that wait for each other's flags in different places. Whether THIS rank's tensor lies in the
+  // symmetric heap only selects a mode inside the chosen kernel, which every kernel announces to its peers.
   void all_gather_locked(const void* in, void* out, size_t count, int idt, int odt, CUstream_st* s) {
     size_t osz = mb_dtype_size(odt), isz = mb_dtype_size(idt);
     if (!osz || !isz) fail("moodist: all_gather: unsupported dtype");
     if (count == 0) return;
     if (idt == odt && want_ce(count * isz, ce_auto_)) {
+      OpScope sc(this, "all_gather", "copy_engine", count * isz, s);
       all_gather_ce((const uint8_t*)in, (uint8_t*)out, count, isz, s);
       return;
     }
-    int64_t off = idt == odt ? heap_off(in, count * isz) : -1;
-    if (idt == odt && off < 0 && world_ > 1 && want_nvls(nvls_ag_min_, count * isz) &&
+    if (idt == odt && world_ > 1 && want_nvls(nvls_ag_min_, count * isz) &&
         (opts_.method == 1 || nvls_ag_max_ < 0 || count * isz <= (size_t)nvls_ag_max_) &&
         (size_t)world_ * count * isz <= comm_.staging_bytes / 2) {
+      OpScope sc(this, "all_gather", "nvls", count * isz, s);
       uint32_t seq = next_seq(s);
       run(mb_all_gather_nvls(&comm_, seq, in, out, count * isz, count * isz, s), "all_gather (NVLS)");
       finish_op(s);
       return;
     }
-    const bool push = off < 0 && (count * osz <= push_bytes_ || (push_large_ >= 0 && count * osz >= (size_t)push_large_));
-    if (push) off = -2;
+    const bool push_class = count * osz <= push_bytes_ || (push_large_ >= 0 && count * osz >= (size_t)push_large_);
+    // this rank's mode inside the P2P kernel: read in place from the heap, pushed, or staged and pulled
+    int64_t off = idt == odt ? heap_off(in, count * isz) : -1;
+    if (off < 0 && push_class) off = -2;
     size_t half = comm_.staging_bytes / 2;
     size_t piece = count;
-    if (world_ > 1 && push && (size_t)world_ * count * osz > half) {
+    if (world_ > 1 && push_class && (size_t)world_ * count * osz > half) {
       piece = (half / ((size_t)world_ * osz)) & ~(size_t)63;  // every peer's slot of a piece fits one half
-    } else if (world_ > 1 && off == -1 && count * osz > half) {
+    } else if (world_ > 1 && !push_class && count * osz > half) {
       piece = (half / osz) & ~(size_t)63;
     }
+    OpScope sc(this, "all_gather", world_ == 1 ? "local" : (push_class ? "p2p_push" : "p2p_pull"), count * isz, s);
     for (size_t done = 0; done < count; done += piece) {
       size_t n = std::min(piece, count - done);
       uint32_t seq = next_seq(s);
@@ -341,22 +509,25 @@ class CudaGroupImpl final : public CudaGroup {
     const bool ce_types = (idt == odt && (idt == MB_F32 || idt == MB_BF16 || idt == MB_F16)) ||
                           (idt == MB_BF16 && odt == MB_F32) || (idt == MB_F32 && odt == MB_BF16);
     if (ce_types && want_ce(count * isz, ce_auto_rs_)) {
+      OpScope sc(this, "reduce_scatter", "copy_engine", count * isz * world_, s);
       reduce_scatter_ce((const uint8_t*)in, (uint8_t*)out, count, idt, odt, op, premul, s);
       return;
     }
-    int64_t off = heap_off(in, count * isz * world_);
     size_t half = comm_.staging_bytes / 2;
     size_t piece = count;
-    if (world_ > 1 && off < 0 && want_nvls(nvls_rs_min_, count * isz) && (size_t)world_ * count * isz <= half &&
+    // pointer alignment is a per-rank fact: the NVLS kernel copes with any on its own (see the all-gather note)
+    if (world_ > 1 && want_nvls(nvls_rs_min_, count * isz) && (size_t)world_ * count * isz <= half &&
         (idt == MB_F32 || idt == MB_BF16) && (odt == MB_F32 || odt == MB_BF16) &&
-        (op == MB_SUM || op == MB_AVG || op == MB_PREMUL_SUM) && (count * isz) % 16 == 0 &&
-        (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+        (op == MB_SUM || op == MB_AVG || op == MB_PREMUL_SUM) && (count * isz) % 16 == 0) {
+      OpScope sc(this, "reduce_scatter", "nvls", count * isz * world_, s);
       uint32_t seq = next_seq(s);
       run(mb_reduce_scatter_nvls(&comm_, seq, in, out, count, count, idt, odt, op, premul, s), "reduce_scatter (NVLS)");
       finish_op(s);
       return;
     }
-    if (world_ > 1 && off < 0 && count * isz * world_ > half) piece = (half / (isz * world_)) & ~(size_t)63;
+    int64_t off = heap_off(in, count * isz * world_);
+    if (world_ > 1 && count * isz * world_ > half) piece = (half / (isz * world_)) & ~(size_t)63;
+    OpScope sc(this, "reduce_scatter", world_ == 1 ? "local" : "p2p", count * isz * world_, s);
     for (size_t done = 0; done < count; done += piece) {
       size_t n = std::min(piece, count - done);
       uint32_t seq = next_seq(s);
@@ -377,8 +548,8 @@ class CudaGroupImpl final : public CudaGroup {
     // 612-683 GB/s) this should give 609-638 GB/s bus bandwidth against 574-586 for the NVLS kernel; it stays
     // off until that is measured as a whole.
     if (ar_compose_ >= 0 && world_ > 1 && count * sz >= (size_t)ar_compose_ && count % (size_t)world_ == 0 &&
-        ((count / world_) * sz) % 16 == 0 && (op == MB_SUM || op == MB_AVG || op == MB_PREMUL_SUM) &&
-        (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+        ((count / world_) * sz) % 16 == 0 && (op == MB_SUM || op == MB_AVG || op == MB_PREMUL_SUM)) {
+      note("all_reduce", "composed", count * sz);
       const size_t chunk = count / world_;
       uint8_t* mine = (uint8_t*)out + (size_t)rank_ * chunk * sz;
       reduce_scatter_locked(in, mine, chunk, dt, dt, op, premul, s);
@@ -386,7 +557,7 @@ class CudaGroupImpl final : public CudaGroup {
       return;
     }
     size_t half = comm_.staging_bytes / 2;
-    size_t oneshot_max = (size_t)env_long("MOODIST_AR_ONESHOT_BYTES", 2 << 20);
+    size_t oneshot_max = (size_t)ar_oneshot_;
     // two-shot needs 2*world*chunk bytes of the half; keep pieces well inside
     size_t piece = count;
     if (world_ > 1 && count * sz * 2 + (size_t)world_ * 2 * 64 * sz > half)
@@ -395,8 +566,9 @@ class CudaGroupImpl final : public CudaGroup {
       size_t n = std::min(piece, count - done);
       int variant = (n * sz <= oneshot_max) ? 0 : 1;
       bool nvls = world_ > 1 && want_nvls(nvls_ar_min_, n * sz) && (dt == MB_F32 || dt == MB_BF16) &&
-                  (op == MB_SUM || op == MB_AVG || op == MB_PREMUL_SUM) &&
-                  ((((uintptr_t)in + done * sz) | ((uintptr_t)out + done * sz)) & 15) == 0;
+                  (op == MB_SUM || op == MB_AVG || op == MB_PREMUL_SUM);
+      OpScope sc(this, "all_reduce", world_ == 1 ? "local" : (nvls ? "nvls" : (variant == 0 ? "p2p_oneshot" : "p2p_twoshot")),
+                 n * sz, s);
       uint32_t seq = next_seq(s);
       if (nvls)
         run(mb_all_reduce_nvls(&comm_, seq, (const uint8_t*)in + done * sz, (uint8_t*)out + done * sz, n, dt, op, premul, s),
@@ -414,6 +586,7 @@ class CudaGroupImpl final : public CudaGroup {
     if (bytes == 0 || world_ == 1) return;
     size_t half = comm_.staging_bytes / 2;
     size_t piece = std::min(bytes, half & ~(size_t)1023);
+    OpScope sc(this, "broadcast", "p2p_pull", bytes, s);
     for (size_t done = 0; done < bytes; done += piece) {
       size_t n = std::min(piece, bytes - done);
       uint32_t seq = next_seq(s);
@@ -437,6 +610,9 @@ class CudaGroupImpl final : public CudaGroup {
     }
     // senders write straight into the output when it lives in the symmetric heap, else into staging
     int64_t off = heap_off(out, total);
+    size_t sent = 0;
+    for (int r = 0; r < world_; ++r) sent += send_bytes[r];
+    OpScope sc(this, "all_to_all", "p2p_push", sent, s);
     uint32_t seq = next_seq(s);
     run(mb_all_to_all(&comm_, seq, in, off, out, &tab, s), "all_to_all");
     finish_op(s);
@@ -444,6 +620,7 @@ class CudaGroupImpl final : public CudaGroup {
 
   void barrier(CUstream_st* s) override {
     std::lock_guard<std::mutex> lk(mu_);
+    OpScope sc(this, "barrier", "flags", 0, s);
     uint32_t seq = next_seq(s);
     run(mb_barrier(&comm_, seq, s), "barrier");
     finish_op(s);
@@ -473,6 +650,10 @@ class CudaGroupImpl final : public CudaGroup {
   int numa_node_ = -1;
   uint64_t ce_copies_ = 0;
   long nvls_ar_min_ = -1, nvls_rs_min_ = -1, nvls_ag_min_ = -1, nvls_ag_max_ = -1;
+  long ar_oneshot_ = 2 << 20;
+  int stats_every_ = 64;
+  std::map<std::string, long> table_;
+  std::map<std::string, Stat> stats_;
   uint64_t launches_ = 0;
   void* scratch_ = nullptr;
   size_t scratch_bytes_ = 0;

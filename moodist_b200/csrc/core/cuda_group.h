@@ -11,7 +11,9 @@
 #include <cstddef>
 #include <cstdint>
 #include <memory>
+#include <map>
 #include <string>
+#include <vector>
 
 #include "kvstore.h"
 
@@ -28,11 +30,18 @@ struct GroupOptions {
   int method = -1;  // -1 auto, 0 P2P kernels, 1 NVLS kernels, 2 copy engine (DMA copies between flag kernels)
 };
 
-struct OpCounters {
+// One row of CudaGroup::stats(): an operation and the kernel family that served it ("all_gather/nvls").
+struct OpStat {
+  std::string name;
   uint64_t calls = 0;
-  uint64_t bytes = 0;
-  uint64_t launches = 0;
+  uint64_t bytes = 0;        // payload bytes of all calls
+  uint64_t timed_calls = 0;  // calls whose device time was sampled (every MOODIST_STATS_SAMPLE-th, default 64)
+  double device_us = 0;      // summed device time of the sampled calls
 };
+
+// Thresholds for `world` ranks from a MOODIST_VARIANT_TABLE file ({"<world>": {"MOODIST_...": integer}});
+// empty when the file is missing or malformed (an error is logged and the built-in values stay).
+std::map<std::string, long> load_variant_table(const std::string& path, int world);
 
 class CudaGroup {
  public:
@@ -66,6 +75,10 @@ class CudaGroup {
   // Throws moodist::Error if a device-side wait ran out since the last check.
   virtual void check_status() = 0;
   virtual uint64_t launches() const = 0;                // kernels launched by this group so far
+  // Per-op counters (the reference keeps byte counters per group, core/group.h:217-232). wait: block until the
+  // sampled event pairs still in flight have finished.
+  virtual std::vector<OpStat> stats(bool wait) = 0;
+  virtual void note_op(const char* op, const char* variant, size_t bytes) = 0;  // for ops launched by the glue
   virtual std::string describe() const = 0;
 };
 

@@ -77,26 +77,6 @@ bool recv_all(int fd, void* p, size_t n) {
   return true;
 }
 
-bool send_msg_with_fd(int sock, const Msg& m, int fd) {
-  iovec iov{const_cast<Msg*>(&m), sizeof(m)};
-  alignas(cmsghdr) char ctrl[CMSG_SPACE(sizeof(int))] = {};
-  msghdr mh{};
-  mh.msg_iov = &iov;
-  mh.msg_iovlen = 1;
-  mh.msg_control = ctrl;
-  mh.msg_controllen = sizeof(ctrl);
-  cmsghdr* c = CMSG_FIRSTHDR(&mh);
-  c->cmsg_level = SOL_SOCKET;
-  c->cmsg_type = SCM_RIGHTS;
-  c->cmsg_len = CMSG_LEN(sizeof(int));
-  memcpy(CMSG_DATA(c), &fd, sizeof(int));
-  ssize_t r;
-  do {
-    r = sendmsg(sock, &mh, MSG_NOSIGNAL);
-  } while (r < 0 && errno == EINTR);
-  return r == (ssize_t)sizeof(m);
-}
-
 // receives exactly one Msg; the fd (if any) arrives with the first byte
 bool recv_msg_with_fd(int sock, Msg& m, int& fd) {
   fd = -1;
@@ -143,10 +123,12 @@ struct PeerInfo {
   std::string uid;
   std::string sock;
   std::map<size_t, bool> sent;  // chunk offsets already delivered
+  int groups = 0;               // attached groups that include this peer; the entry goes with the last one
 };
 
 struct GroupState {
   Chunk chunk;
+  std::vector<std::string> peer_uids;
   CUmemGenericAllocationHandle mc_handle = 0;
   CUdeviceptr mc_va = 0;
   size_t mc_size = 0;
@@ -298,11 +280,15 @@ class SymmHeapImpl final : public SymmHeap {
         PeerInfo& pi = peers_[uids[r]];
         pi.uid = uids[r];
         pi.sock = socks[r];
+        pi.groups++;
+        gs.peer_uids.push_back(uids[r]);
         {
           std::lock_guard<std::mutex> lk2(mirror_mu_);
           ensure_mirror_locked(uids[r]);
         }
-        for (auto& [off, ch] : chunks_) deliver_locked(pi, ch);
+        for (auto& [off, ch] : chunks_)
+          if (!deliver_locked(pi, ch, kAttachConnectSeconds))
+            fail("symm heap: peer " + pi.uid + " did not map a chunk (is the process alive?)");
       }
       // 4. this rank's flag page + staging chunk (delivered to all known peers by grow_locked)
       if (!grow_locked(chunk_bytes, true, &gs.chunk)) fail("symm heap: cannot allocate group staging memory");
@@ -420,6 +406,12 @@ class SymmHeapImpl final : public SymmHeap {
     if (gs.bound) cu.cuMulticastUnbind(gs.mc_handle, cudev_, 0, gs.mc_size);
     if (gs.mc_handle) cu.cuMemRelease(gs.mc_handle);
     // The chunk itself stays mapped: peers may hold its mapping and the range is never reused.
+    // A peer that no attached group includes any more is forgotten: later heap growth must not try to reach
+    // a process that may have exited (it would sit in connect() while holding the heap's mutex).
+    for (const std::string& uid : gs.peer_uids) {
+      auto pit = peers_.find(uid);
+      if (pit != peers_.end() && --pit->second.groups <= 0) peers_.erase(pit);
+    }
     groups_.erase(it);
   }
 
@@ -485,13 +477,28 @@ class SymmHeapImpl final : public SymmHeap {
       }
       free_[off] = sz;
     }
-    for (auto& [uid, pi] : peers_) deliver_locked(pi, ch);
+    // A peer that cannot be reached any more (its process is gone) is dropped with an error in the log: the
+    // chunk is mapped and usable here, and the groups that included that peer fail at their next collective
+    // on their own. Growing the heap is called from the allocator, where throwing would leak the chunk.
+    for (auto it = peers_.begin(); it != peers_.end();) {
+      if (deliver_locked(it->second, ch, kGrowConnectSeconds)) {
+        ++it;
+      } else {
+        log_error("symm heap: peer %s did not map a new chunk (process gone?); it is dropped from this heap",
+                  it->first.c_str());
+        it = peers_.erase(it);
+      }
+    }
     if (out) *out = ch;
     return true;
   }
 
-  void deliver_locked(PeerInfo& pi, const Chunk& ch) {
-    if (pi.sent.count(ch.offset)) return;
+  // While a group forms, a peer's server may still be starting: wait long. Later the peer either answers at
+  // once or is gone.
+  static constexpr double kAttachConnectSeconds = 60, kGrowConnectSeconds = 3;
+
+  bool deliver_locked(PeerInfo& pi, const Chunk& ch, double connect_seconds) {
+    if (pi.sent.count(ch.offset)) return true;
     const CudaApi& cu = cuda();
     int fd = -1;
     CU_CHECK(cu.cuMemExportToShareableHandle(&fd, ch.handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
@@ -501,31 +508,14 @@ class SymmHeapImpl final : public SymmHeap {
     snprintf(m.src_uid, sizeof(m.src_uid), "%s", uid_.c_str());
     m.offset = ch.offset;
     m.size = ch.size;
-    bool ok = request(pi.sock, m, fd);
+    bool ok = heap_request(pi.sock, &m, sizeof(m), fd, connect_seconds);
     close(fd);
-    if (!ok) fail("symm heap: peer " + pi.uid + " did not map a chunk (is the process alive?)");
-    pi.sent[ch.offset] = true;
+    if (ok) pi.sent[ch.offset] = true;
+    return ok;
   }
 
-  // connect, send one message (+fd), wait for the 4-byte status
   bool request(const std::string& sock, const Msg& m, int fd) {
-    int s = socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
-    if (s < 0) return false;
-    socklen_t len;
-    sockaddr_un a = abstract_addr(sock, len);
-    double deadline = now_seconds() + 60;
-    while (connect(s, (sockaddr*)&a, len) != 0) {
-      if (now_seconds() > deadline) {
-        close(s);
-        return false;
-      }
-      usleep(2000);
-    }
-    bool ok = send_msg_with_fd(s, m, fd);
-    int32_t status = -1;
-    ok = ok && recv_all(s, &status, 4) && status == 0;
-    close(s);
-    return ok;
+    return heap_request(sock, &m, sizeof(m), fd, kAttachConnectSeconds);
   }
 
   Mirror& ensure_mirror_locked(const std::string& uid) {
@@ -677,6 +667,44 @@ std::map<int, std::unique_ptr<SymmHeapImpl>>& heaps() {
 }
 
 }  // namespace
+
+bool heap_request(const std::string& sock, const void* msg, size_t bytes, int fd, double connect_seconds) {
+  int s = socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
+  if (s < 0) return false;
+  socklen_t len;
+  sockaddr_un a = abstract_addr(sock, len);
+  double deadline = now_seconds() + connect_seconds;
+  while (connect(s, (sockaddr*)&a, len) != 0) {
+    if (now_seconds() > deadline) {
+      close(s);
+      return false;
+    }
+    usleep(2000);
+  }
+  iovec iov{const_cast<void*>(msg), bytes};
+  alignas(cmsghdr) char ctrl[CMSG_SPACE(sizeof(int))] = {};
+  msghdr mh{};
+  mh.msg_iov = &iov;
+  mh.msg_iovlen = 1;
+  if (fd >= 0) {
+    mh.msg_control = ctrl;
+    mh.msg_controllen = sizeof(ctrl);
+    cmsghdr* c = CMSG_FIRSTHDR(&mh);
+    c->cmsg_level = SOL_SOCKET;
+    c->cmsg_type = SCM_RIGHTS;
+    c->cmsg_len = CMSG_LEN(sizeof(int));
+    memcpy(CMSG_DATA(c), &fd, sizeof(int));
+  }
+  ssize_t r;
+  do {
+    r = sendmsg(s, &mh, MSG_NOSIGNAL);
+  } while (r < 0 && errno == EINTR);
+  bool ok = r == (ssize_t)bytes;
+  int32_t status = -1;
+  ok = ok && recv_all(s, &status, 4) && status == 0;
+  close(s);
+  return ok;
+}
 
 SymmHeap& SymmHeap::instance(int device) {
   std::lock_guard<std::mutex> lk(g_heaps_mu);

@@ -69,4 +69,9 @@ class SymmHeap {
   virtual std::string describe() const = 0;
 };
 
+// One request of the heap's peer-to-peer channel: connect to the abstract Unix socket `sock` (retrying for at
+// most `connect_seconds`: a refused connection means nobody listens there), send `bytes` bytes of `msg` with the
+// file descriptor `fd` attached, and wait for the peer's 4-byte status. True only when the peer answered 0.
+bool heap_request(const std::string& sock, const void* msg, size_t bytes, int fd, double connect_seconds);
+
 }  // namespace moodist

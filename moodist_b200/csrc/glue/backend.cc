@@ -617,6 +617,8 @@ void MoodistBackend::setOption(const std::string& name, int64_t value) {
 
 uint64_t MoodistBackend::kernelLaunches() { return cuda_ ? cuda_->launches() : 0; }
 
+std::vector<OpStat> MoodistBackend::cudaStats(bool wait) { return cuda_ ? cuda_->stats(wait) : std::vector<OpStat>{}; }
+
 std::string MoodistBackend::describe() {
   std::string s = "MoodistBackend(name=" + name_ + ", rank=" + std::to_string(rank_) + "/" + std::to_string(size_);
   if (cuda_) s += ", " + cuda_->describe();

@@ -97,6 +97,7 @@ class MoodistBackend final : public c10d::Backend {
   bool getPreferKernelLess() { return getOption("prefer_kernel_less") != 0; }
   void setPreferKernelLess(bool v) { setOption("prefer_kernel_less", v ? 1 : 0); }
   uint64_t kernelLaunches();
+  std::vector<OpStat> cudaStats(bool wait);
   uint32_t nextCustomOpId() { return ++custom_ops_; }  // compile_op is collective: same ids on every rank
   std::string describe();
 

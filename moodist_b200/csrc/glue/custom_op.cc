@@ -109,7 +109,13 @@ struct PyCustomOp {
     if (remote_readers)
       for (size_t i = 0; i < inputs.size(); ++i)
         stage.push_back(mb_stage_copy_t{inputs[i].data_ptr(), p.stage_offset[p.rank][i], (uint64_t)inputs[i].nbytes()});
+    // The kernel's grid must be the same on every rank (each CTA waits for the READY word of the same CTA index
+    // of every peer), so it is sized from the largest box of ANY rank, which all ranks know from the plan;
+    // what this rank alone stages or copies may be far smaller (or nothing).
     uint64_t biggest = 1;
+    for (auto* side : {&p.inputs, &p.outputs})
+      for (auto& per_rank : *side)
+        for (const BoxSpec& bx : per_rank) biggest = std::max<uint64_t>(biggest, (uint64_t)bx.numel() * p.elem_size);
     for (const CopyPiece& pc : p.pieces) {
       mb_piece_t q{};
       q.src_rank = pc.src_rank;
@@ -121,9 +127,7 @@ struct PyCustomOp {
       q.src_pitch = pc.src_pitch;
       q.dst_pitch = pc.dst_pitch;
       pieces.push_back(q);
-      biggest = std::max<uint64_t>(biggest, pc.rows * pc.row_bytes);
     }
-    for (auto& s : stage) biggest = std::max<uint64_t>(biggest, s.bytes);
     CUstream_st* raw = reinterpret_cast<CUstream_st*>(stream.stream());
     uint32_t seq = g.next_seq(raw);  // orders this op after the group's earlier ones before scratch is reused
     size_t sbytes = stage.size() * sizeof(mb_stage_copy_t), pbytes = pieces.size() * sizeof(mb_piece_t);

@@ -33,11 +33,30 @@ PYBIND11_MODULE(_C, m) {
           .def("set_prefer_kernel_less", &MoodistBackend::setPreferKernelLess)
           .def("kernel_launches", &MoodistBackend::kernelLaunches)
           .def("describe", &MoodistBackend::describe)
+          .def(
+              "stats",
+              [](MoodistBackend& self, bool wait) {
+                // {"all_gather/nvls": {"calls": .., "bytes": .., "timed_calls": .., "device_us": ..}, ...}
+                py::dict out;
+                for (const OpStat& st : self.cudaStats(wait)) {
+                  py::dict row;
+                  row["calls"] = st.calls;
+                  row["bytes"] = st.bytes;
+                  row["timed_calls"] = st.timed_calls;
+                  row["device_us"] = st.device_us;
+                  out[py::str(st.name)] = row;
+                }
+                return out;
+              },
+              py::arg("wait") = true,
+              "per operation and kernel family: calls, payload bytes, and the device time of the sampled calls")
           .def("all_gather_cast", &MoodistBackend::allGatherCast, py::arg("output"), py::arg("input"),
                py::call_guard<py::gil_scoped_release>())
           .def("reduce_scatter_cast", &MoodistBackend::reduceScatterCast, py::arg("output"), py::arg("input"),
                py::arg("op") = 0, py::arg("premul") = 1.0, py::call_guard<py::gil_scoped_release>());
   m.attr("MoodistProcessGroup") = backend;
+  m.def("load_variant_table", &load_variant_table, py::arg("path"), py::arg("world"),
+        "thresholds a group of `world` ranks would take from a MOODIST_VARIANT_TABLE file");
   m.def("live_process_groups", &MoodistBackend::live, "every moodist group alive in this process");
   m.def("find_process_group", &MoodistBackend::find, "the live moodist group with this name, or None");
 

@@ -98,7 +98,7 @@ void run_rc(int rc, const char* what) {
 // valid until the collective after next on this group.
 std::tuple<at::Tensor, at::Tensor> ag_gemm(c10::intrusive_ptr<MoodistBackend> pg, const at::Tensor& shard,
                                            const at::Tensor& other, bool gather_weight, bool out_fp32, int64_t epilogue,
-                                           int64_t comm_ctas) {
+                                           int64_t comm_ctas, c10::optional<at::Tensor> out) {
   TORCH_CHECK(shard.is_cuda() && other.is_cuda() && shard.scalar_type() == at::kBFloat16 &&
                   other.scalar_type() == at::kBFloat16 && shard.dim() == 2 && other.dim() == 2,
               "moodist ag_gemm: 2-D bf16 CUDA tensors");
@@ -110,7 +110,10 @@ std::tuple<at::Tensor, at::Tensor> ag_gemm(c10::intrusive_ptr<MoodistBackend> pg
   const int64_t N = gather_weight ? shard.size(0) * world : other.size(0);
   c10::cuda::CUDAGuard guard(shard.device());
   auto stream = c10::cuda::getCurrentCUDAStream();
-  at::Tensor y = at::empty({M, N}, shard.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+  at::Tensor y = out.has_value() ? *out : at::empty({M, N}, shard.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+  TORCH_CHECK(y.dim() == 2 && y.size(0) == M && y.size(1) == N && y.is_contiguous() &&
+                  y.scalar_type() == (out_fp32 ? at::kFloat : at::kBFloat16),
+              "moodist ag_gemm: bad output tensor");
   CudaGroup& g = pg->cudaGroup(shard.get_device());
   const mb_comm_t* comm = static_cast<const mb_comm_t*>(g.comm_struct());
   CUstream_st* raw = reinterpret_cast<CUstream_st*>(stream.stream());
@@ -126,6 +129,7 @@ std::tuple<at::Tensor, at::Tensor> ag_gemm(c10::intrusive_ptr<MoodistBackend> pg
   int rc = mb_ag_gemm(comm, seq, shard.data_ptr(), other.data_ptr(), y.data_ptr(), (int)M, (int)N, (int)K, other.stride(0),
                       N, gather_weight ? 1 : 0, 0, out_fp32, (int)epilogue, (int)comm_ctas, raw);
   g.finish_op(raw);
+  g.note_op("ag_gemm", gather_weight ? "fused_gather_b" : "fused_gather_a", (size_t)shard.nbytes());
   run_rc(rc, "ag_gemm");
   const int64_t rows = gather_weight ? N : M;
   gathered = at::from_blob(mb_stage_pointer(comm, seq), {rows, K}, shard.options());
@@ -159,6 +163,7 @@ at::Tensor gemm_rs(c10::intrusive_ptr<MoodistBackend> pg, const at::Tensor& a, c
   int rc = mb_gemm_rs(comm, seq, a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
                       N, trans_b, out_fp32, (float)scale, scale != 1.0, raw);
   g.finish_op(raw);
+  g.note_op("gemm_rs", "fused", (size_t)out.nbytes() * world);
   run_rc(rc, "gemm_rs");
   return out;
 }
@@ -168,7 +173,7 @@ at::Tensor gemm_rs(c10::intrusive_ptr<MoodistBackend> pg, const at::Tensor& a, c
 void bind_fused(pybind11::module_& m) {
   m.def("ag_gemm", &ag_gemm, pybind11::arg("group"), pybind11::arg("shard"), pybind11::arg("other"),
         pybind11::arg("gather_weight") = false, pybind11::arg("out_fp32") = false, pybind11::arg("epilogue") = 0,
-        pybind11::arg("comm_ctas") = 0);
+        pybind11::arg("comm_ctas") = 0, pybind11::arg("out") = pybind11::none());
   m.def("gemm_rs", &gemm_rs, pybind11::arg("group"), pybind11::arg("a"), pybind11::arg("b"),
         pybind11::arg("trans_b") = false, pybind11::arg("out_fp32") = false, pybind11::arg("scale") = 1.0);
 }

@@ -89,7 +89,7 @@ class Attention(nn.Module):
         self.n_heads, self.n_kv = cfg.n_heads, cfg.n_kv_heads
         self.hd = cfg.dim // cfg.n_heads
         # fused QKV projection: one GEMM whose gathered weight arrives through the all-gather
-        self.wqkv = Linear(cfg.dim, (cfg.n_heads + 2 * cfg.n_kv_heads) * self.hd, device=device)
+        self.wqkv = Linear(cfg.dim, (cfg.n_heads + 2 * cfg.n_kv_heads) * self.hd, device=device, fuse_gather=True)
         self.wo = Linear(cfg.n_heads * self.hd, cfg.dim, device=device)
 
     def forward(self, x, rope: RopeTables):
@@ -109,7 +109,7 @@ class MLP(nn.Module):
     def __init__(self, cfg: LlamaConfig, device=None):
         super().__init__()
         # gate and up projections share one GEMM (the "up" GEMM the all-gather is fused into)
-        self.w13 = Linear(cfg.dim, 2 * cfg.ffn_dim, device=device)
+        self.w13 = Linear(cfg.dim, 2 * cfg.ffn_dim, device=device, fuse_gather=True)
         self.w2 = Linear(cfg.ffn_dim, cfg.dim, device=device)
 
     def forward(self, x):
@@ -129,11 +129,23 @@ class Block(nn.Module):
         return x + self.mlp(self.mlp_norm(x))
 
 
+class Embedding(nn.Embedding):
+    """Token embedding whose table a sharding engine may take over (it then leaves a handle on the module)."""
+
+    _mb_regather_kind = "embedding"
+
+    def forward(self, tokens):
+        h = self.__dict__.get("_mb_handle")
+        if h is not None:
+            return h.embedding(tokens)
+        return super().forward(tokens)
+
+
 class Llama(nn.Module):
     def __init__(self, cfg: LlamaConfig, device=None):
         super().__init__()
         self.cfg = cfg
-        self.embed = nn.Embedding(cfg.vocab_size, cfg.dim, device=device, dtype=torch.bfloat16)
+        self.embed = Embedding(cfg.vocab_size, cfg.dim, device=device, dtype=torch.bfloat16)
         self.layers = nn.ModuleList([Block(cfg, device=device) for _ in range(cfg.n_layers)])
         self.norm = RMSNorm(cfg.dim, cfg.norm_eps, device=device)
         self.lm_head = Linear(cfg.dim, cfg.vocab_size, device=device)

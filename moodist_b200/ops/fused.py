@@ -20,15 +20,15 @@ def fused_launches() -> int:
     return _launches
 
 
-def ag_gemm(group, shard, other, gather_weight=False, out_fp32=False, epilogue=0, comm_ctas=0):
+def ag_gemm(group, shard, other, gather_weight=False, out_fp32=False, epilogue=0, comm_ctas=0, out=None):
     """``all_gather(shard) @ other.T`` (``gather_weight=False``) or ``other @ all_gather(shard).T``.
 
     Returns ``(y, gathered)``; ``gathered`` aliases the group's staging area and is valid until the
-    collective after next on this group.
+    collective after next on this group.  ``out`` (contiguous ``[M, N]``) receives ``y`` when given.
     """
     global _launches
     _launches += 1
-    return _C.ag_gemm(group, shard, other, gather_weight, out_fp32, epilogue, comm_ctas)
+    return _C.ag_gemm(group, shard, other, gather_weight, out_fp32, epilogue, comm_ctas, out)
 
 
 def gemm_rs(group, a, b, trans_b=False, out_fp32=False, scale=1.0):

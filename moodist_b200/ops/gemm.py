@@ -81,12 +81,20 @@ def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 
 class Linear(torch.nn.Module):
-    """Bias-free linear layer whose forward and backward GEMMs run on the tcgen05 kernel."""
+    """Bias-free linear layer whose forward and backward GEMMs run on the tcgen05 kernel.
 
-    def __init__(self, in_features: int, out_features: int, device=None, dtype=torch.bfloat16):
+    A sharding engine may take the weight over (``parallel.regather``): it then leaves a handle on the module
+    and the layer's matmuls, the gathering of the weight and its gradient all go through that handle.
+    ``fuse_gather=True`` marks a layer whose weight all-gather such an engine should fuse into the GEMM.
+    """
+
+    _mb_regather_kind = "linear"
+
+    def __init__(self, in_features: int, out_features: int, device=None, dtype=torch.bfloat16, fuse_gather=False):
         super().__init__()
         self.in_features = in_features
         self.out_features = out_features
+        self._mb_fuse_gather = bool(fuse_gather)
         self.weight = torch.nn.Parameter(torch.empty(out_features, in_features, device=device, dtype=dtype))
         self.weight._mb_linear_weight = True  # lets a sharded engine route the weight gradient (see _Linear)
 
@@ -94,6 +102,9 @@ class Linear(torch.nn.Module):
         torch.nn.init.normal_(self.weight, mean=0.0, std=std)
 
     def forward(self, x):
+        h = self.__dict__.get("_mb_handle")
+        if h is not None:
+            return h.linear(x)
         w = self.weight
         if w.is_cuda and w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16:
             return linear(x, w)

@@ -4,8 +4,15 @@
 over a process group whose collectives are this library's sm_100a kernels, and exposes ``step(tokens)``,
 which takes a pinned host batch and returns the loss as a Python float.  Two engines:
 
-``engine="native"`` (default)  ``moodist_b200.parallel.sharded.ShardedEngine``: gathered parameters stay
-    resident (180 GB of HBM make the second all-gather of the classic schedule pointless), gradients are
+``engine="native"`` (default) with ``schedule="regather"`` (default)
+    ``moodist_b200.parallel.regather.RegatherEngine``: the FSDP2 schedule on this library's own kernels.
+    Parameters are sharded by rows at rest; a block's weights are gathered for its forward and again for its
+    backward.  The gathers of the QKV and gate/up weights happen inside their GEMM kernels
+    (``ops.fused.ag_gemm``), the others one block ahead on a side stream; weight gradients leave through a
+    reduce-scatter (bf16 on the wire, fp32 sum) per weight as soon as the GEMM that made them is done, and
+    AdamW updates this rank's rows.
+``engine="native"`` with ``schedule="resident"``  ``moodist_b200.parallel.sharded.ShardedEngine``: gathered
+    parameters stay resident (only possible while the whole model fits one GPU), gradients are
     reduce-scattered from bf16 with fp32 accumulation, AdamW runs on the flat shard and the updated shard
     is all-gathered in place, all per unit on a side stream under the rest of the backward pass.
 ``engine="fsdp2"``  torch's ``fully_shard`` per transformer block (bf16 parameters, fp32 reduce), the
@@ -37,6 +44,8 @@ class ShardedTrainer:
         reshard_after_forward: bool = True,
         engine: str = "native",
         symmetric_memory: bool = True,
+        schedule: str = "regather",
+        fused: bool = True,
     ):
         if not torch.cuda.is_available():
             raise RuntimeError("ShardedTrainer needs a CUDA device")
@@ -50,15 +59,25 @@ class ShardedTrainer:
         self.model.init_weights(seed)
         self.engine = None
         self.opt = None
+        self.schedule = schedule if engine == "native" else "fsdp2"
         if engine == "native":
-            from .sharded import ShardedEngine
-
             m = self.model
             units = [("embed", [m.embed])]
             units += [(f"layers.{i}", [layer]) for i, layer in enumerate(m.layers)]
             units += [("head", [m.norm, m.lm_head])]
-            self.engine = ShardedEngine(units, group=self.group, lr=lr, betas=(0.9, 0.95), weight_decay=0.1,
-                                        symmetric_memory=symmetric_memory)
+            if schedule == "regather":
+                from .regather import RegatherEngine
+
+                names = {id(p): n for n, p in m.named_parameters()}
+                self.engine = RegatherEngine(units, group=self.group, lr=lr, betas=(0.9, 0.95), weight_decay=0.1,
+                                             fused=fused, symmetric_memory=symmetric_memory, param_names=names)
+            elif schedule == "resident":
+                from .sharded import ShardedEngine
+
+                self.engine = ShardedEngine(units, group=self.group, lr=lr, betas=(0.9, 0.95), weight_decay=0.1,
+                                            symmetric_memory=symmetric_memory)
+            else:
+                raise ValueError(f"unknown schedule {schedule!r} (regather or resident)")
         elif engine == "fsdp2":
             ranks = dist.get_process_group_ranks(self.group)
             mesh = DeviceMesh.from_group(self.group, "cuda", mesh=torch.tensor(ranks), mesh_dim_names=("dp",))

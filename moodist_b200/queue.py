@@ -1,4 +1,4 @@
-"""Distributed queues of tensors and Python objects (reference: ``py/moodist/queue.py:11-100``).
+"""Distributed queues of tensors and Python objects.
 
     q = moodist.Queue(group, location=0)            # lives on rank 0; every rank may put / get
     q.put_tensor(torch.arange(4))
@@ -7,8 +7,13 @@
     with q.transaction() as tx:                     # all puts become visible together, or not at all
         tx.put_tensor(a); tx.put_tensor(b)
 
-``location`` may be a list of ranks: every item is then delivered to each of them (multicast).  Queues
-with a ``name`` can be recreated from (group name, location, name) and so can be pickled.
+``location`` may be an iterable of ranks: every item is then delivered to each of them (multicast).  A
+queue that has a ``name`` can be rebuilt anywhere in the job from the name of its group, its location and
+that name, which is what pickling one does.
+
+The public surface (constructor arguments, method names and their keyword arguments, ``Empty`` on a timed
+out ``get``) is that of the reference's ``py/moodist/queue.py``; the native queue behind it is
+``csrc/core/queue.cc``.
 """
 
 from __future__ import annotations
@@ -19,86 +24,103 @@ from ._core import deserialize, serialize
 from .backend import find_process_group
 
 
+def _native_group(group):
+    """The native moodist group behind whatever the caller passed: a group name, a moodist group, or a
+    ``torch.distributed`` process group that runs on the moodist backend."""
+    if isinstance(group, str):
+        found = find_process_group(group)
+        if found is None:
+            raise ValueError(f"no live moodist process group is named {group!r} in this process")
+        return found
+    if hasattr(group, "Queue") and hasattr(group, "moodist_name"):
+        return group
+    getter = getattr(group, "_get_backend", None)
+    if getter is not None:
+        import torch
+
+        for device in ("cpu", "cuda"):
+            try:
+                native = getter(torch.device(device))
+            except RuntimeError:
+                continue
+            if hasattr(native, "Queue") and hasattr(native, "moodist_name"):
+                return native
+    raise TypeError(f"moodist.Queue needs a moodist process group (or its name), not {type(group).__name__}")
+
+
+class Queue:
+    """A FIFO that lives on one rank (or, multicast, on several) and that every rank of the group can use."""
+
+    def __init__(self, process_group, location, streaming=False, name=None):
+        native = _native_group(process_group)
+        self.location = location if isinstance(location, int) else [int(r) for r in location]
+        self.streaming = bool(streaming)
+        self.process_group_name = native.moodist_name()
+        self.impl = native.Queue(location=self.location, streaming=self.streaming, name=name)
+
+    # ---- producers --------------------------------------------------------------------------------
+    def put_tensor(self, tensor, *, transaction=0):
+        """Queue a tensor.  The returned work object finishes the transfer when it is waited on or dropped."""
+        return self.impl.put(tensor, transaction, True)
+
+    def put_object(self, object, *, transaction=0):
+        """Queue any Python object ``moodist.serialize`` can encode."""
+        return self.impl.put(serialize(object), transaction, False)
+
+    def transaction(self):
+        """``with q.transaction() as tx``: the block's puts reach consumers together and in order, or, if the
+        block raises, not at all."""
+        return TransactionContextManager(self)
+
+    # ---- consumers --------------------------------------------------------------------------------
+    def get_tensor(self, block=True, timeout=None, return_size=False):
+        item, remaining = self.impl.get(block=block, timeout=timeout)
+        if item is None:
+            raise Empty
+        if return_size:
+            return item, remaining
+        return item
+
+    def get_object(self, block=True, timeout=None, return_size=False):
+        item, remaining = self.get_tensor(block=block, timeout=timeout, return_size=True)
+        value = deserialize(item)
+        if return_size:
+            return value, remaining
+        return value
+
+    def qsize(self):
+        return self.impl.qsize()
+
+    def empty(self):
+        return self.qsize() == 0
+
+    def wait(self, timeout=None):
+        """Block until the queue holds something (or ``timeout`` seconds have passed); truthy when it does."""
+        return self.impl.wait(timeout=timeout)
+
+    # ---- pickling: a named queue travels as the recipe to look it up again ---------------------------------
+    def __reduce__(self):
+        return Queue, (self.process_group_name, self.location, self.streaming, self.impl.name())
+
+
 class TransactionContextManager:
+    """Groups puts: begun on entry, committed on a clean exit, cancelled when the block raises."""
+
     def __init__(self, queue):
         self.queue = queue
+        self.id = None
 
     def __enter__(self):
         self.id = self.queue.impl.transaction_begin()
         return self
 
     def __exit__(self, exc_type, exc_value, traceback):
-        if exc_type is not None:
-            self.queue.impl.transaction_cancel(self.id)
-        else:
-            self.queue.impl.transaction_commit(self.id)
+        finish = self.queue.impl.transaction_cancel if exc_type is not None else self.queue.impl.transaction_commit
+        finish(self.id)
+        return False
 
     def put_tensor(self, tensor):
         return self.queue.put_tensor(tensor, transaction=self.id)
 
     def put_object(self, object):
         return self.queue.put_object(object, transaction=self.id)
-
-
-class Queue:
-    def __init__(self, process_group, location, streaming=False, name=None):
-        if isinstance(process_group, str):
-            pg_name = process_group
-            process_group = find_process_group(pg_name)
-            if process_group is None:
-                raise ValueError("The Moodist process group by name '%s' could not be found" % pg_name)
-        if not hasattr(process_group, "Queue"):
-            # a torch.distributed ProcessGroup whose backend is moodist is fine too
-            backend = None
-            if hasattr(process_group, "_get_backend"):
-                import torch
-
-                try:
-                    backend = process_group._get_backend(torch.device("cpu"))
-                except RuntimeError:
-                    backend = None
-            if backend is None or not hasattr(backend, "Queue"):
-                raise RuntimeError(
-                    "moodist.Queue process_group parameter must be a MoodistProcessGroup, but got %s"
-                    % str(type(process_group)),
-                )
-            process_group = backend
-        if not isinstance(location, int):
-            location = list(location)
-        self.impl = process_group.Queue(location=location, streaming=streaming, name=name)
-        self.process_group_name = process_group.moodist_name()
-        self.location = location
-        self.streaming = streaming
-
-    def __reduce__(self):
-        return type(self), (self.process_group_name, self.location, self.streaming, self.impl.name())
-
-    def put_tensor(self, tensor, *, transaction=0):
-        return self.impl.put(tensor, transaction, True)  # the work waits for completion when dropped
-
-    def get_tensor(self, block=True, timeout=None, return_size=False):
-        r, size = self.impl.get(block=block, timeout=timeout)
-        if r is None:
-            raise Empty
-        return (r, size) if return_size else r
-
-    def put_object(self, object, *, transaction=0):
-        return self.impl.put(serialize(object), transaction, False)
-
-    def get_object(self, block=True, timeout=None, return_size=False):
-        if return_size:
-            tensor, size = self.get_tensor(block=block, timeout=timeout, return_size=True)
-            return deserialize(tensor), size
-        return deserialize(self.get_tensor(block=block, timeout=timeout))
-
-    def qsize(self):
-        return self.impl.qsize()
-
-    def empty(self):
-        return self.impl.qsize() == 0
-
-    def wait(self, timeout=None):
-        return self.impl.wait(timeout=timeout)
-
-    def transaction(self):
-        return TransactionContextManager(self)

@@ -6,8 +6,13 @@ measured on one 8 x B200 NVSwitch machine; this module re-derives them from a sw
 
     torchrun ... benchmarks/collective_sweep.py --impls moodist_p2p,moodist_nvls,moodist_ce,nccl --out sweep.jsonl
     python -m moodist_b200.utils.tuning sweep.jsonl            # prints the table and the settings
-    eval "$(python -m moodist_b200.utils.tuning sweep.jsonl --export)"   # MOODIST_* variables for the next run
+    python -m moodist_b200.utils.tuning sweep.jsonl --table variants.json   # adds this world size to the file
+    MOODIST_VARIANT_TABLE=variants.json torchrun ...           # groups load their thresholds from it
+    eval "$(python -m moodist_b200.utils.tuning sweep.jsonl --export)"   # or: MOODIST_* variables by hand
 
+The table file holds one block of thresholds per world size (``{"8": {"MOODIST_NVLS_AG_MIN_BYTES": 32768,
+...}, "2": {...}}``); a CUDA group reads the block of its own size when it is created.  A variable set in
+the environment still wins over the table, and the table over the built-in values.
 ``apply(settings)`` puts the variables into ``os.environ`` (before the process group is created).  The
 reference picks its algorithm per call from fixed rules in ``core/processgroup.cc``; it has no measured table.
 """
@@ -94,6 +99,19 @@ def settings_from(table: dict[str, list[dict]]) -> dict[str, int]:
     return out
 
 
+def write_table(path: str, world: int, settings: dict[str, int]) -> dict:
+    """Merge ``settings`` as the block for ``world`` ranks into the table file at ``path``; returns the table."""
+    table = {}
+    if os.path.exists(path):
+        with open(path) as f:
+            table = json.load(f)
+    table[str(int(world))] = {k: int(v) for k, v in sorted(settings.items())}
+    with open(path, "w") as f:
+        json.dump(table, f, indent=1, sort_keys=True)
+        f.write("\n")
+    return table
+
+
 def apply(settings: dict[str, int]) -> None:
     """Set the variables for this process; call before ``init_process_group``."""
     for k, v in settings.items():
@@ -113,13 +131,29 @@ def format_table(table: dict[str, list[dict]]) -> str:
 def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     export = "--export" in argv
+    table_path = None
+    if "--table" in argv:
+        i = argv.index("--table")
+        if i + 1 >= len(argv):
+            print(__doc__)
+            return 2
+        table_path = argv[i + 1]
+        del argv[i : i + 2]
     paths = [a for a in argv if not a.startswith("--")]
     if len(paths) != 1:
         print(__doc__)
         return 2
-    table = variant_table(load_sweep(paths[0]))
+    rows = load_sweep(paths[0])
+    table = variant_table(rows)
     settings = settings_from(table)
-    if export:
+    if table_path:
+        worlds = {int(r["world"]) for r in rows if "world" in r}
+        if len(worlds) != 1:
+            print(f"--table needs a sweep of one world size, this one has {sorted(worlds)}")
+            return 2
+        write_table(table_path, worlds.pop(), settings)
+        print(f"wrote the block for world size {rows[0]['world']} to {table_path}")
+    elif export:
         for k, v in settings.items():
             print(f"export {k}={v}")
     else:

@@ -1,6 +1,11 @@
 // Stand-alone checks of the torch-free core: wire format golden bytes, the registered-memory table,
 // the bootstrap ring (ranks as threads), the store mesh, and the CPU reduce loops.
+#include <sys/socket.h>
+#include <sys/un.h>
+#include <unistd.h>
+
 #include <algorithm>
+#include <cstddef>
 #include <cmath>
 #include <cstring>
 #include <condition_variable>
@@ -19,6 +24,7 @@
 #include "core/topology.h"
 #include "core/setup_comms.h"
 #include "core/store.h"
+#include "core/symm_heap.h"
 #include "core/tcp_transport.h"
 #include "core/wire.h"
 
@@ -395,7 +401,45 @@ static void test_planner_random() {
   CHECK(threw);
 }
 
+// The symmetric heap's request channel against peers that are gone or refuse: a socket nobody listens on
+// gives up after the connect window (heap growth uses a short one so that an exited peer cannot stall the
+// allocator), and a peer that answers non-zero is a failure too.
+static void test_heap_request() {
+  char msg[64] = {1, 2, 3};
+  double t0 = now_seconds();
+  CHECK(!heap_request("moodist-selftest-no-such-socket-" + std::to_string(getpid()), msg, sizeof(msg), -1, 0.3));
+  double dt = now_seconds() - t0;
+  CHECK(dt >= 0.25 && dt < 3.0);
+  // a live peer: answers 0 the first time, 7 the second
+  std::string name = "moodist-selftest-heap-" + std::to_string(getpid());
+  int ls = socket(AF_UNIX, SOCK_STREAM, 0);
+  sockaddr_un a{};
+  a.sun_family = AF_UNIX;
+  memcpy(a.sun_path + 1, name.data(), name.size());
+  socklen_t len = (socklen_t)(offsetof(sockaddr_un, sun_path) + 1 + name.size());
+  CHECK(bind(ls, (sockaddr*)&a, len) == 0 && listen(ls, 4) == 0);
+  std::thread server([&] {
+    for (int32_t status : {0, 7}) {
+      int c = accept(ls, nullptr, nullptr);
+      char buf[64];
+      size_t got = 0;
+      while (got < sizeof(buf)) {
+        ssize_t r = recv(c, buf + got, sizeof(buf) - got, 0);
+        if (r <= 0) break;
+        got += (size_t)r;
+      }
+      (void)!write(c, &status, 4);
+      close(c);
+    }
+  });
+  CHECK(heap_request(name, msg, sizeof(msg), -1, 1.0));
+  CHECK(!heap_request(name, msg, sizeof(msg), -1, 1.0));
+  server.join();
+  close(ls);
+}
+
 int main() {
+  test_heap_request();
   test_wire();
   test_planner_random();
   test_topology();

@@ -72,6 +72,19 @@ def _patterns(rank, world, port, device):
     fr = _global((n, n), torch.float32, 4)
     r, c = n // world, n // world
     _run(moodist, pg, fr, [{"offset": [rank * r, 0], "shape": [r, n]}], [{"offset": [0, rank * c], "shape": [n, c]}], dev)
+    # uneven boxes: per-rank maxima on different sides of the kernel's grid thresholds (1 MiB on rank 0, 512 KiB
+    # on the others) and a rank that holds nothing while the others move more than one CTA's worth
+    big = _global((384 * world + 128, 512), torch.float32, 5)  # 2 KiB rows
+    r0 = 512 if rank == 0 else 256
+    lo = 0 if rank == 0 else 512 + (rank - 1) * 256
+    total = 512 + (world - 1) * 256
+    big = big[:total].contiguous() if big.shape[0] >= total else _global((total, 512), torch.float32, 5)
+    cols = 512 // world
+    _run(moodist, pg, big, [{"offset": [lo, 0], "shape": [r0, 512]}], [{"offset": [0, rank * cols], "shape": [total, cols]}], dev,
+         repeat=2)
+    wide = _global((96, 1024), torch.float32, 6)  # 384 KiB in one box
+    wbox = {"offset": [0, 0], "shape": [96, 1024]}
+    _run(moodist, pg, wide, [wbox] if rank == 0 else None, [wbox] if rank == 1 else None, dev, repeat=2)
     # uncovered output is an error on every rank
     with pytest.raises(RuntimeError, match="no input covers"):
         moodist.compile_op(pg, shape=(4, 4), dtype=torch.float32, inputs=[{"offset": [0, 0], "shape": [2, 4]}] if rank == 0 else None,

@@ -1,4 +1,5 @@
-"""CUDA collectives on 2 GPUs (P2P kernels over the symmetric heap) against CPU oracles."""
+"""CUDA collectives on 2, 4 and 8 GPUs (P2P, NVLS and copy-engine kernels over the symmetric heap) against CPU
+oracles; every case runs on as many world sizes as the machine has GPUs for."""
 
 import pytest
 import torch
@@ -6,6 +7,13 @@ import torch
 from moodist_b200.utils.testing import init_moodist, run_ranks
 
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+WORLDS = [2, 4, 8]
+
+
+def _need(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
 
 
 def _cuda_collectives(rank, world, port):
@@ -80,8 +88,10 @@ def _cuda_collectives(rank, world, port):
     dist.destroy_process_group()
 
 
-def test_cuda_collectives_2gpu():
-    run_ranks(_cuda_collectives, 2, timeout=240, env={"MOODIST_DEVICE_TIMEOUT_MS": 5000})
+@pytest.mark.parametrize("world", WORLDS)
+def test_cuda_collectives(world):
+    _need(world)
+    run_ranks(_cuda_collectives, world, timeout=300, env={"MOODIST_DEVICE_TIMEOUT_MS": 5000})
 
 
 def _nvls_variants(rank, world, port):
@@ -121,8 +131,147 @@ def _nvls_variants(rank, world, port):
     dist.destroy_process_group()
 
 
-def test_nvls_variants_2gpu():
-    run_ranks(_nvls_variants, 2, timeout=240, env={"MOODIST_DEVICE_TIMEOUT_MS": 5000})
+@pytest.mark.parametrize("world", WORLDS)
+def test_nvls_variants(world):
+    _need(world)
+    run_ranks(_nvls_variants, world, timeout=300, env={"MOODIST_DEVICE_TIMEOUT_MS": 5000})
+
+
+def _mixed_modes(rank, world, port):
+    """Ranks that differ in per-rank facts — only rank 0's tensors live in the symmetric heap, only the last
+    rank's pointers are off a 16-byte boundary — still pick the same kernel family and piece count for one
+    collective, at sizes of every family (push, NVLS, pull)."""
+    dist = init_moodist(rank, world, port, device="cuda")
+    import moodist_b200
+    from moodist_b200.allocator import symmetric_mem_pool
+
+    dev = torch.device("cuda", rank)
+    pool = symmetric_mem_pool()
+
+    def alloc(n, dtype, heap):
+        if heap:
+            with torch.cuda.use_mem_pool(pool):
+                return torch.zeros(n, dtype=dtype, device=dev)
+        return torch.zeros(n, dtype=dtype, device=dev)
+
+    for nbytes in (16 << 10, 1 << 20, 8 << 20):
+        n = nbytes // 2
+        g = torch.Generator().manual_seed(nbytes)
+        full = (torch.rand(world, n, generator=g) * 2 - 1).to(torch.bfloat16)
+        x = alloc(n, torch.bfloat16, heap=(rank == 0))
+        x.copy_(full[rank])
+        out = torch.empty(world * n, device=dev, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(out, x)
+        assert torch.equal(out.cpu().view(world, n), full), ("mixed all_gather", nbytes)
+        # reduce-scatter: rank 0's input in the heap (read in place by the peers), the others staged
+        allin = (torch.rand(world, world, n // 4, generator=g) * 2 - 1).to(torch.bfloat16)
+        xin = alloc(world * (n // 4), torch.bfloat16, heap=(rank == 0))
+        xin.copy_(allin[rank].reshape(-1))
+        o = torch.empty(n // 4, device=dev, dtype=torch.bfloat16)
+        dist.reduce_scatter_tensor(o, xin, op=dist.ReduceOp.AVG)
+        torch.testing.assert_close(o.float().cpu(), allin[:, rank].float().mean(0), rtol=2e-2, atol=2e-2)
+    # all-reduce in the NVLS size range with one rank's buffer off a 16-byte boundary
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 3e-2)):
+        n = (4 << 20) // (4 if dtype == torch.float32 else 2)
+        g = torch.Generator().manual_seed(n)
+        allin = torch.randn(world, n, generator=g).to(dtype)
+        buf = torch.empty(n + 8, device=dev, dtype=dtype)
+        t = buf[1 : n + 1] if rank == world - 1 else buf[:n]
+        t.copy_(allin[rank])
+        dist.all_reduce(t)
+        ref = allin.double().sum(0)
+        err = (t.double().cpu() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
+        assert err <= tol, ("misaligned all_reduce", dtype, err)
+    pg = moodist_b200.get_backend()
+    if "nvls=1" in pg.describe():
+        with pg.options(method=1):  # NVLS reduce-scatter with the output of one rank misaligned
+            n = 1 << 18
+            g = torch.Generator().manual_seed(3)
+            allin = (torch.rand(world, world, n, generator=g) * 2 - 1).to(torch.bfloat16)
+            buf = torch.empty(n + 8, device=dev, dtype=torch.float32)
+            o = buf[1 : n + 1] if rank == world - 1 else buf[:n]
+            pg.reduce_scatter_cast(o, allin[rank].reshape(-1).to(dev), int(dist.ReduceOp.SUM), 1.0)
+            # the switch accumulates in fp32 but hands back bf16 values: bf16-sized tolerance
+            torch.testing.assert_close(o.cpu(), allin[:, rank].float().sum(0), rtol=2e-2, atol=2e-2)
+    stats = pg.stats()
+    assert any(k.startswith("all_gather/") for k in stats) and all(v["calls"] > 0 for v in stats.values()), stats
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_mixed_heap_and_alignment_modes(world):
+    _need(world)
+    run_ranks(_mixed_modes, world, timeout=300, env={"MOODIST_DEVICE_TIMEOUT_MS": 5000})
+
+
+def _stress(rank, world, port):
+    """100 back-to-back collectives of each kind and an interleaved mix, small sizes: sequence parity, the two
+    staging halves and the per-grid counters are reused hundreds of times (modelled on the reference's
+    tests/test_stress.py)."""
+    dist = init_moodist(rank, world, port, device="cuda")
+    dev = torch.device("cuda", rank)
+    sizes = [1, 7, 64, 255, 1024, 4096, 65536]
+    for n in sizes:
+        x = torch.full((n,), float(rank + 1), device=dev)
+        out = torch.empty(world * n, device=dev)
+        for _ in range(100):
+            dist.all_gather_into_tensor(out, x)
+        assert torch.equal(out.view(world, n)[:, 0].cpu(), torch.arange(1, world + 1, dtype=torch.float32)), ("ag", n)
+        xin = torch.arange(world * n, device=dev, dtype=torch.float32) + rank
+        o = torch.empty(n, device=dev)
+        for _ in range(100):
+            dist.reduce_scatter_tensor(o, xin)
+        want = world * torch.arange(rank * n, (rank + 1) * n, dtype=torch.float32) + sum(range(world))
+        assert torch.equal(o.cpu(), want), ("rs", n)
+        t = torch.full((n,), 1.0, device=dev)
+        for i in range(100):
+            t.fill_(float(rank + i))
+            dist.all_reduce(t)
+        assert bool((t == sum(range(world)) + 99 * world).all()), ("ar", n)
+        for i in range(100):
+            b = torch.full((n,), float(rank * 1000 + i), device=dev)
+            dist.broadcast(b, src=i % world)
+            if i == 99:
+                assert bool((b == (99 % world) * 1000 + 99).all()), ("bc", n)
+    # interleaved mix with a barrier now and then
+    for i in range(100):
+        n = sizes[i % len(sizes)]
+        x = torch.full((n,), float(rank + i), device=dev)
+        out = torch.empty(world * n, device=dev)
+        dist.all_gather_into_tensor(out, x)
+        o = torch.empty(n, device=dev)
+        dist.reduce_scatter_tensor(o, out)
+        dist.all_reduce(x, op=dist.ReduceOp.MAX)
+        dist.broadcast(o, src=(i + 1) % world)
+        if i % 10 == 9:
+            dist.barrier()
+        assert bool((x == world - 1 + i).all()), ("mix", i)
+    for _ in range(10):
+        big = torch.full((1 << 20,), float(rank), device=dev)  # 4 MiB
+        dist.all_reduce(big)
+    assert bool((big == sum(range(world))).all())
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("kernel_less", [False, True])
+def test_stress_back_to_back(world, kernel_less):
+    _need(world)
+    env = {"MOODIST_DEVICE_TIMEOUT_MS": 5000}
+    if kernel_less:
+        env["MOODIST_CE_MIN_BYTES"] = 0  # every all-gather / reduce-scatter goes through the DMA variant
+    run_ranks(_stress_kl if kernel_less else _stress, world, timeout=600, env=env)
+
+
+def _stress_kl(rank, world, port):
+    import moodist_b200
+
+    moodist_b200.set_prefer_kernel_less(True)
+    _stress(rank, world, port)
 
 
 def _copy_engine_variants(rank, world, port):

@@ -1,4 +1,4 @@
-"""Fused collective GEMMs on 2 GPUs against torch.matmul of the gathered / reduced operands (fp32)."""
+"""Fused collective GEMMs on 2, 4 and 8 GPUs against torch.matmul of the gathered / reduced operands (fp32)."""
 
 import pytest
 import torch
@@ -64,5 +64,8 @@ def _fused(rank, world, port):
     dist.destroy_process_group()
 
 
-def test_fused_gemm_collectives_2gpu():
-    run_ranks(_fused, 2, timeout=240, env={"MOODIST_DEVICE_TIMEOUT_MS": 5000})
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_gemm_collectives(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    run_ranks(_fused, world, timeout=300, env={"MOODIST_DEVICE_TIMEOUT_MS": 5000})

@@ -141,14 +141,14 @@ def _tiny_cfg():
     return LlamaConfig(vocab_size=1024, dim=256, n_layers=2, n_heads=4, n_kv_heads=2, ffn_dim=512, max_seq_len=128)
 
 
-def _trainer_run(rank, world, port, steps):
+def _trainer_run(rank, world, port, steps, schedule="resident", fused=True):
     from moodist_b200.models.llama import Llama, loss_fn
     from moodist_b200.parallel.fsdp import ShardedTrainer
 
     dist = init_moodist(rank, world, port, device="cuda")
     dev = torch.device("cuda", rank)
     cfg = _tiny_cfg()
-    tr = ShardedTrainer(cfg, lr=1e-3, seed=0)
+    tr = ShardedTrainer(cfg, lr=1e-3, seed=0, schedule=schedule, fused=fused)
     # oracle on this GPU: same bf16 model, every rank's batch, fp32 AdamW on the averaged gradient is too
     # strict for bf16 weights, so compare losses and parameters with bf16-sized tolerances
     torch.manual_seed(0)
@@ -174,11 +174,28 @@ def _trainer_run(rank, world, port, steps):
     tr.engine.wait()
     torch.cuda.synchronize()
     worst = 0.0
-    for (n, p), (_, q) in zip(tr.model.named_parameters(), ref.named_parameters()):
-        worst = max(worst, (p.float() - q.float()).abs().max().item())
-    assert worst < 2e-2, worst
-    # every rank holds the same gathered parameters
-    flat = torch.cat([u.full.float() for u in tr.engine.units])
+    if schedule == "regather":
+        # at rest a rank holds its rows only: gather every weight for the comparison
+        full = tr.engine.full_parameters()
+        mine = dict(tr.model.named_parameters())
+        for n, q in ref.named_parameters():
+            p = full[n] if n in full else mine[n]
+            assert p.shape == q.shape, (n, p.shape, q.shape)
+            worst = max(worst, (p.float() - q.float()).abs().max().item())
+        assert worst < 2e-2, worst
+        if world > 1:
+            assert all(h.param.shape[0] * world >= h.n and h.param.shape[0] < h.n for u in tr.engine.units for h in u.weights)
+            # every weight whose shape allows it (QKV and gate/up of every block) is gathered inside its GEMM
+            per_step = sum(h.fused for u in tr.engine.units for h in u.weights)
+            assert (per_step > 0) == bool(fused), per_step
+            assert tr.engine.fused_calls == per_step * steps, (tr.engine.fused_calls, per_step, steps)
+        flat = torch.cat([v.float().reshape(-1) for v in full.values()] + [tr.engine._small_full.float()])
+    else:
+        for (n, p), (_, q) in zip(tr.model.named_parameters(), ref.named_parameters()):
+            worst = max(worst, (p.float() - q.float()).abs().max().item())
+        assert worst < 2e-2, worst
+        # every rank holds the same gathered parameters
+        flat = torch.cat([u.full.float() for u in tr.engine.units])
     lo, hi = flat.clone(), flat.clone()
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
@@ -194,6 +211,25 @@ def test_native_engine_one_gpu():
 @pytest.mark.multigpu
 def test_native_engine_two_gpus():
     run_ranks(_trainer_run, 2, 4, timeout=300)
+
+
+def test_regather_engine_one_gpu():
+    run_ranks(_trainer_run, 1, 4, "regather", timeout=300)
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("fused", [True, False])
+def test_regather_engine_two_gpus(fused):
+    """The FSDP2-style schedule on two GPUs (weights gathered inside the QKV / gate-up GEMMs when fused)
+    against single-process AdamW on the rank-averaged gradient."""
+    run_ranks(_trainer_run, 2, 4, "regather", fused, timeout=300, env={"MOODIST_DEVICE_TIMEOUT_MS": 10000})
+
+
+@pytest.mark.multigpu
+def test_regather_engine_four_gpus():
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    run_ranks(_trainer_run, 4, 3, "regather", True, timeout=300, env={"MOODIST_DEVICE_TIMEOUT_MS": 10000})
 
 
 def _fsdp2_run(rank, world, port):

@@ -48,3 +48,23 @@ def test_apply_sets_environment(monkeypatch):
     import os
 
     assert os.environ["MOODIST_CE_AUTO_BYTES"] == str(1 << 26)
+
+
+def test_table_file_round_trip_through_the_native_loader(tmp_path):
+    """The file `--table` writes is what a CUDA group reads at creation (MOODIST_VARIANT_TABLE)."""
+    from moodist_b200._core import _C
+
+    sweep = tmp_path / "sweep.jsonl"
+    sweep.write_text("\n".join(json.dumps(r) for r in _rows()))
+    path = tmp_path / "variants.json"
+    assert tuning.main([str(sweep), "--table", str(path)]) == 0
+    tuning.write_table(str(path), 2, {"MOODIST_CE_AUTO_BYTES": 123456, "MOODIST_NVLS_RS_MIN_BYTES": -1})
+    want8 = tuning.settings_from(tuning.variant_table(tuning.load_sweep(str(sweep))))
+    got8 = _C.load_variant_table(str(path), 8)
+    assert got8 == {k: int(v) for k, v in want8.items()}
+    assert _C.load_variant_table(str(path), 2) == {"MOODIST_CE_AUTO_BYTES": 123456, "MOODIST_NVLS_RS_MIN_BYTES": -1}
+    assert _C.load_variant_table(str(path), 4) == {}
+    bad = tmp_path / "bad.json"
+    bad.write_text('{"8": ["not", "an", "object"]}')
+    assert _C.load_variant_table(str(bad), 8) == {}
+    assert _C.load_variant_table(str(tmp_path / "missing.json"), 8) == {}
