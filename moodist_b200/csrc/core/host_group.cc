@@ -1,6 +1,7 @@
 #include "host_group.h"
 
 #include <pthread.h>
+#include <sys/prctl.h>
 #include <unistd.h>
 
 #include <atomic>
@@ -11,6 +12,7 @@
 #include <list>
 #include <map>
 #include <mutex>
+#include <random>
 #include <thread>
 
 #include "cpu_reduce.h"
@@ -116,6 +118,30 @@ class HostGroupImpl final : public HostGroup {
         fail("moodist: host engine start-up failed: " + why);
       }
       usleep(1000);
+    }
+    // Ranks on this machine move payloads with one process_vm_readv copy instead of a loopback socket
+    // (reference: core/cputhread.cc:3369-3379, 3589-3603). Every rank publishes its pid and a probe word;
+    // whoever manages to read a peer's probe word uses the direct path towards that peer, everybody else
+    // stays on TCP (another machine, another PID namespace, a kernel that forbids it).
+    // MOODIST_DIRECT_CPU=0 switches it off.
+    if (world > 1 && env_long("MOODIST_DIRECT_CPU", 1)) {
+      prctl(PR_SET_PTRACER, PR_SET_PTRACER_ANY, 0, 0, 0);  // same-user peers may read us under Yama scope 1
+      std::random_device rd;
+      probe_word_ = ((uint64_t)rd() << 32) ^ rd() ^ 0x6d6f6f64u;
+      transport_.set_direct_min_bytes((size_t)env_long("MOODIST_DIRECT_CPU_MIN_BYTES", 8192));
+      store.set(pfx + "proc/" + std::to_string(rank),
+                encode(boot_id(), (int64_t)getpid(), (uint64_t)(uintptr_t)&probe_word_, probe_word_));
+      for (int r = 0; r < world; ++r) {
+        if (r == rank) continue;
+        std::string boot;
+        int64_t pid = 0;
+        uint64_t addr = 0, value = 0;
+        decode_exact(store.get(pfx + "proc/" + std::to_string(r)), boot, pid, addr, value);
+        if (boot != boot_id()) continue;
+        run_on_engine([this, r, pid, addr, value] {
+          if (transport_.probe_direct(r, pid, (uintptr_t)addr, value)) ++direct_peers_;
+        });
+      }
     }
     store.barrier(pfx + "moodist_ready", rank, world);
   }
@@ -376,6 +402,19 @@ class HostGroupImpl final : public HostGroup {
   void post_read_strided(int src, void* local, uint64_t rows, size_t row_bytes, size_t dst_pitch, uint32_t rkey,
                          uint64_t raddr, size_t src_pitch, std::function<void(bool ok)> done) override {
     transport_.post_read_strided(src, local, rows, row_bytes, dst_pitch, rkey, (uintptr_t)raddr, src_pitch, std::move(done));
+  }
+
+  std::vector<uint64_t> transport_counters() override {
+    // read on the engine thread, where the counters are written
+    auto out = std::make_shared<std::vector<uint64_t>>();
+    auto waiter = std::make_shared<Waiter>();
+    run_on_engine([this, out, waiter] {
+      *out = {transport_.bytes_sent(), transport_.bytes_received(), transport_.bytes_direct(), (uint64_t)direct_peers_};
+      waiter->finish();
+    });
+    std::unique_lock<std::mutex> lk(waiter->mu);
+    waiter->cv.wait_for(lk, std::chrono::seconds(5), [&] { return waiter->done; });
+    return *out;
   }
 
   bool in_error() const override { return error_state_.load(); }
@@ -753,6 +792,8 @@ class HostGroupImpl final : public HostGroup {
   int rank_, world_;
   Poller poller_;
   TcpTransport transport_;
+  uint64_t probe_word_ = 0;  // same-machine peers read this word to find out whether they may read this process
+  int direct_peers_ = 0;     // peers whose memory this rank reads directly (engine thread)
   struct ScratchPool {
     std::mutex mu;
     std::vector<std::unique_ptr<Bytes>> free;

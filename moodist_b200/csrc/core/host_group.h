@@ -95,6 +95,9 @@ class HostGroup {
                                  uint64_t raddr, size_t src_pitch, std::function<void(bool ok)> done) = 0;
 
   // ---- health ----
+  // {payload+header bytes sent over TCP, received over TCP, payload bytes copied directly between address
+  // spaces of this machine, number of peers this rank reads directly}
+  virtual std::vector<uint64_t> transport_counters() = 0;
   virtual bool in_error() const = 0;
   virtual std::string error_text() const = 0;
   virtual void shutdown() = 0;  // coordinated: tells every peer, waits briefly for theirs

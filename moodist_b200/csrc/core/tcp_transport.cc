@@ -1,5 +1,10 @@
 #include "tcp_transport.h"
 
+#include <sys/uio.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <cerrno>
 #include <cstring>
 #include <deque>
 #include <mutex>
@@ -75,11 +80,50 @@ void MrTable::add_landed(uint32_t key, uint64_t n) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// copies between address spaces of one machine
+// ------------------------------------------------------------------------------------------------
+bool vm_read(int64_t pid, void* local, uintptr_t remote, size_t bytes) {
+  uint8_t* l = (uint8_t*)local;
+  while (bytes) {
+    iovec li{l, bytes}, ri{(void*)remote, bytes};
+    ssize_t n = process_vm_readv((pid_t)pid, &li, 1, &ri, 1, 0);
+    if (n <= 0) return false;
+    l += n;
+    remote += (size_t)n;
+    bytes -= (size_t)n;
+  }
+  return true;
+}
+
+bool vm_read_strided(int64_t pid, void* local, size_t dst_pitch, uintptr_t remote, size_t src_pitch, uint64_t rows,
+                     size_t row_bytes) {
+  constexpr int kBatch = 512;  // well under IOV_MAX
+  iovec li[kBatch], ri[kBatch];
+  for (uint64_t r0 = 0; r0 < rows; r0 += kBatch) {
+    int n = (int)std::min<uint64_t>(kBatch, rows - r0);
+    for (int i = 0; i < n; ++i) {
+      li[i] = iovec{(uint8_t*)local + (r0 + i) * dst_pitch, row_bytes};
+      ri[i] = iovec{(void*)(remote + (r0 + i) * src_pitch), row_bytes};
+    }
+    ssize_t got = process_vm_readv((pid_t)pid, li, n, ri, n, 0);
+    if (got != (ssize_t)((size_t)n * row_bytes)) {
+      // a short transfer stops at an iovec boundary or inside one: finish row by row
+      for (int i = 0; i < n; ++i)
+        if (!vm_read(pid, li[i].iov_base, (uintptr_t)ri[i].iov_base, row_bytes)) return false;
+    }
+  }
+  return true;
+}
+
+// ------------------------------------------------------------------------------------------------
 // transport
 // ------------------------------------------------------------------------------------------------
 struct TcpTransport::Peer {
   std::shared_ptr<Conn> conn;
   bool ready = false;
+  int64_t pid = 0;             // > 0: this rank may read that process's memory
+  bool reads_me = false;       // the peer has told us it may read ours
+  int64_t reader_pid = 0;
   std::vector<std::pair<std::string, int>> candidates;
   size_t next_candidate = 0;
   int attempts = 0;
@@ -275,9 +319,27 @@ void TcpTransport::post_write(int dst, const void* src, size_t bytes, uint32_t r
     return;
   }
   uint64_t index = next_index_++;
+  if (peers_[dst]->reads_me && bytes >= direct_min_) {
+    // the receiver checks the destination against its table and then fetches the bytes itself
+    Pending pend{std::move(done), nullptr, bytes};
+    pend.keep = std::move(keep);
+    pending_[index] = std::move(pend);
+    send_record(dst, encode((uint8_t)kMsgWriteDirect, index, rkey, (uint64_t)raddr, (uint64_t)bytes, (uint64_t)(uintptr_t)src),
+                nullptr, 0, nullptr);
+    return;
+  }
   pending_[index] = Pending{std::move(done), nullptr, bytes};
   send_record(dst, encode((uint8_t)kMsgWrite, index, rkey, (uint64_t)raddr, (uint64_t)bytes), src, bytes,
               std::move(keep));
+}
+
+bool TcpTransport::probe_direct(int peer, int64_t pid, uintptr_t probe_addr, uint64_t probe_value) {
+  if (peer == rank_ || pid <= 0) return false;
+  uint64_t v = 0;
+  if (!vm_read(pid, &v, probe_addr, sizeof(v)) || v != probe_value) return false;
+  peers_[peer]->pid = pid;
+  send_record(peer, encode((uint8_t)kMsgDirectOk, (int64_t)getpid()), nullptr, 0, nullptr);
+  return true;
 }
 
 void TcpTransport::post_read(int dst, void* local, size_t bytes, uint32_t rkey, uintptr_t raddr, Done done) {
@@ -288,6 +350,14 @@ void TcpTransport::post_read(int dst, void* local, size_t bytes, uint32_t rkey, 
     return;
   }
   uint64_t index = next_index_++;
+  if (peers_[dst]->pid > 0 && bytes >= direct_min_) {
+    Pending pend{std::move(done), local, bytes};
+    pend.raddr = raddr;
+    pend.peer = dst;
+    pending_[index] = std::move(pend);
+    send_record(dst, encode((uint8_t)kMsgReadCheck, index, rkey, (uint64_t)raddr, (uint64_t)bytes), nullptr, 0, nullptr);
+    return;
+  }
   pending_[index] = Pending{std::move(done), local, bytes};
   send_record(dst, encode((uint8_t)kMsgRead, index, rkey, (uint64_t)raddr, (uint64_t)bytes), nullptr, 0, nullptr);
 }
@@ -311,6 +381,15 @@ void TcpTransport::post_read_strided(int dst, void* local, uint64_t rows, size_t
   pend.rows = rows;
   pend.row_bytes = row_bytes;
   pend.dst_pitch = dst_pitch;
+  if (peers_[dst]->pid > 0 && (size_t)rows * row_bytes >= direct_min_) {
+    pend.raddr = raddr;
+    pend.src_pitch = src_pitch;
+    pend.peer = dst;
+    pending_[index] = std::move(pend);
+    uint64_t span = (rows - 1) * (uint64_t)src_pitch + row_bytes;
+    send_record(dst, encode((uint8_t)kMsgReadCheck, index, rkey, (uint64_t)raddr, span), nullptr, 0, nullptr);
+    return;
+  }
   pending_[index] = std::move(pend);
   send_record(dst, encode((uint8_t)kMsgReadStrided, index, rkey, (uint64_t)raddr, rows, (uint64_t)row_bytes, (uint64_t)src_pitch),
               nullptr, 0, nullptr);
@@ -477,6 +556,58 @@ void TcpTransport::handle_record(int peer, Reader& r) {
         auto keep = sc;
         p.conn->read_into(sc->base, sc->row_bytes, [keep] { keep->step(); });
       }
+      break;
+    }
+    case kMsgDirectOk: {
+      int64_t pid = r.read<int64_t>();
+      p.reads_me = pid > 0;
+      p.reader_pid = pid;
+      break;
+    }
+    case kMsgWriteDirect: {
+      uint64_t index, raddr, bytes, src;
+      uint32_t rkey;
+      r(index, rkey, raddr, bytes, src);
+      void* dst = MrTable::instance().check(rkey, (uintptr_t)raddr, bytes);
+      bool ok = dst != nullptr && p.pid > 0;
+      if (!ok) {
+        log_error("tcp transport: rank %d asked for a direct write outside registered memory (key %u, %llu bytes)", peer,
+                  rkey, (unsigned long long)bytes);
+      } else if (!vm_read(p.pid, dst, (uintptr_t)src, bytes)) {
+        log_error("tcp transport: reading %llu bytes from rank %d's memory failed: %s", (unsigned long long)bytes, peer,
+                  strerror(errno));
+        ok = false;
+      }
+      if (ok) {
+        bytes_direct_ += bytes;
+        MrTable::instance().add_landed(rkey, bytes);
+      }
+      send_record(peer, encode((uint8_t)(ok ? kMsgCompletionSuccess : kMsgCompletionError), index), nullptr, 0, nullptr);
+      break;
+    }
+    case kMsgReadCheck: {
+      uint64_t index, raddr, span;
+      uint32_t rkey;
+      r(index, rkey, raddr, span);
+      bool ok = MrTable::instance().check(rkey, (uintptr_t)raddr, span) != nullptr;
+      if (!ok) log_error("tcp transport: rank %d read outside registered memory (key %u)", peer, rkey);
+      send_record(peer, encode((uint8_t)(ok ? kMsgReadGranted : kMsgCompletionError), index), nullptr, 0, nullptr);
+      break;
+    }
+    case kMsgReadGranted: {
+      uint64_t index = r.read<uint64_t>();
+      auto it = pending_.find(index);
+      if (it == pending_.end()) break;
+      Pending pend = std::move(it->second);
+      pending_.erase(it);
+      bool ok = pend.rows <= 1 ? vm_read(p.pid, pend.local, pend.raddr, pend.bytes)
+                               : vm_read_strided(p.pid, pend.local, pend.dst_pitch, pend.raddr, pend.src_pitch, pend.rows,
+                                                 pend.row_bytes);
+      if (ok)
+        bytes_direct_ += pend.bytes;
+      else
+        log_error("tcp transport: reading from rank %d's memory failed: %s", peer, strerror(errno));
+      if (pend.done) pend.done(ok);
       break;
     }
     default:

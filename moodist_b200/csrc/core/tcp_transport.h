@@ -35,7 +35,21 @@ enum TcpMsg : uint8_t {
   // extension (not in the reference's record set): one request for `rows` runs of `row_bytes` bytes that lie
   // `src_pitch` apart; answered by one ReadSuccess whose payload is the runs back to back
   kMsgReadStrided = 7,
+  // extensions for two ranks on one machine that may read each other's address space (process_vm_readv):
+  // the bytes move with one copy made by the process that receives them, the connection only carries the
+  // request, the owner's bounds check and the completion.
+  kMsgDirectOk = 8,     // u8 | i64 pid : "I can read your memory" (sent once, after a successful probe)
+  kMsgWriteDirect = 9,  // u8 | u64 index | u32 rkey | uptr raddr | size_t bytes | uptr source address
+  kMsgReadCheck = 10,   // u8 | u64 index | u32 rkey | uptr raddr | size_t span : owner answers Granted / Error
+  kMsgReadGranted = 11, // u8 | u64 index
 };
+
+// Copies between this process and `pid` with process_vm_readv (the reference moves CPU tensors between ranks
+// of one machine the same way, core/cputhread.cc:3369-3379). False when the kernel refuses (ptrace rules,
+// another PID namespace) or the copy comes up short.
+bool vm_read(int64_t pid, void* local, uintptr_t remote, size_t bytes);
+bool vm_read_strided(int64_t pid, void* local, size_t dst_pitch, uintptr_t remote, size_t src_pitch, uint64_t rows,
+                     size_t row_bytes);
 
 // Process-global registered-memory table (reference: MrManager, core/rdma_tcp.cc:17-65).
 class MrTable {
@@ -84,8 +98,16 @@ class TcpTransport {
   // Return 0 to send normally, 1 to drop, 2 to send twice.
   std::function<int(int dst, const Bytes& payload)> fault_hook;
 
+  // Same-machine fast path. probe_direct: try to read the 8-byte word at `probe_addr` of process `pid` (rank
+  // `peer`); when it holds `probe_value` this rank may read that process, remembers it and tells the peer,
+  // which from then on lets this rank fetch the payload of its writes itself. Transfers below
+  // `direct_min_bytes` keep travelling inline on the connection.
+  bool probe_direct(int peer, int64_t pid, uintptr_t probe_addr, uint64_t probe_value);
+  void set_direct_min_bytes(size_t n) { direct_min_ = n; }
+
   uint64_t bytes_sent() const { return bytes_sent_; }
   uint64_t bytes_received() const { return bytes_recv_; }
+  uint64_t bytes_direct() const { return bytes_direct_; }  // payload bytes copied with process_vm_readv
 
  private:
   struct Peer;
@@ -107,9 +129,14 @@ class TcpTransport {
     size_t bytes = 0;
     uint64_t rows = 1;        // > 1: the reply is scattered, row_bytes at a time, dst_pitch apart
     size_t row_bytes = 0, dst_pitch = 0;
+    std::shared_ptr<void> keep;  // direct writes: the source stays alive until the receiver has fetched it
+    uintptr_t raddr = 0;         // direct reads: what to fetch once the owner has granted it
+    size_t src_pitch = 0;
+    int peer = -1;
   };
   std::unordered_map<uint64_t, Pending> pending_;
-  uint64_t bytes_sent_ = 0, bytes_recv_ = 0;
+  uint64_t bytes_sent_ = 0, bytes_recv_ = 0, bytes_direct_ = 0;
+  size_t direct_min_ = 8192;
   Bytes sink_;
 };
 

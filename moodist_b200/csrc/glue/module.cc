@@ -34,6 +34,22 @@ PYBIND11_MODULE(_C, m) {
           .def("kernel_launches", &MoodistBackend::kernelLaunches)
           .def("describe", &MoodistBackend::describe)
           .def(
+              "host_stats",
+              [](MoodistBackend& self) {
+                std::vector<uint64_t> c;
+                {
+                  py::gil_scoped_release nogil;
+                  c = self.hostGroup().transport_counters();
+                }
+                py::dict out;
+                out["tcp_bytes_sent"] = c.at(0);
+                out["tcp_bytes_received"] = c.at(1);
+                out["direct_bytes"] = c.at(2);
+                out["direct_peers"] = c.at(3);
+                return out;
+              },
+              "traffic of the host engine: bytes over TCP, bytes copied directly between processes of this machine")
+          .def(
               "stats",
               [](MoodistBackend& self, bool wait) {
                 // {"all_gather/nvls": {"calls": .., "bytes": .., "timed_calls": .., "device_us": ..}, ...}

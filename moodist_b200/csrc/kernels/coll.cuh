@@ -19,6 +19,16 @@
 namespace mb {
 namespace coll {
 
+// Register budget of the 512-thread collective kernels. A collective usually runs on a side stream under a
+// persistent tcgen05 GEMM that holds one CTA on every SM (192 threads x 120 registers = 23,040 of the SM's
+// 65,536, and nearly all of its shared memory). With 80 registers per thread a collective CTA takes 40,960
+// and fits beside it; at the 84-128 the compiler picks on its own it does not, and then either kernel keeps
+// the other off every SM it occupies: the GEMM runs on the SMs the collective left over and its statically
+// assigned tiles on the missing SMs wait for the collective to end. ptxas reports no spills at 80 for the
+// float / bf16 paths (a few hundred bytes for the 64-bit integer min / max variants).
+#define MB_COLL_REGS 80
+#define MB_COLL_BOUNDS __maxnreg__(MB_COLL_REGS)
+
 constexpr int kMaxCtas = 128;  // READY has room for this many producer CTAs per rank
 constexpr int F_DONE = 0;      // [8]
 constexpr int F_ANN = 16;      // [2][8][4]  {off_lo, off_hi, aux, seq}, bank = seq & 1 (a fast peer may already

@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(32, 1) barrier_kernel(const __grid_constant__ 
 // ---------------------------------------------------------------------------------------------
 // kCast: 0 bytes (same dtype), else converts InT -> OutT while staging.
 template <typename InT, typename OutT, bool kCast>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void MB_COLL_BOUNDS
     all_gather_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, int64_t in_heap_off,
                       void* out, size_t count, size_t out_stride) {
   // How this rank offers its shard (in_heap_off): >= 0 in place from its heap (mode 1), -1 staged locally and
@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 // reduce-scatter
 // ---------------------------------------------------------------------------------------------
 template <typename InT, typename OutT, int kOp>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void MB_COLL_BOUNDS
     reduce_scatter_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, int64_t in_heap_off,
                           void* out, size_t count, size_t in_stride, float scale, int use_scale) {
   const int b = blockIdx.x, G = gridDim.x;
@@ -218,7 +218,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 // ---------------------------------------------------------------------------------------------
 // one-shot: every rank pushes its whole vector to every peer's slot [rank], then reduces world inputs.
 template <typename T, int kOp>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void MB_COLL_BOUNDS
     all_reduce_oneshot_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, void* out,
                               size_t count, float scale, int use_scale) {
   const int b = blockIdx.x, G = gridDim.x;
@@ -249,7 +249,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 // two-shot in one launch: reduce-scatter into the owner, owner pushes the reduced chunk to everyone.
 template <typename T, int kOp>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void MB_COLL_BOUNDS
     all_reduce_twoshot_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, void* out,
                               size_t count, size_t chunk, float scale, int use_scale) {
   const int b = blockIdx.x, G = gridDim.x;
@@ -307,7 +307,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 // ---------------------------------------------------------------------------------------------
 // broadcast (pull from the root's staging copy, or straight from the root's heap memory)
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void MB_COLL_BOUNDS
     broadcast_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, void* data, int64_t heap_off, size_t bytes,
                      int root) {
   const int b = blockIdx.x, G = gridDim.x;
@@ -351,7 +351,7 @@ __device__ __forceinline__ size_t a2a_first_half(size_t bytes) {
   if (bytes < (1u << 20)) return bytes;
   return (bytes / 2) & ~(size_t)255;
 }
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void MB_COLL_BOUNDS
     all_to_all_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, int64_t out_heap_off,
                       void* out, const __grid_constant__ mb_a2a_table_t tab) {
   const int b = blockIdx.x, G = gridDim.x;
@@ -450,7 +450,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 // ---------------------------------------------------------------------------------------------
 // compile_op lowering: 2-D pieces, sources in peers' staging areas (inputs are staged first)
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void MB_COLL_BOUNDS
     gather_scatter_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const mb_stage_copy_t* stage_in,
                           int num_stage, const mb_piece_t* pieces, int num_pieces) {
   const int b = blockIdx.x, G = gridDim.x;
@@ -510,14 +510,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 // local cast / scale copy (world == 1 paths, staging helpers)
 // ---------------------------------------------------------------------------------------------
 template <typename InT, typename OutT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void MB_COLL_BOUNDS
     copy_cast_kernel(const void* in, void* out, size_t count, float scale, int use_scale) {
   size_t begin, len;
   slice_of(count, gridDim.x, blockIdx.x, begin, len);
   cta_cast_copy<InT, OutT>(reinterpret_cast<OutT*>(out) + begin, reinterpret_cast<const InT*>(in) + begin, len,
                            scale, use_scale);
 }
-__global__ void __launch_bounds__(kThreads, 1) copy_bytes_kernel(const void* in, void* out, size_t bytes) {
+__global__ void MB_COLL_BOUNDS copy_bytes_kernel(const void* in, void* out, size_t bytes) {
   size_t begin, len;
   slice_of(bytes, gridDim.x, blockIdx.x, begin, len);
   cta_copy(reinterpret_cast<uint8_t*>(out) + begin, reinterpret_cast<const uint8_t*>(in) + begin, len);
@@ -690,7 +690,7 @@ __global__ void __launch_bounds__(32, 1) ce_end_kernel(const __grid_constant__ m
 }
 // out[0..count) = op over `nsrc` local buffers (this rank's own slice and the staged slices of the peers)
 template <typename InT, typename OutT, int kOp>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void MB_COLL_BOUNDS
     reduce_local_kernel(const InT* s0, const InT* staged, size_t slot_stride, int rank, int world, OutT* out,
                         size_t count, float scale, int use_scale) {
   size_t begin, len;

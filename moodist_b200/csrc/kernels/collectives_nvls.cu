@@ -61,7 +61,7 @@ __device__ __forceinline__ bool wait_all_ready(const mb_comm_t& c, uint32_t seq,
 
 // count elements, chunk = elements per rank (multiple of 64); region A [world*chunk] inputs, region B results
 template <typename T>
-__global__ void __launch_bounds__(kNvlsThreads, 1)
+__global__ void MB_COLL_BOUNDS
     all_reduce_nvls_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, void* out, size_t count,
                            size_t chunk, float scale, int use_scale) {
   constexpr int N = 16 / sizeof(T);
@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 1)
 
 // out[count] = reduce over ranks of in[rank*in_stride ..]; count multiple of 64 handled by padding rules of the caller
 template <typename T, typename OutT>
-__global__ void __launch_bounds__(kNvlsThreads, 1)
+__global__ void MB_COLL_BOUNDS
     reduce_scatter_nvls_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, void* out, size_t count,
                                size_t in_stride, float scale, int use_scale) {
   constexpr int N = 16 / sizeof(T);
@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 1)
 }
 
 // bytes per rank; every rank's shard goes to all staging areas with one multimem.st stream
-__global__ void __launch_bounds__(kNvlsThreads, 1)
+__global__ void MB_COLL_BOUNDS
     all_gather_nvls_kernel(const __grid_constant__ mb_comm_t c, uint32_t seq, const void* in, void* out, size_t bytes,
                            size_t out_stride) {
   const int b = blockIdx.x, G = gridDim.x;

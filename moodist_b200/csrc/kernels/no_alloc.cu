@@ -4,6 +4,8 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include "coll.cuh"
 
 namespace {
@@ -47,17 +49,17 @@ __global__ void __launch_bounds__(kThreads, 1) strided_copy_kernel(const mb_piec
 // Device address of the table, looked up once per device with that device current. In host code the
 // array's name is only a handle for the runtime, never something to hand to a kernel.
 mb_piece_t* table_address(int device) {
-  static void* addr[64] = {};
+  static std::atomic<void*> addr[64];  // zero-initialised; concurrent first calls store the same address
   if (device < 0 || device >= 64) return nullptr;
-  if (!addr[device]) {
-    void* p = nullptr;
+  void* p = addr[device].load(std::memory_order_acquire);
+  if (!p) {
     if (cudaGetSymbolAddress(&p, g_piece_table) != cudaSuccess || !p) {
       cudaGetLastError();
       return nullptr;
     }
-    addr[device] = p;
+    addr[device].store(p, std::memory_order_release);
   }
-  return static_cast<mb_piece_t*>(addr[device]);
+  return static_cast<mb_piece_t*>(p);
 }
 
 }  // namespace

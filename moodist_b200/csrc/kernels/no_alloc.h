@@ -4,9 +4,8 @@
 //
 // Who needs it: code that runs inside someone else's memory budget or critical section — a plugin
 // loaded into an inference server whose device memory is fully pre-planned, a signal/health handler,
-// a teardown or out-of-memory recovery path, a region between cudaStreamBeginCapture/EndCapture of a
-// host application — cannot call cudaMalloc (it may fail, block on other streams, or simply be
-// forbidden by the host application's rules). The regular strided-copy entry point, mb_gather_scatter,
+// a teardown or out-of-memory recovery path — cannot call cudaMalloc (it may fail, block on other
+// streams, or simply be forbidden by the host application's rules). The regular strided-copy entry point, mb_gather_scatter,
 // needs its table of copy pieces in device memory that somebody has to allocate. This variant keeps that
 // table in a fixed array compiled into the library instead.
 //
@@ -20,7 +19,8 @@
 //   * the table lives in a static device array of MB_NOALLOC_MAX_PIECES * sizeof(mb_piece_t) bytes that
 //     every GPU which loads this library holds until the process exits;
 //   * the first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
-//     first call before any stream capture begins;
+//     first call before any stream capture begins. Threads may make first calls at the same time: the
+//     address is cached in an atomic, and two threads that both look it up store the same value;
 //   * all calls share the one array per device and it keeps the previous call's table, so two calls whose
 //     kernels could overlap on the GPU (different streams, no ordering between them) race: order them on
 //     one stream or with events. The table upload itself is ordered on `stream` before the kernel;

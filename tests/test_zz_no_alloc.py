@@ -2,8 +2,8 @@
 gather/scatter entry point run as a one-rank group.
 
 Some callers of the kernel library may not allocate device memory (a plugin inside a server with a fixed
-memory plan, a recovery or teardown path, code between stream-capture calls of a host application), so
-``mb_strided_copy_noalloc`` keeps its piece table in a static device array.  The test runs both entry
+memory plan, a recovery or teardown path), so ``mb_strided_copy_noalloc`` keeps its piece table in a static
+device array.  The test runs both entry
 points on the same pieces, twice in a row (the second call reuses the array with a different table), and
 expects bit-identical outputs: both are pure copies.  Collected last so that a failure here cannot hide
 the result of any other test.
@@ -123,6 +123,49 @@ def test_noalloc_strided_copy_matches_regular_entry_point():
         assert torch.equal(b0[: R - variant], src[: R - variant, C // 2:])
         if variant:
             assert torch.equal(b0[R - variant:].reshape(-1), src.reshape(-1)[: variant * (C // 2)])
+
+
+def _fill(arr, specs):
+    for p, (s, d, rows, rb, sp, dp) in zip(arr, specs):
+        p.src_rank, p.rows, p.src_off, p.src_local, p.dst = 0, rows, 0, s, d
+        p.row_bytes, p.src_pitch, p.dst_pitch = rb, sp, dp
+
+
+def test_noalloc_unaligned_pieces_and_full_table():
+    """Pieces off every 16-byte boundary (odd row length, odd pitches, source pointer moved by three bytes,
+    an empty piece), then a call that fills the table to its last slot."""
+    lib = _lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator().manual_seed(11)
+    src = torch.randint(0, 256, (200_000,), generator=g, dtype=torch.uint8).to(dev)
+    dst = torch.zeros(200_000, dtype=torch.uint8, device=dev)
+    rows, rb, sp, dp = 37, 1003, 2011, 1005
+    specs = [
+        (src.data_ptr() + 3, dst.data_ptr() + 1, rows, rb, sp, dp),          # strided, nothing aligned
+        (src.data_ptr() + 100_001, dst.data_ptr() + 100_003, 1, 12_345, 12_345, 12_345),  # contiguous, unaligned
+        (src.data_ptr(), dst.data_ptr() + 199_000, 0, 64, 64, 64),           # no rows: copies nothing
+    ]
+    arr = (Piece * len(specs))()
+    _fill(arr, specs)
+    assert lib.mb_strided_copy_noalloc(arr, len(arr), stream) == 0
+    torch.cuda.synchronize()
+    s_host, d_host = src.cpu(), dst.cpu()
+    want = torch.zeros(200_000, dtype=torch.uint8)
+    for r in range(rows):
+        want[1 + r * dp : 1 + r * dp + rb] = s_host[3 + r * sp : 3 + r * sp + rb]
+    want[100_003 : 100_003 + 12_345] = s_host[100_001 : 100_001 + 12_345]
+    assert torch.equal(d_host, want)
+    # exactly MB_NOALLOC_MAX_PIECES pieces of 48 bytes each: a gather of every other 48-byte block
+    n = 4096
+    dst2 = torch.zeros(n * 48, dtype=torch.uint8, device=dev)
+    specs = [(src.data_ptr() + i * 96, dst2.data_ptr() + i * 48, 1, 48, 48, 48) for i in range(n)]
+    arr = (Piece * n)()
+    _fill(arr, specs)
+    assert lib.mb_strided_copy_noalloc(arr, n, stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dst2.cpu().view(n, 48), s_host[: n * 96].view(n, 96)[:, :48])
 
 
 def test_noalloc_rejects_oversized_tables():
