@@ -417,6 +417,23 @@ class HostGroupImpl final : public HostGroup {
     return *out;
   }
 
+  void inject_faults(int drop_every, int duplicate_every, int delay_ms) override {
+    run_on_engine([this, drop_every, duplicate_every, delay_ms] {
+      if (drop_every <= 0 && duplicate_every <= 0 && delay_ms <= 0) {
+        transport_.fault_hook = nullptr;
+        return;
+      }
+      auto count = std::make_shared<uint64_t>(0);
+      transport_.fault_hook = [=](int, const Bytes&) {
+        uint64_t n = ++*count;
+        if (delay_ms > 0) usleep((useconds_t)delay_ms * 1000);
+        if (drop_every > 0 && n % (uint64_t)drop_every == 0) return 1;
+        if (duplicate_every > 0 && n % (uint64_t)duplicate_every == 0) return 2;
+        return 0;
+      };
+    });
+  }
+
   bool in_error() const override { return error_state_.load(); }
   std::string error_text() const override {
     std::lock_guard<std::mutex> lk(error_mu_);
@@ -509,7 +526,16 @@ class HostGroupImpl final : public HostGroup {
       std::lock_guard<std::mutex> lk(error_mu_);
       if (error_text_.empty()) error_text_ = why;
     }
-    if (!error_state_.exchange(true)) log_error("process group %s rank %d: %s", name_.c_str(), rank_, why.c_str());
+    if (!error_state_.exchange(true)) {
+      log_error("process group %s rank %d: %s", name_.c_str(), rank_, why.c_str());
+      // tell the others: their collectives with this rank can no longer complete, and without this notice
+      // they would only find out through the heartbeat
+      std::string text = strf("rank %d reported: %s", rank_, why.c_str());
+      run_on_engine([this, text] {
+        for (int p = 0; p < world_; ++p)
+          if (p != rank_ && !peer_shutdown_[p]) send_message(p, kOpErrorNotice, encode(text));
+      });
+    }
   }
 
   void on_peer_error(int peer, const std::string& why) {
@@ -663,6 +689,10 @@ class HostGroupImpl final : public HostGroup {
       last_heard_[src] = now_seconds();
       switch (op) {
         case kOpHeartbeat: return;
+        case kOpErrorNotice: {
+          set_error(r.read<std::string>());
+          return;
+        }
         case kOpMessageShutdown: {
           bool begin = r.read<bool>();
           peer_shutdown_[src] = begin ? 1 : 2;

@@ -47,6 +47,8 @@ enum OpType : uint32_t {
   kOpHeartbeat = 99,    // the reference heartbeats with RDMA writes; over plain TCP it is a message
   kOpScatterCpu = 100,  // not in the reference (scatter throws there)
   kOpSendRecv = 101,    // point-to-point payloads (send/recv are unsupported in the reference)
+  kOpErrorNotice = 102, // "this rank entered its error state because ...": the receivers enter theirs at once
+                        // (the reference's ranks learn of a peer's error state only when that process exits)
 };
 
 struct TraceEvent {
@@ -98,6 +100,10 @@ class HostGroup {
   // {payload+header bytes sent over TCP, received over TCP, payload bytes copied directly between address
   // spaces of this machine, number of peers this rank reads directly}
   virtual std::vector<uint64_t> transport_counters() = 0;
+  // Host-side fault injection for tests, applied to the two-sided engine messages this rank sends from now on:
+  // every `drop_every`-th is dropped, every `duplicate_every`-th is sent twice, and each one is held back for
+  // `delay_ms` first (0 switches a kind off). One-sided payload transfers are not touched.
+  virtual void inject_faults(int drop_every, int duplicate_every, int delay_ms) = 0;
   virtual bool in_error() const = 0;
   virtual std::string error_text() const = 0;
   virtual void shutdown() = 0;  // coordinated: tells every peer, waits briefly for theirs

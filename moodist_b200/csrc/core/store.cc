@@ -104,6 +104,11 @@ enum MsgType : uint8_t {
   kCompareSet = 0xd,
   kDelete = 0xe,
   kNumKeys = 0xf,
+  // diagnostics of a request that timed out: a probe follows the route of the request; every rank it passes
+  // (and the owner) reports back to the origin what it sees (the reference gathers the same reports from the
+  // intermediate hops over a UDP side channel, core/store.cc:707-794, 1799-1907)
+  kDiagnosticProbe = 0x10,
+  kDiagnosticInfo = 0x11,
 };
 
 // In-memory image is what travels (28 bytes, little-endian), as in the reference (core/store.cc:49-63).
@@ -196,6 +201,8 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
     }
     exit_seen_.assign(world, false);
     shutdown_seen_.assign(world, false);
+    keepalive_s_ = (double)env_long("MOODIST_STORE_KEEPALIVE_MS", 20000) / 1000.0;
+    fault_break_every_ = (int)env_long("MOODIST_STORE_FAULT_BREAK_EVERY", 0);
     thread_ = std::thread([this] { run(); });
     // the constructor returns once the mesh edges of this rank are up (or the timeout expires)
     double deadline = now_seconds() + std::max(1.0, (double)timeout.count() / 1000.0);
@@ -222,6 +229,18 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
   std::chrono::milliseconds timeout() const override { return timeout_; }
   void set_timeout(std::chrono::milliseconds t) override { timeout_ = t; }
   std::vector<int> edges() const override { return mesh_[rank_]; }
+  void inject_faults(int break_every) override {
+    post([this, break_every] { fault_break_every_ = break_every; });
+  }
+  uint64_t injected_breaks() override {
+    auto w = std::make_shared<WaitObj>();
+    post([this, w] { w->finish(encode(fault_breaks_)); });
+    std::unique_lock<std::mutex> lk(w->mu);
+    if (!w->cv.wait_for(lk, std::chrono::seconds(2), [&] { return w->done; })) return 0;
+    uint64_t n = 0;
+    decode_exact(w->result, n);
+    return n;
+  }
 
   // ---------------------------------------------------------------------------------------------
   // operations (caller threads)
@@ -314,7 +333,7 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
       w->cv.wait_for(lk, std::chrono::milliseconds(250));  // sliced so signals and shutdown are noticed
       if (!w->done && now_seconds() - start > limit) {
         lk.unlock();
-        std::string diag = diagnose(dest);
+        std::string diag = diagnose(dest, what);
         post([this, idp] { pending_.erase(*idp); });
         fail(strf("TcpStore(%s): timed out after %.1f s on key '%s' (owner rank %d). %s", store_key_.c_str(),
                   now_seconds() - start, what.c_str(), dest, diag.c_str()));
@@ -324,10 +343,12 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
     return std::move(w->result);
   }
 
-  // which hop of the route to `dest` looks unhealthy, from this rank's point of view
-  std::string diagnose(int dest) {
+  // Which hop of the route to `dest` looks unhealthy: this rank's own view of its first hop, plus what every
+  // rank further along the route (and the owner of the key) answers to a probe within about a second.
+  std::string diagnose(int dest, const std::string& key) {
     auto w = std::make_shared<WaitObj>();
-    post([this, dest, w] {
+    auto idp = std::make_shared<uint32_t>(0);
+    post([this, dest, key, w, idp] {
       std::string s;
       if (dest == rank_) {
         s = "The key lives on this rank and was never set.";
@@ -341,13 +362,70 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
           s = strf("Route: rank %d -> rank %d%s. Edge to rank %d: %s, %zu unacknowledged messages, last heard %.1f s ago.",
                    rank_, hop, hop == dest ? "" : " -> ...", hop, e.connected ? "connected" : "NOT connected",
                    e.unacked.size(), now_seconds() - e.last_recv);
+          uint32_t id = next_id_++;
+          *idp = id;
+          diag_reports_[id];
+          send_to(dest, kDiagnosticProbe, id, encode(key));
         }
       }
       w->finish(Bytes(s.begin(), s.end()));
     });
-    std::unique_lock<std::mutex> lk(w->mu);
-    if (!w->cv.wait_for(lk, std::chrono::seconds(1), [&] { return w->done; })) return "";
-    return std::string(w->result.begin(), w->result.end());
+    std::string text;
+    {
+      std::unique_lock<std::mutex> lk(w->mu);
+      if (!w->cv.wait_for(lk, std::chrono::seconds(1), [&] { return w->done; })) return "";
+      text.assign(w->result.begin(), w->result.end());
+    }
+    if (*idp == 0) return text;
+    // reports trickle in while the probe travels; the owner's report ends the wait early
+    auto done = std::make_shared<WaitObj>();
+    double deadline = now_seconds() + (double)env_long("MOODIST_STORE_DIAGNOSE_MS", 1000) / 1000.0;
+    std::vector<std::string> reports;
+    bool reached = false;
+    while (now_seconds() < deadline && !reached) {
+      usleep(20000);
+      auto got = std::make_shared<WaitObj>();
+      post([this, idp, got] {
+        std::string all;
+        for (const std::string& r : diag_reports_[*idp]) all += r + "\n";
+        got->finish(Bytes(all.begin(), all.end()));
+      });
+      std::unique_lock<std::mutex> lk(got->mu);
+      if (!got->cv.wait_for(lk, std::chrono::milliseconds(500), [&] { return got->done; })) break;
+      std::string all(got->result.begin(), got->result.end());
+      reports.clear();
+      size_t pos = 0;
+      while (pos < all.size()) {
+        size_t e = all.find('\n', pos);
+        reports.push_back(all.substr(pos, e - pos));
+        pos = e + 1;
+      }
+      for (const std::string& r : reports) reached = reached || r.find("owner") != std::string::npos;
+    }
+    post([this, idp] { diag_reports_.erase(*idp); });
+    for (const std::string& r : reports) text += " " + r;
+    if (!reached) text += " The probe did not reach the owner within the diagnosis window.";
+    return text;
+  }
+
+  // a rank that forwards (or owns the target of) a diagnostic probe tells the origin what it sees
+  void report_probe(const MessageHeader& h, int next_hop, const std::string& key) {
+    std::string s;
+    if (next_hop < 0) {
+      auto wit = waiters_.find(key);
+      s = strf("Rank %d (owner): the probe arrived; key '%s' %s, %zu request(s) wait for it.", rank_, key.c_str(),
+               kv_.count(key) ? "IS set" : "has not been set", wit == waiters_.end() ? (size_t)0 : wit->second.size());
+    } else {
+      auto it = edges_.find(next_hop);
+      if (it == edges_.end()) {
+        s = strf("Rank %d: no edge towards rank %d.", rank_, next_hop);
+      } else {
+        const Edge& e = it->second;
+        s = strf("Rank %d: forwards to rank %d over an edge that is %s, %zu unacknowledged messages, last heard %.1f s ago.",
+                 rank_, next_hop, e.connected ? "connected" : "NOT connected", e.unacked.size(), now_seconds() - e.last_recv);
+      }
+    }
+    send_to((int)h.sourceRank, kDiagnosticInfo, h.id, encode(s));
   }
 
   void stop_thread() {
@@ -596,9 +674,9 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
         continue;
       }
       // keepalive: ping after 20 s of silence, drop after 40 s (reference: core/store.cc:1563-1615)
-      if (now - e.last_recv > 40) {
-        e.conn->close("no traffic for 40 s");
-      } else if (now - e.last_recv > 20 && now - e.last_send > 5) {
+      if (now - e.last_recv > 2 * keepalive_s_) {
+        e.conn->close("no traffic for twice the keepalive interval");
+      } else if (now - e.last_recv > keepalive_s_ && now - e.last_send > keepalive_s_ / 4) {
         e.conn->send_frame(encode(kSigKeepalive));
         e.last_send = now;
       }
@@ -652,6 +730,13 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
     w.raw(payload, n);
     e.unacked.emplace_back(h.seq, w.out);
     if (e.connected && e.conn && e.conn->open()) {
+      if (fault_break_every_ > 0 && ++fault_count_ % (uint64_t)fault_break_every_ == 0) {
+        // injected fault: the message is lost with its connection; the redial retransmits it (and anything else
+        // the peer has not acknowledged) in order, and the peer drops what it had seen already
+        ++fault_breaks_;
+        e.conn->close("injected fault");
+        return;
+      }
       e.conn->send_frame(w.out);
       e.last_send = now_seconds();
     }
@@ -693,6 +778,10 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
       if (h.ttl <= 1) {
         log_error("TcpStore rank %d: dropping a message for rank %u whose TTL ran out", rank_, h.destinationRank);
         return;
+      }
+      if (h.messageType == kDiagnosticProbe) {
+        Reader rr(r.p, r.remaining());
+        report_probe(h, first_hop_[h.destinationRank], rr.read<std::string>());
       }
       MessageHeader f = h;
       f.ttl = h.ttl - 1;
@@ -791,6 +880,12 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
         return;
       }
       case kNumKeys: reply(h, encode((int64_t)kv_.size())); return;
+      case kDiagnosticProbe: report_probe(h, -1, r.read<std::string>()); return;
+      case kDiagnosticInfo: {
+        auto it = diag_reports_.find(h.id);
+        if (it != diag_reports_.end()) it->second.push_back(r.read<std::string>());
+        return;
+      }
       case kShutdown: shutdown_seen_[h.sourceRank] = true; return;
       case kExit: {
         exit_seen_[h.sourceRank] = true;
@@ -875,6 +970,10 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
   std::unordered_map<std::string, Bytes> kv_;
   std::unordered_map<std::string, std::vector<PendingAtOwner>> waiters_;
   std::unordered_map<uint32_t, std::shared_ptr<WaitObj>> pending_;
+  std::unordered_map<uint32_t, std::vector<std::string>> diag_reports_;  // probe id -> reports received so far
+  int fault_break_every_ = 0;   // test hook: every Nth message, the edge's connection is cut instead of used
+  uint64_t fault_count_ = 0, fault_breaks_ = 0;
+  double keepalive_s_ = 20;     // ping after this much silence, drop the connection after twice as much
   std::set<uint64_t> seen_broadcast_;
   uint32_t next_id_ = 1;
   std::string error_;

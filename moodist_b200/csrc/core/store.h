@@ -54,6 +54,11 @@ class TcpStore : public KVStore {
   // Starts the coordinated shutdown; called by the destructor of the last handle.
   virtual void shutdown() = 0;
 
+  // Host-side fault injection for tests: from now on every `break_every`-th message this rank sends over a mesh
+  // edge is lost together with its connection (0 switches it off). The edge redials and retransmits.
+  virtual void inject_faults(int break_every) = 0;
+  virtual uint64_t injected_breaks() = 0;
+
   // Mesh introspection (tests, diagnostics)
   virtual std::vector<int> edges() const = 0;
   virtual std::string describe() const = 0;

@@ -34,6 +34,13 @@ PYBIND11_MODULE(_C, m) {
           .def("kernel_launches", &MoodistBackend::kernelLaunches)
           .def("describe", &MoodistBackend::describe)
           .def(
+              "_inject_faults",
+              [](MoodistBackend& self, int drop_every, int duplicate_every, int delay_ms) {
+                self.hostGroup().inject_faults(drop_every, duplicate_every, delay_ms);
+              },
+              py::arg("drop_every") = 0, py::arg("duplicate_every") = 0, py::arg("delay_ms") = 0,
+              "test hook (host engine): drop / duplicate every N-th two-sided message this rank sends, delay each one")
+          .def(
               "host_stats",
               [](MoodistBackend& self) {
                 std::vector<uint64_t> c;

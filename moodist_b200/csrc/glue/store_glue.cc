@@ -53,6 +53,8 @@ class TcpStoreGlue final : public c10d::Store {
 #undef GUARD
   std::string describe() const { return impl_->describe(); }
   std::vector<int> edges() const { return impl_->edges(); }
+  void injectFaults(int break_every) { impl_->inject_faults(break_every); }
+  uint64_t injectedBreaks() { return impl_->injected_breaks(); }
 
  private:
   std::shared_ptr<TcpStore> impl_;
@@ -70,7 +72,10 @@ void bind_store(pybind11::module_& m) {
            py::arg("hostname"), py::arg("port"), py::arg("key"), py::arg("world_size"), py::arg("rank"),
            py::arg("timeout") = std::chrono::milliseconds(300000), py::call_guard<py::gil_scoped_release>())
       .def("describe", &TcpStoreGlue::describe)
-      .def("edges", &TcpStoreGlue::edges);
+      .def("edges", &TcpStoreGlue::edges)
+      .def("_inject_faults", &TcpStoreGlue::injectFaults, py::arg("break_every"),
+           "test hook: every N-th message this rank sends over a mesh edge is lost with its connection (0: off)")
+      .def("_injected_breaks", &TcpStoreGlue::injectedBreaks);
   m.def("store_string_hash", &store_string_hash);
   m.def("store_mesh", &store_mesh);
 }

@@ -139,7 +139,7 @@ def test_noalloc_unaligned_pieces_and_full_table():
     torch.cuda.set_device(0)
     stream = torch.cuda.current_stream().cuda_stream
     g = torch.Generator().manual_seed(11)
-    src = torch.randint(0, 256, (200_000,), generator=g, dtype=torch.uint8).to(dev)
+    src = torch.randint(0, 256, (400_000,), generator=g, dtype=torch.uint8).to(dev)  # 4096 x 96 bytes fit
     dst = torch.zeros(200_000, dtype=torch.uint8, device=dev)
     rows, rb, sp, dp = 37, 1003, 2011, 1005
     specs = [
