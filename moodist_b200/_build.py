@@ -54,7 +54,17 @@ def _q(s) -> str:
     return str(s).replace(" ", "$ ")
 
 
-def generate(with_torch: bool = True) -> Path:
+SANITIZERS = ("address", "thread", "undefined")
+
+
+def generate(with_torch: bool = True, sanitize: str | None = None) -> Path:
+    """Write the ninja file.  ``sanitize`` ("address", "thread" or "undefined") describes a second build of the
+    torch-free core with that sanitizer, in ``build/native-<sanitizer>/`` (nothing in-tree is touched): the host
+    sources are recompiled with ``-fsanitize=...``, the CUDA objects of the regular build are linked in as they
+    are.  The reference has the same switches in its CMake file (``ENABLE_ASAN`` / ``ENABLE_TSAN``,
+    ``CMakeLists.txt:6-25, 213-218``)."""
+    if sanitize is not None:
+        return _generate_sanitized(sanitize)
     cuda = _cuda_home()
     BUILD.mkdir(parents=True, exist_ok=True)
     pyinc = sysconfig.get_paths()["include"]
@@ -144,10 +154,63 @@ def generate(with_torch: bool = True) -> Path:
     return path
 
 
-def build(with_torch: bool = True, verbose: bool = False) -> None:
-    """Build (incrementally) all native libraries for sm_100a."""
+def sanitized_dir(sanitize: str) -> Path:
+    return BUILD.parent / f"native-{sanitize}"
+
+
+def _generate_sanitized(sanitize: str) -> Path:
+    if sanitize not in SANITIZERS:
+        raise ValueError(f"unknown sanitizer {sanitize!r}: one of {SANITIZERS}")
+    cuda = _cuda_home()
+    out = sanitized_dir(sanitize)
+    out.mkdir(parents=True, exist_ok=True)
+    cxx = os.environ.get("MOODIST_CXX", "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
+    san = f"-fsanitize={sanitize} -fno-omit-frame-pointer"
+    if sanitize == "undefined":
+        san += " -fno-sanitize-recover=undefined"
+    common = f"-O1 -g -fPIC -std=c++20 -Wall -Wno-unused-function -pthread {san} -I{CSRC} -I{cuda}/include"
+    lines = [
+        f"cxx = {cxx}",
+        f"cflags = {common}",
+        "rule cxx",
+        "  command = $cxx $cflags -MMD -MF $out.d -c $in -o $out",
+        "  depfile = $out.d",
+        "  deps = gcc",
+        "rule link",
+        "  command = $cxx -shared -o $out $in $ldflags",
+        "",
+    ]
+    objs = []
+    for src in _sources("core", (".cc",)):
+        obj = out / "core" / (src.stem + ".o")
+        lines.append(f"build {_q(obj)}: cxx {_q(src)}")
+        objs.append(obj)
+    # device code is not instrumented: the objects nvcc made for the regular build are reused
+    kernel_objs = [BUILD / "kernels" / (src.stem + ".o") for src in _sources("kernels", (".cu",))]
+    lib = out / "libmoodist_b200.so"
+    lines.append(f"build {_q(lib)}: link {' '.join(_q(o) for o in objs + kernel_objs)}")
+    lines.append(f"  ldflags = {san} -L{cuda}/lib64 -lcudart_static -lrt -ldl -pthread")
+    lines.append(f"default {_q(lib)}")
+    path = out / "build.ninja"
+    text = "\n".join(lines) + "\n"
+    if not path.exists() or path.read_text() != text:
+        path.write_text(text)
+    return path
+
+
+def build(with_torch: bool = True, verbose: bool = False, sanitize: str | None = None) -> None:
+    """Build (incrementally) all native libraries for sm_100a; with ``sanitize`` the instrumented core as well."""
     generate(with_torch)
     jobs = os.environ.get("MOODIST_BUILD_JOBS", str(os.cpu_count() or 4))
+    if sanitize is not None:
+        build(with_torch=False, verbose=verbose)  # the CUDA objects come from the regular build
+        generate(sanitize=sanitize)
+        cmd = [sys.executable, "-m", "ninja", "-C", str(sanitized_dir(sanitize)), "-j", jobs]
+        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout[-20000:])
+            raise RuntimeError(f"{sanitize}-sanitizer build failed")
+        return
     cmd = [sys.executable, "-m", "ninja", "-C", str(BUILD), "-j", jobs]
     if verbose:
         cmd.append("-v")
@@ -160,5 +223,12 @@ def build(with_torch: bool = True, verbose: bool = False) -> None:
 
 
 if __name__ == "__main__":
-    build(with_torch="--no-torch" not in sys.argv, verbose="-v" in sys.argv)
-    print("built:", ", ".join(p.name for p in sorted(ROOT.glob("*.so"))))
+    san = next((a.split("=", 1)[1] for a in sys.argv if a.startswith("--sanitize=")), None)
+    if "--sanitize" in sys.argv:
+        san = sys.argv[sys.argv.index("--sanitize") + 1]
+    if san:
+        build(sanitize=san, verbose="-v" in sys.argv)
+        print("built:", sanitized_dir(san) / "libmoodist_b200.so")
+    else:
+        build(with_torch="--no-torch" not in sys.argv, verbose="-v" in sys.argv)
+        print("built:", ", ".join(p.name for p in sorted(ROOT.glob("*.so"))))

@@ -134,6 +134,7 @@ struct TcpTransport::Peer {
     std::shared_ptr<void> keep;
   };
   std::deque<Queued> backlog;  // records issued before the connection was ready
+  std::function<void()> dial;  // tries the next advertised address of this peer (dialing side only)
 };
 
 TcpTransport::TcpTransport(Poller& poller, std::string group, int rank, int world)
@@ -202,9 +203,9 @@ void TcpTransport::connect_all(const std::vector<std::vector<std::string>>& addr
       p.candidates.emplace_back(s.substr(0, sp), atoi(s.c_str() + sp + 1));
     }
     // Same host is the common case here: loopback works even when no other interface is shared.
-    std::function<void()> dial;
-    auto dial_ptr = std::make_shared<std::function<void()>>();
-    *dial_ptr = [this, r, dial_ptr]() {
+    // the closure lives in the peer record and refers to itself through it (a shared_ptr to itself would
+    // never be released)
+    p.dial = [this, r]() {
       Peer& p = *peers_[r];
       if (p.ready) return;
       if (p.candidates.empty()) {
@@ -218,14 +219,14 @@ void TcpTransport::connect_all(const std::vector<std::vector<std::string>>& addr
       auto cand = p.candidates[p.next_candidate % p.candidates.size()];
       ++p.next_candidate;
       ++p.attempts;
-      poller_.connect(cand.first, cand.second, [this, r, dial_ptr](std::shared_ptr<Conn> c) {
+      poller_.connect(cand.first, cand.second, [this, r](std::shared_ptr<Conn> c) {
         Peer& p = *peers_[r];
         if (p.ready) {
           if (c) c->close("not needed");
           return;
         }
         if (!c) {
-          (*dial_ptr)();
+          p.dial();
           return;
         }
         c->send_frame(encode(kTcpDevSig, group_, (uint32_t)rank_));
@@ -257,12 +258,12 @@ void TcpTransport::connect_all(const std::vector<std::vector<std::string>>& addr
           }
         });
         c->on_data([reader](const uint8_t* d, size_t n) { return (*reader)(d, n); });
-        c->on_close([this, r, dial_ptr, greeted](const std::string&) {
-          if (!*greeted) (*dial_ptr)();  // wrong process behind that address: try the next one
+        c->on_close([this, r, greeted](const std::string&) {
+          if (!*greeted) peers_[r]->dial();  // wrong process behind that address: try the next one
         });
       });
     };
-    (*dial_ptr)();
+    p.dial();
   }
 }
 
