@@ -20,15 +20,15 @@ import torch
 
 from ._core import LIB_PATH, _C
 
-_pluggable = None
 _enabled = False
 
 
-def _pluggable_allocator():
-    global _pluggable
-    if _pluggable is None:
-        _pluggable = torch.cuda.memory.CUDAPluggableAllocator(LIB_PATH, "mb_cuda_alloc", "mb_cuda_free")
-    return _pluggable
+def _allocator():
+    """The symmetric-heap allocator as torch's allocator object.  It is created natively so that the hooks
+    Python's ``CUDAPluggableAllocator`` cannot install are there too: ``Tensor.record_stream`` reaches the heap
+    (a block used on a side stream is not handed out again before that stream is done with it) and
+    ``getBaseAllocation`` answers."""
+    return _C.cuda_allocator()
 
 
 def enable_cuda_allocator() -> None:
@@ -36,7 +36,9 @@ def enable_cuda_allocator() -> None:
     global _enabled
     if _enabled:
         return
-    torch.cuda.memory.change_current_allocator(_pluggable_allocator())
+    if torch.cuda.is_initialized() and torch.cuda.memory_allocated() > 0:
+        raise RuntimeError("enable_cuda_allocator() must be called before the first CUDA allocation of the process")
+    _C.enable_cuda_allocator()
     _enabled = True
 
 
@@ -47,13 +49,13 @@ def cuda_allocator_enabled() -> bool:
 def symmetric_mem_pool() -> "torch.cuda.MemPool":
     """A ``torch.cuda.MemPool`` backed by the symmetric heap, for ``torch.cuda.use_mem_pool``; tensors
     allocated from it stay valid for as long as the pool object is alive."""
-    return torch.cuda.MemPool(_pluggable_allocator().allocator())
+    return torch.cuda.MemPool(_allocator())
 
 
 @contextlib.contextmanager
 def symmetric_pool():
     """Allocations inside the block come from the symmetric heap; yields the ``torch.cuda.MemPool``."""
-    pool = torch.cuda.MemPool(_pluggable_allocator().allocator())
+    pool = torch.cuda.MemPool(_allocator())
     with torch.cuda.use_mem_pool(pool):
         yield pool
 
@@ -65,7 +67,10 @@ def cuda_allocator_stats(device: int | None = None) -> dict:
     lib = ctypes.CDLL(LIB_PATH)
     out = (ctypes.c_uint64 * 5)()
     lib.mb_cuda_allocator_stats(ctypes.c_int(device), out)
-    return dict(zip(("live_bytes", "cached_bytes", "hits", "misses", "heap_mapped_bytes"), (int(v) for v in out)))
+    stats = dict(zip(("live_bytes", "cached_bytes", "hits", "misses", "heap_mapped_bytes"), (int(v) for v in out)))
+    lib.mb_cuda_allocator_cross_stream_frees.restype = ctypes.c_uint64
+    stats["cross_stream_frees"] = int(lib.mb_cuda_allocator_cross_stream_frees(ctypes.c_int(device)))
+    return stats
 
 
 def enable_cpu_allocator() -> None:

@@ -43,6 +43,7 @@ std::string status_text(uint32_t st) {
     case 0x202: what = "timed out waiting for a peer's data"; break;
     case 0x203: what = "timed out waiting for a peer's address announcement"; break;
     case 0x204: what = "timed out at exit waiting for a peer"; break;
+    case 0x205: what = "timed out waiting for the sender of a point-to-point CUDA tensor (Queue item or recv)"; break;
     case 0x101: what = "GEMM producer timed out"; break;
     case 0x102: what = "GEMM MMA issuer timed out"; break;
     case 0x103: what = "GEMM epilogue timed out"; break;

@@ -47,6 +47,7 @@ enum OpType : uint32_t {
   kOpHeartbeat = 99,    // the reference heartbeats with RDMA writes; over plain TCP it is a message
   kOpScatterCpu = 100,  // not in the reference (scatter throws there)
   kOpSendRecv = 101,    // point-to-point payloads (send/recv are unsupported in the reference)
+  kOpCudaItemDone = 103, // a receiver has copied a point-to-point CUDA tensor: the sender may release its buffer
   kOpErrorNotice = 102, // "this rank entered its error state because ...": the receivers enter theirs at once
                         // (the reference's ranks learn of a peer's error state only when that process exits)
 };

@@ -10,6 +10,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <cuda_runtime_api.h>
+#include <torch/csrc/cuda/CUDAPluggableAllocator.h>
 #include <torch/extension.h>
 
 #include <mutex>
@@ -19,8 +20,30 @@
 #include "core/cpu_allocator.h"
 #include "core/log.h"
 
+extern "C" {
+void* mb_cuda_alloc(ssize_t size, int device, cudaStream_t stream);
+void mb_cuda_free(void* ptr, ssize_t size, int device, cudaStream_t stream);
+void mb_cuda_record_stream(void* ptr, cudaStream_t stream);
+void* mb_cuda_base_allocation(void* ptr, size_t* size);
+}
+
 namespace moodist {
 namespace {
+
+// torch's pluggable CUDA allocator over the symmetric heap, with the hooks Python's CUDAPluggableAllocator
+// cannot set: record_stream (a block used on a side stream is not reused before that stream is done with it)
+// and the base-allocation query (reference: wrapper/allocator_wrapper.cc:92-100, getBaseAllocation).
+std::shared_ptr<c10::cuda::CUDACachingAllocator::CUDAAllocator> cuda_allocator() {
+  static std::shared_ptr<c10::cuda::CUDACachingAllocator::CUDAAllocator> alloc = [] {
+    auto a = std::make_shared<torch::cuda::CUDAPluggableAllocator::CUDAPluggableAllocator>(
+        [](size_t n, int dev, cudaStream_t s) { return mb_cuda_alloc((ssize_t)n, dev, s); },
+        [](void* p, size_t n, int dev, cudaStream_t s) { mb_cuda_free(p, (ssize_t)n, dev, s); });
+    a->set_record_stream_fn([](void* p, cudaStream_t s) { mb_cuda_record_stream(p, s); });
+    a->set_base_alloc_fn([](void* p, size_t* n) { return mb_cuda_base_allocation(p, n); });
+    return std::static_pointer_cast<c10::cuda::CUDACachingAllocator::CUDAAllocator>(a);
+  }();
+  return alloc;
+}
 
 void delete_cpu(void* p) { cpu_free(p); }
 
@@ -115,6 +138,13 @@ void bind_allocators(pybind11::module_& m, BackendClass& backend) {
     return self->hostGroup().last_trace_path();
   });
   m.def("set_prefer_kernel_less", [](bool v) { MoodistBackend::setDefaultPreferKernelLess(v); });
+  m.def("cuda_allocator", &cuda_allocator,
+        "the symmetric-heap CUDA allocator as a torch allocator object (for torch.cuda.MemPool or "
+        "torch.cuda.memory.change_current_allocator), with record_stream and base-allocation hooks");
+  m.def("enable_cuda_allocator", [] {
+    // also records the allocator as torch's "current custom allocator", which its deleters go through
+    torch::cuda::CUDAPluggableAllocator::changeCurrentAllocator(cuda_allocator());
+  });
 }
 
 }  // namespace moodist

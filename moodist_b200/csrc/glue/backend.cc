@@ -172,6 +172,12 @@ MoodistBackend::~MoodistBackend() {
     auto it = registry().find(name_);
     if (it != registry().end() && it->second == this) registry().erase(it);
   }
+  if (p2p_) {
+    // acknowledgements still queued as host callbacks on some stream refer to host_: let them run first
+    cudaSetDevice(cuda_->device());
+    cudaDeviceSynchronize();
+    p2p_.reset();
+  }
   try {
     if (host_) host_->shutdown();
   } catch (...) {
@@ -192,6 +198,18 @@ CudaGroup& MoodistBackend::cudaGroup(int device) {
   TORCH_CHECK(cuda_->device() == device, "moodist: this process group is bound to cuda:", cuda_->device(),
               " but got a tensor on cuda:", device);
   return *cuda_;
+}
+
+CudaP2P* MoodistBackend::cudaP2P(int device) {
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    if (p2p_) return p2p_.get();
+    if (!cuda_ || size_ < 2 || cuda_->device() != device) return nullptr;
+  }
+  HostGroup& h = hostGroup();
+  std::lock_guard<std::mutex> lk(mu_);
+  if (!p2p_) MOODIST_TRANSLATE(p2p_ = std::make_unique<CudaP2P>(*cuda_, h, device);)
+  return p2p_.get();
 }
 
 HostGroup& MoodistBackend::hostGroup() {
@@ -566,11 +584,25 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::barrier(const c10d::BarrierOption
   return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::BARRIER, std::vector<at::Tensor>{});
 }
 
+// CUDA descriptors and host payloads of one (source, tag) pair must never be mistaken for one another
+static constexpr uint32_t kCudaTagBit = 0x80000000u;
+
 c10::intrusive_ptr<c10d::Work> MoodistBackend::send(std::vector<at::Tensor>& tensors, int dstRank, int tag) {
   TORCH_CHECK(tensors.size() == 1, "moodist: send takes one tensor");
   TORCH_CHECK(dstRank >= 0 && dstRank < size_ && dstRank != rank_, "moodist: send: bad destination rank ", dstRank);
   at::Tensor t = tensors[0];
   check_contig(t, "send tensor");
+  if (t.is_cuda()) {
+    if (CudaP2P* p2p = cudaP2P(t.get_device())) {
+      // Nothing here waits for the GPU: the bytes become readable to the receiver in stream order, a flag kernel
+      // tells it when, and only the small descriptor travels through the host path.
+      c10::cuda::CUDAGuard guard(t.device());
+      auto stream = c10::cuda::getCurrentCUDAStream();
+      MOODIST_TRANSLATE(CudaItemDescriptor d = p2p->publish(t, 1, stream.stream());
+                        hostGroup().send(&d, sizeof(d), dstRank, (uint32_t)tag ^ kCudaTagBit);)
+      return c10::make_intrusive<CudaWork>(rank_, c10d::OpType::SEND, tensors, stream);
+    }
+  }
   at::Tensor host = t.is_cuda() ? t.cpu() : t;  // .cpu() synchronises with the producing stream
   MOODIST_TRANSLATE(hostGroup().send(host.data_ptr(), (size_t)host.nbytes(), dstRank, (uint32_t)tag);)
   return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::SEND, tensors);
@@ -581,6 +613,20 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::recv(std::vector<at::Tensor>& ten
   TORCH_CHECK(srcRank >= 0 && srcRank < size_ && srcRank != rank_, "moodist: recv: bad source rank ", srcRank);
   at::Tensor t = tensors[0];
   check_contig(t, "recv tensor");
+  if (t.is_cuda()) {
+    if (CudaP2P* p2p = cudaP2P(t.get_device())) {
+      // the host waits for the descriptor only (the sender posts it when it calls send, whatever its stream is
+      // still busy with); the data follows in stream order on this rank's current stream
+      c10::cuda::CUDAGuard guard(t.device());
+      auto stream = c10::cuda::getCurrentCUDAStream();
+      CudaItemDescriptor d;
+      MOODIST_TRANSLATE(hostGroup().recv(&d, sizeof(d), srcRank, (uint32_t)tag ^ kCudaTagBit);)
+      TORCH_CHECK(d.magic == kCudaItemMagic && d.bytes == (uint64_t)t.nbytes(), "moodist: recv: the sender's tensor has ",
+                  d.bytes, " bytes, this one ", t.nbytes());
+      MOODIST_TRANSLATE(p2p->fetch(d, t.data_ptr(), stream.stream());)
+      return c10::make_intrusive<CudaWork>(rank_, c10d::OpType::RECV, tensors, stream);
+    }
+  }
   at::Tensor host = t.is_cuda() ? at::empty(t.sizes(), t.options().device(at::kCPU).pinned_memory(true)) : t;
   MOODIST_TRANSLATE(hostGroup().recv(host.data_ptr(), (size_t)host.nbytes(), srcRank, (uint32_t)tag);)
   if (t.is_cuda()) t.copy_(host);  // blocking copy from pinned memory: `host` may be released afterwards

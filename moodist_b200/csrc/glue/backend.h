@@ -16,6 +16,7 @@
 #include "core/host_group.h"
 #include "core/kvstore.h"
 #include "core/queue.h"
+#include "cuda_p2p.h"
 
 namespace moodist {
 
@@ -79,8 +80,8 @@ class MoodistBackend final : public c10d::Backend {
   c10::intrusive_ptr<c10d::Work> alltoall(std::vector<at::Tensor>& outputs, std::vector<at::Tensor>& inputs,
                                           const c10d::AllToAllOptions& opts = c10d::AllToAllOptions()) override;
   c10::intrusive_ptr<c10d::Work> barrier(const c10d::BarrierOptions& opts = c10d::BarrierOptions()) override;
-  // point-to-point through the host engine (CUDA tensors are staged through host memory): enough for
-  // control traffic and pipeline hand-offs, not a bandwidth path
+  // point-to-point: CPU tensors through the host engine; CUDA tensors over NVLink without blocking the sender's
+  // host thread (cuda_p2p.h) once the group has run a CUDA collective, through host memory before that
   c10::intrusive_ptr<c10d::Work> send(std::vector<at::Tensor>& tensors, int dstRank, int tag) override;
   c10::intrusive_ptr<c10d::Work> recv(std::vector<at::Tensor>& tensors, int srcRank, int tag) override;
 
@@ -106,6 +107,10 @@ class MoodistBackend final : public c10d::Backend {
   void reduceScatterCast(at::Tensor& output, const at::Tensor& input, int op, double premul);
 
   CudaGroup& cudaGroup(int device);
+  // The NVLink hand-over path for single CUDA tensors (Queue items, send / recv), or null while the group has
+  // not run a CUDA collective yet: creating the CUDA group is itself a collective, which a put or a send
+  // between two ranks must not start. Until then such tensors are staged through host memory.
+  CudaP2P* cudaP2P(int device);
   HostGroup& hostGroup();
   QueueManager& queues();
   KVStore& kv() { return *kv_; }
@@ -123,6 +128,7 @@ class MoodistBackend final : public c10d::Backend {
   std::unique_ptr<CudaGroup> cuda_;
   std::unique_ptr<HostGroup> host_;
   std::unique_ptr<QueueManager> queues_;  // declared after host_: destroyed first
+  std::unique_ptr<CudaP2P> p2p_;          // uses cuda_ and host_: destroyed before both
 };
 
 }  // namespace moodist

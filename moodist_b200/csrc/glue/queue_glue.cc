@@ -1,4 +1,6 @@
 // moodist.Queue bindings: tensors in, tensors out (reference: wrapper/queue_wrapper.cc, wrapper/module.cc:921-1320).
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
 
 #include "bindings.h"
@@ -33,13 +35,49 @@ struct PyQueueWork {
   }
 };
 
+// dtype code of a queue item that is the descriptor of a CUDA tensor: this offset plus the tensor's own dtype
+constexpr int32_t kCudaItemDtypeBase = 1000;
+
 struct PyQueue {
   std::shared_ptr<Queue> q;
   c10::intrusive_ptr<MoodistBackend> owner;  // the group must outlive its queues
+  int readers = 1;                           // locations of the queue: each of them fetches a CUDA item once
+  std::mutex tx_mu;
+  std::map<uint32_t, std::vector<CudaItemDescriptor>> tx_items;  // CUDA items of open transactions
 
   std::shared_ptr<PyQueueWork> put(const at::Tensor& tensor, uint32_t transaction, bool wait_on_destroy) {
-    // CUDA tensors are staged to host memory here (synchronises with the producing stream); the receiving
-    // side always gets a CPU tensor.
+    if (tensor.is_cuda()) {
+      if (CudaP2P* p2p = owner->cudaP2P(tensor.get_device())) {
+        // Stream-ordered: nothing waits for the GPU here. The item that travels is a descriptor; whoever gets it
+        // copies the bytes over NVLink on its own stream and receives a CUDA tensor.
+        at::Tensor t = tensor.contiguous();
+        c10::cuda::CUDAGuard guard(t.device());
+        auto stream = c10::cuda::getCurrentCUDAStream();
+        auto desc = std::make_shared<CudaItemDescriptor>();
+        try {
+          *desc = p2p->publish(t, readers, stream.stream());
+        } catch (const Error& e) {
+          throw std::runtime_error(e.what());
+        }
+        if (transaction) {
+          std::lock_guard<std::mutex> lk(tx_mu);
+          tx_items[transaction].push_back(*desc);
+        }
+        std::vector<int64_t> shape(t.sizes().begin(), t.sizes().end());
+        auto w = std::make_shared<PyQueueWork>();
+        w->wait_on_destroy = wait_on_destroy;
+        py::gil_scoped_release nogil;
+        try {
+          w->work = q->put(desc.get(), sizeof(CudaItemDescriptor), kCudaItemDtypeBase + (int32_t)t.scalar_type(), shape,
+                           transaction, desc);
+        } catch (const Error& e) {
+          throw std::runtime_error(e.what());
+        }
+        return w;
+      }
+    }
+    // Before the group has mapped its peers' memory (its first CUDA collective does that), CUDA tensors are
+    // staged to host memory here, which waits for the producing stream; the receiver then gets a CPU tensor.
     at::Tensor t = tensor.is_cuda() ? tensor.cpu() : tensor;
     t = t.contiguous();
     auto keep = std::make_shared<at::Tensor>(t);
@@ -81,6 +119,26 @@ struct PyQueue {
       }
     }
     if (!item) return py::make_tuple(py::none(), size);
+    if (item->dtype >= kCudaItemDtypeBase) {
+      // the descriptor of a CUDA tensor: fetch the bytes on this rank's current stream
+      TORCH_CHECK(item->data.size() == sizeof(CudaItemDescriptor), "moodist queue: malformed CUDA item");
+      CudaItemDescriptor d;
+      memcpy(&d, item->data.data(), sizeof(d));
+      int device = (int)c10::cuda::current_device();
+      CudaP2P* p2p = owner->cudaP2P(device);
+      TORCH_CHECK(p2p != nullptr, "moodist queue: received a CUDA tensor but this rank's group has no CUDA side yet "
+                                  "(run a CUDA collective on the group first)");
+      auto options = at::TensorOptions().dtype((at::ScalarType)(item->dtype - kCudaItemDtypeBase)).device(at::kCUDA, device);
+      at::Tensor out = at::empty(item->shape, options);
+      TORCH_CHECK((uint64_t)out.nbytes() == d.bytes, "moodist queue: CUDA item size mismatch");
+      auto stream = c10::cuda::getCurrentCUDAStream();
+      try {
+        p2p->fetch(d, out.data_ptr(), stream.stream());
+      } catch (const Error& e) {
+        throw std::runtime_error(e.what());
+      }
+      return py::make_tuple(out, size);
+    }
     auto* holder = new Bytes(std::move(item->data));
     auto options = at::TensorOptions().dtype((at::ScalarType)item->dtype).device(at::kCPU);
     at::Tensor out = at::from_blob(holder->data(), item->shape, [holder](void*) { delete holder; }, options);
@@ -108,8 +166,29 @@ void bind_queue(pybind11::module_& m, BackendClass& backend) {
       .def("qsize", &PyQueue::qsize)
       .def("wait", &PyQueue::wait, py::arg("timeout") = py::none())
       .def("transaction_begin", [](PyQueue& s) { return s.q->transaction_begin(); })
-      .def("transaction_commit", [](PyQueue& s, uint32_t id) { s.q->transaction_commit(id); })
-      .def("transaction_cancel", [](PyQueue& s, uint32_t id) { s.q->transaction_cancel(id); })
+      .def("transaction_commit",
+           [](PyQueue& s, uint32_t id) {
+             s.q->transaction_commit(id);
+             std::lock_guard<std::mutex> lk(s.tx_mu);
+             s.tx_items.erase(id);
+           })
+      .def("transaction_cancel",
+           [](PyQueue& s, uint32_t id) {
+             s.q->transaction_cancel(id);
+             // nobody will ever fetch the CUDA items of a cancelled transaction: release their buffers
+             std::vector<CudaItemDescriptor> items;
+             {
+               std::lock_guard<std::mutex> lk(s.tx_mu);
+               auto it = s.tx_items.find(id);
+               if (it != s.tx_items.end()) {
+                 items = std::move(it->second);
+                 s.tx_items.erase(it);
+               }
+             }
+             if (!items.empty())
+               if (CudaP2P* p2p = s.owner->cudaP2P((int)c10::cuda::current_device()))
+                 for (auto& d : items) p2p->drop(d);
+           })
       .def("name", [](PyQueue& s) { return s.q->name(); });
 
   backend.def(
@@ -125,6 +204,7 @@ void bind_queue(pybind11::module_& m, BackendClass& backend) {
         if (!name.is_none()) nm = name.cast<std::string>();
         auto out = std::make_shared<PyQueue>();
         out->owner = self;
+        out->readers = (int)std::max<size_t>(1, locations.size());
         {
           py::gil_scoped_release nogil;
           try {

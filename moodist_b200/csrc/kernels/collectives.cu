@@ -717,6 +717,43 @@ int launch_reduce_local(const void* s0, const void* staged, size_t slot_stride, 
 }
 }  // namespace
 
+// ---------------------------------------------------------------------------------------------
+// point-to-point flags: a producer's stream raises a word once its data is in place, a consumer's stream
+// (on another GPU, through its mapping of the producer's memory) waits for it before it copies
+// ---------------------------------------------------------------------------------------------
+namespace mb {
+namespace coll {
+__global__ void __launch_bounds__(32, 1) flag_set_kernel(uint32_t* flag, uint32_t value) {
+  if (threadIdx.x == 0) {
+    __threadfence_system();  // everything this stream wrote before is visible to whoever sees the flag
+    st_release_sys(flag, value);
+  }
+}
+__global__ void __launch_bounds__(32, 1)
+    flag_wait_kernel(const uint32_t* flag, uint32_t value, uint32_t* status, uint64_t wait_ns, uint32_t code) {
+  if (threadIdx.x == 0) {
+    if (!wait_geq_sys(flag, value, wait_ns)) {
+      volatile uint32_t* s = status;
+      if (*s == 0) *s = code;
+    }
+  }
+}
+}  // namespace coll
+}  // namespace mb
+
+extern "C" int mb_flag_set(uint32_t* flag, uint32_t value, void* stream) {
+  flag_set_kernel<<<1, 32, 0, MB_STREAM(stream)>>>(flag, value);
+  return check_launch();
+}
+
+// Bounded: when `flag` has not reached `value` after wait_ns the kernel records `code` in *status (if it is
+// still 0) and ends; what follows on the stream runs all the same, so the host must check the status word.
+extern "C" int mb_flag_wait(const uint32_t* flag, uint32_t value, uint32_t* status, uint64_t wait_ns, uint32_t code,
+                            void* stream) {
+  flag_wait_kernel<<<1, 32, 0, MB_STREAM(stream)>>>(flag, value, status, wait_ns, code);
+  return check_launch();
+}
+
 extern "C" int mb_ce_phase(const mb_comm_t* c, uint32_t seq, int phase, void* stream) {
   cudaStream_t s = MB_STREAM(stream);
   switch (phase) {

@@ -141,6 +141,13 @@ int mb_ce_phase(const mb_comm_t* c, uint32_t seq, int phase, void* stream);
 int mb_reduce_local(const mb_comm_t* c, uint32_t seq, const void* own, void* out, size_t count, int in_dtype,
                     int out_dtype, int op, float premul, void* stream);
 
+// --- point-to-point hand-over between two GPUs (Queue items, send / recv) -------------------------------
+// mb_flag_set: once everything queued on `stream` so far is done, *flag = value (release, system scope).
+// mb_flag_wait: hold `stream` until *flag >= value (the flag may be a peer's memory); gives up after wait_ns and
+// then records `code` in *status instead of hanging.
+int mb_flag_set(uint32_t* flag, uint32_t value, void* stream);
+int mb_flag_wait(const uint32_t* flag, uint32_t value, uint32_t* status, uint64_t wait_ns, uint32_t code, void* stream);
+
 // --- NVLS variants (collectives_nvls.cu); need the multicast alias (mb_nvls_available) ------------------
 int mb_nvls_available(const mb_comm_t* c);
 int mb_all_reduce_nvls(const mb_comm_t* c, uint32_t seq, const void* in, void* out, size_t count, int dtype, int op,

@@ -66,6 +66,36 @@ def _cuda_allocator(rank, world, port):
     assert len(ptrs) <= 2  # same-stream reuse
     st = moodist.cuda_allocator_stats(rank)
     assert st["heap_mapped_bytes"] > 0 and st["hits"] > 0
+    # a block that a side stream still uses is not handed out again: free it while a long kernel of the side
+    # stream reads it (record_stream told the allocator), allocate the same size on the main stream at once
+    side = torch.cuda.Stream(dev)
+    x = torch.full((1 << 22,), 7.0, device=dev)
+    x_ptr = x.data_ptr()
+    torch.cuda.synchronize()
+    big = torch.randn(16384, 16384, device=dev, dtype=torch.bfloat16)
+    out = torch.empty_like(big)
+    torch.matmul(big, big, out=out)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        for _ in range(40):  # some tenths of a second of work on the side stream, few launches
+            torch.matmul(big, big, out=out)
+        y = x * 2
+    x.record_stream(side)
+    del x
+    z = torch.zeros(1 << 22, device=dev)  # same size, main stream, while the side stream still waits
+    still_busy = not side.query()
+    # (growing the heap for `y` may have synchronised the device; the claim only holds while the side stream runs)
+    assert z.data_ptr() != x_ptr or not still_busy
+    z.fill_(-1.0)
+    torch.cuda.synchronize()
+    assert bool((y == 14.0).all())
+    assert moodist.cuda_allocator_stats(rank)["cross_stream_frees"] >= 1
+    del y, z
+    # without record_stream the same sequence reuses the block in stream order (what the cache is for)
+    w = torch.empty(1 << 22, device=dev)
+    w_ptr = w.data_ptr()
+    del w
+    assert torch.empty(1 << 22, device=dev).data_ptr() == w_ptr
     # collectives on heap tensors: peers read them in place
     dist = init_moodist(rank, world, port, device="cuda")
     for n in (1000, (1 << 20) + 3):

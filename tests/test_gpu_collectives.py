@@ -16,6 +16,25 @@ def _need(world):
         pytest.skip(f"needs {world} GPUs")
 
 
+class _Guarded:
+    """An output buffer between two guard bands: the output itself is poison-filled before the collective (a
+    kernel that skips part of it leaves poison behind), and the bands must be untouched afterwards (a kernel
+    that writes outside its output does not get away with it)."""
+
+    GUARD = 256  # elements on each side
+
+    def __init__(self, n, dtype, dev):
+        self.poison = 77 if not dtype.is_floating_point else -12345.0
+        self.buf = torch.full((n + 2 * self.GUARD,), self.poison, dtype=dtype, device=dev)
+        self.out = self.buf[self.GUARD : self.GUARD + n]
+        self.n = n
+
+    def check(self, what):
+        torch.cuda.synchronize()
+        lo, hi = self.buf[: self.GUARD], self.buf[self.GUARD + self.n :]
+        assert bool((lo == self.poison).all()) and bool((hi == self.poison).all()), ("guard band overwritten", what)
+
+
 def _cuda_collectives(rank, world, port):
     dist = init_moodist(rank, world, port, device="cuda")
     dev = torch.device("cuda", rank)
@@ -23,9 +42,11 @@ def _cuda_collectives(rank, world, port):
         for n in (1, 7, 1000, 65536, (1 << 20) + 3):
             g = torch.Generator().manual_seed(n)
             full = (torch.randn(world, n, generator=g) * 10).to(dtype)
-            out = torch.empty(world * n, device=dev, dtype=dtype)
+            gd = _Guarded(world * n, dtype, dev)
+            out = gd.out
             dist.all_gather_into_tensor(out, full[rank].to(dev).contiguous())
             assert torch.equal(out.cpu().view(world, n), full), ("all_gather", dtype, n)
+            gd.check(("all_gather", dtype, n))
     for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2), (torch.int32, 0)):
         for op in (dist.ReduceOp.SUM, dist.ReduceOp.AVG, dist.ReduceOp.MAX, dist.ReduceOp.MIN):
             if dtype == torch.int32 and op == dist.ReduceOp.AVG:
@@ -33,8 +54,10 @@ def _cuda_collectives(rank, world, port):
             for n in (1, 9, 4096, (1 << 18) + 5):
                 g = torch.Generator().manual_seed(n)
                 allin = (torch.randn(world, world, n, generator=g) * 4).to(dtype)
-                out = torch.empty(n, device=dev, dtype=dtype)
+                gd = _Guarded(n, dtype, dev)
+                out = gd.out
                 dist.reduce_scatter_tensor(out, allin[rank].reshape(-1).to(dev).contiguous(), op=op)
+                gd.check(("reduce_scatter", dtype, op, n))
                 col = allin[:, rank].double()
                 ref = {dist.ReduceOp.SUM: col.sum(0), dist.ReduceOp.AVG: col.mean(0), dist.ReduceOp.MAX: col.max(0).values,
                        dist.ReduceOp.MIN: col.min(0).values}[op]
@@ -44,11 +67,14 @@ def _cuda_collectives(rank, world, port):
         for n in (1, 5, 1000, 70000, (1 << 20) + 11):  # one-shot and two-shot paths
             g = torch.Generator().manual_seed(n)
             allin = torch.randn(world, n, generator=g).to(dtype)
-            t = allin[rank].to(dev).contiguous()
+            gd = _Guarded(n, dtype, dev)
+            t = gd.out
+            t.copy_(allin[rank])
             dist.all_reduce(t)
             ref = allin.double().sum(0)
             err = (t.double().cpu() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
             assert err <= tol, ("all_reduce", dtype, n, err)
+            gd.check(("all_reduce", dtype, n))
     for root in (0, world - 1):
         t = torch.full((100001,), float(rank + 1), device=dev)
         dist.broadcast(t, src=root)
