@@ -44,7 +44,10 @@ def parse_args():
     ap.add_argument("--engine", default="native", choices=["native", "fsdp2"],
                     help="native: the resident-parameter sharded engine; fsdp2: torch fully_shard per block")
     ap.add_argument("--kernel-less", action="store_true",
-                    help="collectives move their bytes with DMA copies between flag kernels (no SMs taken from the GEMMs)")
+                    help="collectives move their bytes with DMA copies between flag kernels (no SMs taken from the GEMMs); "
+                         "the re-gather schedule does that by default from 1 MiB per rank up")
+    ap.add_argument("--sm-collectives", action="store_true",
+                    help="re-gather schedule with its plain gathers and reduce-scatters on SM copy kernels")
     ap.add_argument("--no-symmetric", action="store_true", help="keep gathered parameters out of the symmetric heap")
     ap.add_argument("--schedule", default="regather", choices=["regather", "resident"],
                     help="regather: sharded at rest, per-block gathers (FSDP2); resident: gathered parameters stay")
@@ -116,7 +119,8 @@ def main():
             raise SystemExit(3)
 
     trainer = ShardedTrainer(cfg, seed=0, engine=args.engine, symmetric_memory=not args.no_symmetric,
-                             schedule=args.schedule, fused=not args.no_fused)
+                             schedule=args.schedule, fused=not args.no_fused,
+                             copy_engine=False if args.sm_collectives else (True if args.kernel_less else None))
 
     def host_batch(i):
         g = torch.Generator().manual_seed(1000 * rank + i)
@@ -171,6 +175,7 @@ def main():
     value = tokens_per_step / (ms_per_step / 1e3)
 
     fused_calls = getattr(trainer.engine, "fused_calls", 0) if trainer.engine is not None else 0
+    copy_engine_used = bool(getattr(trainer, "copy_engine", False))
     exposed = None
     if args.exposed and trainer.engine is not None and hasattr(trainer.engine, "exposed_events"):
         trainer.engine.exposed_events = []
@@ -272,7 +277,7 @@ def main():
                 "schedule": ("torch fully_shard" if args.engine == "fsdp2" else args.schedule),
                 "fused_all_gather_gemm": bool(fused_calls > 0),
                 "fused_all_gather_gemm_calls": int(fused_calls),
-                "kernel_less": bool(args.kernel_less),
+                "kernel_less": bool(args.kernel_less or copy_engine_used),
                 "reduce_dtype": "fp32",
                 "optimizer": "AdamW, bf16 moments" + (" (flat-shard kernel)" if args.engine == "native" else " (torch fused)"),
                 "l2": "inputs larger than L2: each step streams the 16 GB of bf16 weights plus activations",

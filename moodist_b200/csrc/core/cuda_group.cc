@@ -1,6 +1,7 @@
 #include "cuda_group.h"
 
 #include <cuda_runtime_api.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <algorithm>
 #include <atomic>
@@ -137,6 +138,7 @@ class CudaGroupImpl final : public CudaGroup {
     comm_.tuning = env_long("MOODIST_AG_STAGGER", 1) ? MB_TUNE_STAGGER : 0;
     if (const char* tp = getenv("MOODIST_VARIANT_TABLE"); tp && *tp) table_ = load_variant_table(tp, world);
     stats_every_ = (int)env_long("MOODIST_STATS_SAMPLE", 64);
+    nvtx_ = env_flag("MOODIST_NVTX");
     push_bytes_ = (size_t)threshold("MOODIST_AG_PUSH_BYTES", 1 << 20);
     // Pushing large shards (two pipelined halves per CTA) beat the pull on 2 GPUs from 32 MiB up (447 vs 421 GB/s)
     // but lost on 8 (456-499 vs 557-597 GB/s: seven incoming write streams per GPU plus the copy out of
@@ -307,6 +309,11 @@ class CudaGroupImpl final : public CudaGroup {
   class OpScope {
    public:
     OpScope(CudaGroupImpl* g, const char* op, const char* variant, size_t bytes, CUstream_st* s) : g_(g), s_(s) {
+      if (g->nvtx_) {
+        // a range per collective on the host timeline of profilers that follow NVTX (MOODIST_NVTX=1)
+        nvtxRangePushA((std::string("moodist ") + op + "/" + variant).c_str());
+        ranged_ = true;
+      }
       st_ = &g->stats_[std::string(op) + "/" + variant];
       st_->calls++;
       st_->bytes += bytes;
@@ -319,6 +326,7 @@ class CudaGroupImpl final : public CudaGroup {
       }
     }
     ~OpScope() {
+      if (ranged_) nvtxRangePop();
       if (timed_) {
         cudaEventRecord(b_, (cudaStream_t)s_);
         st_->pending.emplace_back(a_, b_);
@@ -330,7 +338,7 @@ class CudaGroupImpl final : public CudaGroup {
     Stat* st_;
     CUstream_st* s_;
     cudaEvent_t a_ = nullptr, b_ = nullptr;
-    bool timed_ = false;
+    bool timed_ = false, ranged_ = false;
   };
   void drain(Stat& st, bool wait) {
     auto it = st.pending.begin();
@@ -653,6 +661,7 @@ class CudaGroupImpl final : public CudaGroup {
   long nvls_ar_min_ = -1, nvls_rs_min_ = -1, nvls_ag_min_ = -1, nvls_ag_max_ = -1;
   long ar_oneshot_ = 2 << 20;
   int stats_every_ = 64;
+  bool nvtx_ = false;
   std::map<std::string, long> table_;
   std::map<std::string, Stat> stats_;
   uint64_t launches_ = 0;

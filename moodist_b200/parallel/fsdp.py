@@ -46,6 +46,7 @@ class ShardedTrainer:
         symmetric_memory: bool = True,
         schedule: str = "regather",
         fused: bool = True,
+        copy_engine: bool | None = None,
     ):
         if not torch.cuda.is_available():
             raise RuntimeError("ShardedTrainer needs a CUDA device")
@@ -60,6 +61,18 @@ class ShardedTrainer:
         self.engine = None
         self.opt = None
         self.schedule = schedule if engine == "native" else "fsdp2"
+        # The re-gather schedule keeps the side stream busy through forward and backward. Measured on 8 GPUs, its
+        # plain gathers and reduce-scatters cost the concurrent GEMMs less when the bytes move with DMA copies
+        # between one-warp flag kernels (448.5 ms per step) than with SM copy kernels (457.1 ms), so that is the
+        # default for it; `copy_engine=False` keeps the SM kernels, `True` forces DMA for any schedule.
+        if copy_engine is None:
+            copy_engine = engine == "native" and schedule == "regather"
+        self.copy_engine = False
+        if copy_engine and self.world > 1 and dist.get_backend(self.group) == "moodist":
+            from ..backend import get_backend
+
+            get_backend(self.group).set_prefer_kernel_less(True)
+            self.copy_engine = True
         if engine == "native":
             m = self.model
             units = [("embed", [m.embed])]
