@@ -214,25 +214,6 @@ def main():
         torch.cuda.empty_cache()
         return tokens_per_step / (m.item() / args.steps / 1e3)
 
-    vs_nccl = None
-    if world > 1 and args.backend == "moodist" and not args.no_nccl_arms:
-        vs_nccl = {}
-        del trainer
-        import gc
-
-        gc.collect()
-        torch.cuda.empty_cache()
-        for key, (eng, sched) in {"same_engine_nccl": ("native", args.schedule), "torch_fsdp2_nccl": ("fsdp2", "regather")}.items():
-            try:
-                tps = nccl_arm(eng, sched)
-                vs_nccl[key + "_tokens_per_s"] = tps
-                vs_nccl["ratio_vs_" + key] = value / tps
-            except Exception as e:  # the headline stands without the comparison
-                vs_nccl[key + "_error"] = f"{type(e).__name__}: {e}"[:300]
-        vs_nccl["note"] = ("same steps / warm-up / timing; same_engine = this repository's model and sharding engine "
-                           "with nccl collectives (nothing fused); torch_fsdp2 = torch fully_shard per block, bf16 "
-                           "parameters and fp32 reduce, torch fused AdamW with the moments in bf16 like the engine's")
-
     def roofline():
         """Model FLOPs per GPU and step against the measured cuBLAS rate of this pool (extra information only)."""
         try:
@@ -250,6 +231,7 @@ def main():
         except Exception as e:  # never let the extra block break the result line
             return {"error": str(e)}
 
+    out = None
     if rank == 0:
         out = {
             "metric": ("FSDP2 Llama-3-8B training throughput" if args.engine == "fsdp2" or args.schedule == "regather"
@@ -297,13 +279,54 @@ def main():
         }
         if selfcheck is not None:
             out["selfcheck"] = selfcheck
-        if vs_nccl is not None:
-            out["vs_nccl"] = vs_nccl
         if exposed is not None:
             out["exposed_wait"] = exposed
         if op_stats:
             out["collective_stats"] = op_stats
-        print(json.dumps(out))
+
+    # The comparison runs come after the headline is complete and must never cost it: if they have not finished
+    # within their limit, rank 0 prints the line without them and every rank leaves.
+    import threading
+
+    printed = threading.Lock()
+
+    def emit(vs):
+        if not printed.acquire(blocking=False):
+            return
+        if rank == 0:
+            if vs is not None:
+                out["vs_nccl"] = vs
+            print(json.dumps(out), flush=True)
+
+    def abandon():
+        emit({"error": f"the NCCL comparison runs did not finish within {arm_limit} s and were abandoned"})
+        os._exit(0)
+
+    arm_limit = int(os.environ.get("MOODIST_BENCH_ARM_LIMIT_S", "420"))
+    vs_nccl = None
+    if world > 1 and args.backend == "moodist" and not args.no_nccl_arms:
+        vs_nccl = {}
+        watchdog = threading.Timer(arm_limit, abandon)
+        watchdog.daemon = True
+        watchdog.start()
+        del trainer
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        for key, (eng, sched) in {"same_engine_nccl": ("native", args.schedule), "torch_fsdp2_nccl": ("fsdp2", "regather")}.items():
+            try:
+                tps = nccl_arm(eng, sched)
+                vs_nccl[key + "_tokens_per_s"] = tps
+                vs_nccl["ratio_vs_" + key] = value / tps
+            except Exception as e:  # the headline stands without the comparison
+                vs_nccl[key + "_error"] = f"{type(e).__name__}: {e}"[:300]
+        watchdog.cancel()
+        vs_nccl["note"] = ("same steps / warm-up / timing; same_engine = this repository's model and sharding engine "
+                           "with nccl collectives (nothing fused); torch_fsdp2 = torch fully_shard per block, bf16 "
+                           "parameters and fp32 reduce, torch fused AdamW with the moments in bf16 like the engine's")
+
+    emit(vs_nccl)
     dist.barrier()
     dist.destroy_process_group()
     return 0
