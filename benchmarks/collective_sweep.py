@@ -54,6 +54,7 @@ def main():
     ap.add_argument("--ops", default="ag,rs_sum,rs_avg,ar")
     ap.add_argument("--impls", default="moodist,nccl")
     ap.add_argument("--out", default="")
+    ap.add_argument("--quick", action="store_true", help="fewer iterations above 64 MiB per rank")
     args = ap.parse_args()
 
     rank, world, lr = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
@@ -83,8 +84,10 @@ def main():
         es = torch.empty(0, dtype=dt).element_size()
         for nbytes in sizes:
             n = nbytes // es
-            iters = args.iters if nbytes <= (64 << 20) else max(10, args.iters // 5)
-            warm = args.warmup if nbytes <= (64 << 20) else 5
+            # --quick cuts the iteration count above 64 MiB per rank (a full-length 1 GiB point takes seconds per
+            # implementation); without it every size gets the stated warm-up and timed iterations
+            iters = args.iters if (not args.quick or nbytes <= (64 << 20)) else max(10, args.iters // 5)
+            warm = args.warmup if (not args.quick or nbytes <= (64 << 20)) else 5
             for impl in args.impls.split(","):
                 g = groups[impl]
                 if impl.startswith("moodist"):

@@ -1,4 +1,4 @@
-"""Quick correctness check of a CUDA process group against a CPU oracle.
+"""Quick correctness check of a process group (CUDA, or CPU ranks on the host path) against a CPU oracle.
 
 ``run_selfcheck(group)`` runs every collective the backend serves — all-gather, reduce-scatter (sum and
 average), all-reduce, broadcast, uneven all-to-all — at one size per kernel family (small pushes, NVLS
@@ -48,15 +48,16 @@ class _Checker:
 def run_selfcheck(group=None, device=None, fused: bool = True) -> dict:
     """Returns ``{"ok", "max_rel_err", "cases", "failed", "variants"}``; a collective, call on every rank."""
     group = group if group is not None else dist.group.WORLD
-    device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    on_gpu = device.type == "cuda"
     ck = _Checker(group, device)
     w, r = ck.world, ck.rank
     backend = None
     if dist.get_backend(group) == "moodist":
         from ..backend import get_backend
 
-        backend = get_backend(group)
-    before = backend.stats(False) if backend is not None else {}
+        backend = get_backend(group, device=device.type)
+    before = backend.stats(False) if backend is not None and on_gpu else {}
     case = 0
 
     # ---- all-gather: 4 KiB (push), 256 KiB (NVLS where available), 8 MiB (pull) per rank, bf16 ----
@@ -120,7 +121,7 @@ def run_selfcheck(group=None, device=None, fused: bool = True) -> dict:
     ck.compare("all_to_all uneven", out, torch.cat(parts), 0.0)
 
     # ---- fused collective GEMMs (this library's groups only) ----
-    if fused and backend is not None and w > 1:
+    if fused and on_gpu and backend is not None and w > 1:
         from ..ops.fused import ag_gemm, gemm_rs
 
         case += 1
@@ -145,9 +146,10 @@ def run_selfcheck(group=None, device=None, fused: bool = True) -> dict:
             want += (ap @ bp.t()).to(torch.bfloat16).double()
         ck.compare("gemm_rs", out, want.float(), 2e-2)
 
-    torch.cuda.synchronize(device)
+    if on_gpu:
+        torch.cuda.synchronize(device)
     variants = []
-    if backend is not None:
+    if backend is not None and on_gpu:
         after = backend.stats(False)
         for name, row in after.items():
             if row["calls"] > before.get(name, {}).get("calls", 0):
