@@ -408,6 +408,12 @@ class RegatherEngine:
     # ---- backward ---------------------------------------------------------------------------------
     def _begin_backward(self, u: _Unit) -> None:
         if u.bwd_begun:
+            if u.pending == 0:
+                # every gradient of the unit has been reduced and applied already: this is a second backward
+                # pass (or a weight used twice) within one optimizer step, which this schedule cannot serve
+                raise RuntimeError(f"unit {u.name}: a second backward pass before finish_step(); the re-gather engine "
+                                   "applies each weight's gradient as soon as it is produced (one backward per step, "
+                                   "every weight used once)")
             return
         u.bwd_begun = True
         self._fwd_cursor = -1

@@ -83,6 +83,14 @@ def _engine_run(rank, world, port, steps, resume_at):
         b = model(tok[:, :-1])
         torch.testing.assert_close(a, b)
         torch.testing.assert_close(a, ref(tok[:, :-1]), rtol=1e-3, atol=1e-4)
+    # a second backward pass within one step is refused (gradients are applied as they are produced)
+    tok = _batch(rank, 98, cfg)
+    loss_fn(model(tok[:, :-1]), tok[:, 1:]).backward()
+    try:
+        loss_fn(model(tok[:, :-1]), tok[:, 1:]).backward()
+        raise AssertionError("second backward was accepted")
+    except RuntimeError as e:
+        assert "second backward" in str(e)
     # resume from the checkpoint with a fresh engine and replay the remaining steps
     cfg2, model2 = _tiny_model()
     eng2 = _engine(model2, hp)
