@@ -3,8 +3,10 @@
     python examples/train_llama_sharded.py --model tiny --steps 20                       # one GPU
     torchrun --nproc-per-node 8 examples/train_llama_sharded.py --model llama3-8b --steps 10
 
-Every rank trains on its own random token batches (synthetic data); the parameters, gradients reduction and
-optimizer state are sharded by ``moodist_b200.parallel.sharded.ShardedEngine`` over the "moodist" backend.
+Every rank trains on its own random token batches (synthetic data).  By default the FSDP2 schedule runs
+(``moodist_b200.parallel.regather.RegatherEngine``: weights sharded by rows at rest, gathered per block, the QKV
+and gate/up gathers fused into their GEMMs); ``--schedule resident`` keeps gathered parameters on every GPU
+(``moodist_b200.parallel.sharded.ShardedEngine``).  Both run over the "moodist" backend.
 """
 
 import argparse
@@ -28,6 +30,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--seq-len", type=int, default=0, help="0: the model's maximum")
     ap.add_argument("--lr", type=float, default=3e-4)
+    ap.add_argument("--schedule", default="regather", choices=["regather", "resident"])
     ap.add_argument("--checkpoint", default="", help="directory for one shard file per rank at the end")
     args = ap.parse_args()
 
@@ -41,7 +44,7 @@ def main():
 
     cfg = LlamaConfig.llama3_8b() if args.model == "llama3-8b" else LlamaConfig.tiny()
     seq = args.seq_len or cfg.max_seq_len
-    trainer = ShardedTrainer(cfg, lr=args.lr)
+    trainer = ShardedTrainer(cfg, lr=args.lr, schedule=args.schedule)
     gen = torch.Generator().manual_seed(rank)
     t0 = time.time()
     for step in range(args.steps):
