@@ -1,8 +1,9 @@
 // enable_cpu_allocator / cpu_allocator_debug / cuda_copy / enable_profiling / set_prefer_kernel_less.
-// The CUDA allocator is installed from Python through torch's pluggable-allocator API with the
-// mb_cuda_alloc / mb_cuda_free hooks of the core library (moodist_b200/allocator.py); the reference
-// subclasses CUDACachingAllocator::CUDAAllocator instead (wrapper/allocator_wrapper.cc:14-199), an interface
-// that changes between torch releases.
+// The CUDA allocator is torch's CUDAPluggableAllocator built here over the mb_cuda_* hooks of the core library
+// (alloc, free, record_stream, base allocation) and handed to Python as an allocator object
+// (moodist_b200/allocator.py installs it or wraps it in a MemPool); the reference subclasses
+// CUDACachingAllocator::CUDAAllocator itself (wrapper/allocator_wrapper.cc:14-199), an interface that changes
+// between torch releases.
 #include "core/numa.h"
 #include "core/topology.h"
 #include <c10/core/Allocator.h>

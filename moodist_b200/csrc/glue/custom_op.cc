@@ -135,9 +135,7 @@ struct PyCustomOp {
     size_t poff = (sbytes + 15) & ~(size_t)15;
     if (sbytes) TORCH_CHECK(cudaMemcpyAsync(scratch, stage.data(), sbytes, cudaMemcpyHostToDevice, stream.stream()) == cudaSuccess);
     if (pbytes) TORCH_CHECK(cudaMemcpyAsync(scratch + poff, pieces.data(), pbytes, cudaMemcpyHostToDevice, stream.stream()) == cudaSuccess);
-    if (p.world == 1) {
-      // single rank: pieces are all local; run them through the same kernel with no peers
-    }
+    // (a one-rank group runs the same kernel: all its pieces are local, no peer is waited for)
     int rc = mb_gather_scatter(comm, seq, reinterpret_cast<mb_stage_copy_t*>(scratch), (int)stage.size(),
                                reinterpret_cast<mb_piece_t*>(scratch + poff), (int)pieces.size(), biggest, stream.stream());
     g.finish_op(raw);
