@@ -1,0 +1,73 @@
+"""Static checks of the Python files that only run on GPU boxes (bench.py, benchmarks/, the GPU paths of the
+package): every file compiles, and no name is read that the file never binds (a typo there would otherwise
+show only on a GPU).  Plus the reference arm of the benchmark, which must answer without a GPU."""
+
+import ast
+import builtins
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _python_files():
+    for top in ("bench.py", "__graft_entry__.py", "benchmarks", "examples", "moodist_b200", "tests"):
+        path = os.path.join(ROOT, top)
+        if os.path.isfile(path):
+            yield path
+        for d, _, files in os.walk(path):
+            for f in files:
+                if f.endswith(".py"):
+                    yield os.path.join(d, f)
+
+
+def _bound_names(tree):
+    bound = set(dir(builtins)) | {"__file__", "__name__", "__doc__", "__class__"}
+    for node in ast.walk(tree):
+        if isinstance(node, (ast.FunctionDef, ast.AsyncFunctionDef, ast.ClassDef)):
+            bound.add(node.name)
+        if isinstance(node, (ast.FunctionDef, ast.AsyncFunctionDef, ast.Lambda)):
+            a = node.args
+            for arg in a.posonlyargs + a.args + a.kwonlyargs + ([a.vararg] if a.vararg else []) + ([a.kwarg] if a.kwarg else []):
+                bound.add(arg.arg)
+        elif isinstance(node, ast.Name) and isinstance(node.ctx, (ast.Store, ast.Del)):
+            bound.add(node.id)
+        elif isinstance(node, (ast.Import, ast.ImportFrom)):
+            for alias in node.names:
+                bound.add((alias.asname or alias.name).split(".")[0])
+        elif isinstance(node, ast.ExceptHandler) and node.name:
+            bound.add(node.name)
+        elif isinstance(node, (ast.Global, ast.Nonlocal)):
+            bound.update(node.names)
+        elif isinstance(node, ast.MatchAs) and node.name:
+            bound.add(node.name)
+    return bound
+
+
+def test_every_python_file_compiles_and_reads_only_names_it_binds():
+    problems = []
+    for path in sorted(set(_python_files())):
+        src = open(path).read()
+        try:
+            tree = ast.parse(src, filename=path)
+            compile(src, path, "exec")
+        except SyntaxError as e:
+            problems.append(f"{path}: {e}")
+            continue
+        bound = _bound_names(tree)
+        for node in ast.walk(tree):
+            if isinstance(node, ast.Name) and isinstance(node.ctx, ast.Load) and node.id not in bound:
+                problems.append(f"{os.path.relpath(path, ROOT)}:{node.lineno}: name '{node.id}' is never bound in this file")
+    assert not problems, "\n".join(problems)
+
+
+def test_bench_reference_arm_answers_without_a_gpu():
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "1"],
+                       capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line and "\n" not in line["unavailable"]
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--help"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "--schedule" in r.stdout and "--gpus" in r.stdout
