@@ -80,6 +80,8 @@ PYBIND11_MODULE(_C, m) {
   m.attr("MoodistProcessGroup") = backend;
   m.def("load_variant_table", &load_variant_table, py::arg("path"), py::arg("world"),
         "thresholds a group of `world` ranks would take from a MOODIST_VARIANT_TABLE file");
+  // the reference's module has the same liveness probe (wrapper/module.cc:1355-1428, `hello`)
+  m.def("hello", [] { return std::string("moodist_b200 native extension (sm_100a kernels, host engine, TcpStore)"); });
   m.def("live_process_groups", &MoodistBackend::live, "every moodist group alive in this process");
   m.def("find_process_group", &MoodistBackend::find, "the live moodist group with this name, or None");
 
