@@ -208,3 +208,20 @@ def adamw_(p, g, m, v, lr: float, betas=(0.9, 0.95), eps: float = 1e-8, weight_d
     p.copy_(pf)
     m.copy_(mf)
     v.copy_(vf)
+
+
+def adamw_master_(p, master, g, m, v, lr: float, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.1,
+                  step: int = 1) -> None:
+    """AdamW on an fp32 master copy with fp32 moments; ``p`` (any float dtype, usually bf16) receives the rounded
+    result.  The arithmetic mixed-precision FSDP keeps per shard: ``master``, ``m`` and ``v`` are fp32 tensors of
+    ``p``'s shape, ``g`` the gradient in fp32 or bf16.  Plain PyTorch ops on whatever device the tensors live on
+    (several passes over the shard; the single-pass kernel is ``adamw_``, which keeps bf16 state)."""
+    b1, b2 = betas
+    gr = g if g.dtype == torch.float32 else g.float()
+    m.mul_(b1).add_(gr, alpha=1 - b1)
+    v.mul_(b2).addcmul_(gr, gr, value=1 - b2)
+    bc1 = 1 - b1**step
+    bc2 = 1 - b2**step
+    denom = v.sqrt().div_(bc2**0.5).add_(eps)
+    master.mul_(1 - lr * weight_decay).addcdiv_(m, denom, value=-lr / bc1)
+    p.copy_(master)

@@ -47,6 +47,7 @@ class ShardedTrainer:
         schedule: str = "regather",
         fused: bool = True,
         copy_engine: bool | None = None,
+        master_weights: bool = False,
     ):
         if not torch.cuda.is_available():
             raise RuntimeError("ShardedTrainer needs a CUDA device")
@@ -83,7 +84,8 @@ class ShardedTrainer:
 
                 names = {id(p): n for n, p in m.named_parameters()}
                 self.engine = RegatherEngine(units, group=self.group, lr=lr, betas=(0.9, 0.95), weight_decay=0.1,
-                                             fused=fused, symmetric_memory=symmetric_memory, param_names=names)
+                                             fused=fused, symmetric_memory=symmetric_memory, param_names=names,
+                                             master_weights=master_weights)
             elif schedule == "resident":
                 from .sharded import ShardedEngine
 

@@ -36,7 +36,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from ..ops.train import adamw_
+from ..ops.train import adamw_, adamw_master_
 
 _ALIGN = 128  # elements
 
@@ -169,11 +169,15 @@ class RegatherEngine:
     """
 
     def __init__(self, units, group=None, lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, fused=True,
-                 symmetric_memory=True, sync_init=True, param_names=None):
+                 symmetric_memory=True, sync_init=True, param_names=None, master_weights=False):
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        # master_weights: every shard also exists in fp32 with fp32 AdamW moments (what a mixed-precision FSDP2
+        # run keeps); the bf16 shard the GEMMs and gathers read is the rounded master. Default off: bf16 shards
+        # updated in place with bf16 moments by the single-pass kernel.
+        self.master_weights = bool(master_weights)
         self.step_count = 0
         first = next(p for _, mods in units for m in mods for p in m.parameters())
         self.device = first.device
@@ -192,6 +196,7 @@ class RegatherEngine:
         self.exposed_events = None  # list of (before, after) event pairs when profiling the forward/backward waits
         self.units: list[_Unit] = []
         self._small = []  # parameters kept whole
+        self._small_master = None
         self._step_open = False
         self._fwd_cursor = -1  # unit whose forward is in progress
         names = param_names or {}
@@ -246,8 +251,10 @@ class RegatherEngine:
                 with torch.no_grad():
                     if hi > lo:
                         h.shard[: hi - lo].copy_(p.data[lo:hi])
-                h.exp_avg = torch.zeros_like(h.shard)
-                h.exp_avg_sq = torch.zeros_like(h.shard)
+                state_dtype = torch.float32 if self.master_weights else h.shard.dtype
+                h.exp_avg = torch.zeros_like(h.shard, dtype=state_dtype)
+                h.exp_avg_sq = torch.zeros_like(h.shard, dtype=state_dtype)
+                h.master = h.shard.to(torch.float32, copy=True) if self.master_weights else None
                 if w > 1:
                     h.gshard = torch.zeros((h.rows, h.k), dtype=torch.float32, device=self.device)
                 p.data = h.shard  # the parameter now *is* this rank's rows
@@ -285,8 +292,9 @@ class RegatherEngine:
             self._small_full = self._alloc((self._small_numel,), dtype, symmetric=True)
             self._small_grad = self._alloc((self._small_numel,), dtype, symmetric=True)
             n = self._small_numel // w
-            self._small_m = torch.zeros(n, dtype=dtype, device=self.device)
-            self._small_v = torch.zeros(n, dtype=dtype, device=self.device)
+            state_dtype = torch.float32 if self.master_weights else dtype
+            self._small_m = torch.zeros(n, dtype=state_dtype, device=self.device)
+            self._small_v = torch.zeros(n, dtype=state_dtype, device=self.device)
             with torch.no_grad():
                 for p, o in zip(self._small, self._small_offsets):
                     view = self._small_full[o : o + p.numel()].view(p.shape)
@@ -294,6 +302,9 @@ class RegatherEngine:
                     p.data = view
             if sync_init and w > 1:
                 dist.broadcast(self._small_full, src=src, group=self.group)
+            n = self._small_numel // w
+            if self.master_weights:
+                self._small_master = self._small_full[r * n : (r + 1) * n].to(torch.float32, copy=True)
         self._small_ready = None
 
     # ---- stream helpers ----------------------------------------------------------------------------
@@ -446,8 +457,7 @@ class RegatherEngine:
             else:
                 grad = g
             step = self.step_count + 1
-            adamw_(h.shard.view(-1), grad.reshape(-1), h.exp_avg.view(-1), h.exp_avg_sq.view(-1), self.lr, self.betas,
-                   self.eps, self.weight_decay, step)
+            self._adamw(h.shard.view(-1), h.master, grad.reshape(-1), h.exp_avg.view(-1), h.exp_avg_sq.view(-1), step)
             if self.cuda:
                 ev = torch.cuda.Event()
                 ev.record()
@@ -462,6 +472,12 @@ class RegatherEngine:
                 ev = torch.cuda.Event()
                 ev.record(self.comm_stream)
                 u.updated = ev
+
+    def _adamw(self, p, master, g, m, v, step) -> None:
+        if master is not None:
+            adamw_master_(p, master.view(-1), g, m, v, self.lr, self.betas, self.eps, self.weight_decay, step)
+        else:
+            adamw_(p, g, m, v, self.lr, self.betas, self.eps, self.weight_decay, step)
 
     def _reduce_scatter(self, out32, g) -> None:
         if self._moodist is not None:
@@ -507,7 +523,7 @@ class RegatherEngine:
             else:
                 g = torch.empty(n, dtype=torch.float32, device=self.device)
                 self._reduce_scatter(g, self._small_grad)
-            adamw_(pshard, g, self._small_m, self._small_v, self.lr, self.betas, self.eps, self.weight_decay, step)
+            self._adamw(pshard, self._small_master, g, self._small_m, self._small_v, step)
             if w > 1:
                 if self.cuda:
                     dist.all_gather_into_tensor(self._small_full, pshard, group=self.group)
@@ -559,10 +575,14 @@ class RegatherEngine:
             for h in u.weights:
                 st["weights"][h.name] = {"param": h.shard.clone(), "exp_avg": h.exp_avg.clone(),
                                          "exp_avg_sq": h.exp_avg_sq.clone()}
+                if h.master is not None:
+                    st["weights"][h.name]["master"] = h.master.clone()
         if self._small:
             n = self._small_numel // self.world
             st["small"] = {"param": self._small_full[self.rank * n : (self.rank + 1) * n].clone(),
                            "exp_avg": self._small_m.clone(), "exp_avg_sq": self._small_v.clone()}
+            if self._small_master is not None:
+                st["small"]["master"] = self._small_master.clone()
         return st
 
     def load_state_dict(self, state: dict) -> None:
@@ -577,6 +597,8 @@ class RegatherEngine:
                     h.shard.copy_(s["param"])
                     h.exp_avg.copy_(s["exp_avg"])
                     h.exp_avg_sq.copy_(s["exp_avg_sq"])
+                    if h.master is not None:
+                        h.master.copy_(s["master"] if "master" in s else s["param"])
                 u.version += 1
             if self._small:
                 s = state["small"]
@@ -585,6 +607,8 @@ class RegatherEngine:
                 pshard.copy_(s["param"])
                 self._small_m.copy_(s["exp_avg"])
                 self._small_v.copy_(s["exp_avg_sq"])
+                if self._small_master is not None:
+                    self._small_master.copy_(s["master"] if "master" in s else s["param"])
                 if self.world > 1:
                     if self.cuda:
                         dist.all_gather_into_tensor(self._small_full, pshard, group=self.group)

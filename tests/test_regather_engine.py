@@ -29,11 +29,11 @@ def _batch(rank, step, cfg):
     return torch.randint(0, cfg.vocab_size, (2, 9), generator=g)
 
 
-def _engine(model, hp):
+def _engine(model, hp, **kw):
     from moodist_b200.parallel.regather import RegatherEngine
 
     names = {id(p): n for n, p in model.named_parameters()}
-    return RegatherEngine(_units(model), param_names=names, **hp)
+    return RegatherEngine(_units(model), param_names=names, **hp, **kw)
 
 
 def _check(eng, model, ref, rtol, atol, what=""):
@@ -43,14 +43,14 @@ def _check(eng, model, ref, rtol, atol, what=""):
         torch.testing.assert_close(got, q, rtol=rtol, atol=atol, msg=lambda m, n=n: f"{what}{n}: {m}")
 
 
-def _engine_run(rank, world, port, steps, resume_at):
+def _engine_run(rank, world, port, steps, resume_at, master=False):
     from moodist_b200.models.llama import loss_fn
 
     dist = init_moodist(rank, world, port)
     cfg, model = _tiny_model()
     ref = copy.deepcopy(model)
     hp = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
-    eng = _engine(model, hp)
+    eng = _engine(model, hp, master_weights=master)
     # at rest every matrix parameter is this rank's rows only
     for u in eng.units:
         for h in u.weights:
@@ -93,7 +93,7 @@ def _engine_run(rank, world, port, steps, resume_at):
         assert "second backward" in str(e)
     # resume from the checkpoint with a fresh engine and replay the remaining steps
     cfg2, model2 = _tiny_model()
-    eng2 = _engine(model2, hp)
+    eng2 = _engine(model2, hp, master_weights=master)
     eng2.load_state_dict(saved)
     for step in range(resume_at, steps):
         tok = _batch(rank, step, cfg2)
@@ -114,3 +114,27 @@ def test_regather_world1():
 
 def test_regather_world3_padded_rows():
     run_ranks(_engine_run, 3, 3, 2, timeout=180)
+
+
+def test_regather_with_fp32_master_weights_world2():
+    """fp32 master shards and fp32 moments (the torch-op AdamW path): same trajectory as the oracle, and the
+    master copies travel through the checkpoint."""
+    run_ranks(_engine_run, 2, 4, 2, True, timeout=180)
+
+
+def test_adamw_master_matches_torch_adamw_and_rounds_into_bf16():
+    from moodist_b200.ops.train import adamw_master_
+
+    torch.manual_seed(0)
+    master = torch.randn(1000)
+    p = master.to(torch.bfloat16)
+    q = master.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([q], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m, v = torch.zeros(1000), torch.zeros(1000)
+    for step in range(1, 5):
+        g = torch.randn(1000)
+        q.grad = g.clone()
+        opt.step()
+        adamw_master_(p, master, g.to(torch.bfloat16) if step % 2 else g, m, v, 1e-2, (0.9, 0.95), 1e-8, 0.1, step)
+    torch.testing.assert_close(master, q.detach(), rtol=2e-2, atol=2e-2)  # two of the gradients were rounded to bf16
+    assert torch.equal(p, master.to(torch.bfloat16))
