@@ -88,7 +88,7 @@ def _drops(rank, world, port):
 
 
 def test_dropped_message_is_detected_and_reported_everywhere():
-    statuses = run_ranks(_drops, 3, timeout=120, expect_failure=True, env={"MOODIST_HEARTBEAT_MS": 300})
+    statuses = run_ranks(_drops, 3, timeout=120, expect_failure=True, env={"MOODIST_HEARTBEAT_MS": 1000})
     assert statuses == ["ok"] * 3, statuses
 
 
