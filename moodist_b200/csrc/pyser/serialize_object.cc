@@ -197,13 +197,18 @@ class Packer {
       raw(&d, 8);
       return;
     }
-    // everything below is memoised by identity
-    auto [slot, fresh] = memo_.try_emplace(obj, out.size());
-    if (!fresh) {
-      out[*slot] |= 0x80;
-      byte(T_OFFSET);
-      u64(*slot);
-      return;
+    // Everything below is memoised by identity, except objects with a single reference: whoever holds that
+    // reference is the only way to reach them, so they cannot come up a second time (and cannot be the target of
+    // a cycle, which would be a second reference). Skipping them keeps the memo small for the common case of
+    // containers full of freshly built strings and tuples; the bytes produced are the same.
+    if (Py_REFCNT(obj) != 1) {
+      auto [slot, fresh] = memo_.try_emplace(obj, out.size());
+      if (!fresh) {
+        out[*slot] |= 0x80;
+        byte(T_OFFSET);
+        u64(*slot);
+        return;
+      }
     }
     if (depth_ > 2000) {
       PyErr_SetString(PyExc_RecursionError, "moodist.serialize: object nesting too deep");
