@@ -88,6 +88,7 @@ Ref checked(PyObject* o) {
 }
 
 PyObject *s_qualname, *s_module, *s_reduce_ex, *s_dict, *s_setstate, *s_dot, *s_extend, *s_append, *s_five;
+PyObject* g_newobj;  // copyreg.__newobj__, what object.__reduce_ex__(2+) names as the constructor
 
 void init_strings() {
   if (s_qualname) return;
@@ -100,6 +101,11 @@ void init_strings() {
   s_extend = PyUnicode_InternFromString("extend");
   s_append = PyUnicode_InternFromString("append");
   s_five = PyLong_FromLong(5);
+  if (PyObject* copyreg = PyImport_ImportModule("copyreg")) {
+    g_newobj = PyObject_GetAttrString(copyreg, "__newobj__");
+    Py_DECREF(copyreg);
+  }
+  if (!g_newobj) PyErr_Clear();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -177,6 +183,67 @@ class PtrMap {
   }
   std::vector<PyObject*> keys_;
   std::vector<size_t> vals_;
+  size_t mask_ = 0, count_ = 0;
+  int shift_ = 0;
+};
+
+// Offsets of stored objects -> the objects, for the unpacker: open addressing on offset + 1 (0 marks an empty
+// slot). Holds one reference per entry.
+class OffsetMap {
+ public:
+  OffsetMap() { rehash(256); }
+  ~OffsetMap() {
+    for (size_t i = 0; i < keys_.size(); ++i)
+      if (keys_[i]) Py_DECREF(vals_[i]);
+  }
+  OffsetMap(const OffsetMap&) = delete;
+  OffsetMap& operator=(const OffsetMap&) = delete;
+
+  PyObject* find(size_t offset) const {
+    size_t key = offset + 1;
+    for (size_t i = index(key); keys_[i]; i = (i + 1) & mask_)
+      if (keys_[i] == key) return vals_[i];
+    return nullptr;
+  }
+  // takes its own reference; a second object stored at the same offset replaces the first
+  void put(size_t offset, PyObject* o) {
+    if ((count_ + 1) * 2 > keys_.size()) rehash(keys_.size() * 2);
+    Py_INCREF(o);
+    size_t key = offset + 1;
+    size_t i = index(key);
+    for (; keys_[i]; i = (i + 1) & mask_) {
+      if (keys_[i] == key) {
+        Py_DECREF(vals_[i]);
+        vals_[i] = o;
+        return;
+      }
+    }
+    keys_[i] = key;
+    vals_[i] = o;
+    ++count_;
+  }
+
+ private:
+  size_t index(size_t key) const { return (size_t)((uint64_t)key * 0x9E3779B97F4A7C15ull >> shift_); }
+  void rehash(size_t n) {
+    std::vector<size_t> ok;
+    std::vector<PyObject*> ov;
+    ok.swap(keys_);
+    ov.swap(vals_);
+    keys_.assign(n, 0);
+    vals_.assign(n, nullptr);
+    mask_ = n - 1;
+    shift_ = 64 - __builtin_ctzll(n);
+    for (size_t j = 0; j < ok.size(); ++j) {
+      if (!ok[j]) continue;
+      size_t i = index(ok[j]);
+      while (keys_[i]) i = (i + 1) & mask_;
+      keys_[i] = ok[j];
+      vals_[i] = ov[j];
+    }
+  }
+  std::vector<size_t> keys_;
+  std::vector<PyObject*> vals_;
   size_t mask_ = 0, count_ = 0;
   int shift_ = 0;
 };
@@ -430,9 +497,6 @@ class Packer {
 class Unpacker {
  public:
   Unpacker(const uint8_t* data, size_t n) : base_(data), p_(data), end_(data + n) {}
-  ~Unpacker() {
-    for (auto& [off, o] : stored_) Py_DECREF(o);
-  }
 
   size_t consumed() const { return (size_t)(p_ - base_); }
 
@@ -520,10 +584,10 @@ class Unpacker {
       case T_CLASS: return unpack_class(store, offset);
       case T_OFFSET: {
         uint64_t off = read<uint64_t>();
-        auto it = stored_.find(off);
-        if (it == stored_.end()) bad("reference to an object that was not stored");
-        Py_INCREF(it->second);
-        return it->second;
+        PyObject* found = stored_.find(off);
+        if (!found) bad("reference to an object that was not stored");
+        Py_INCREF(found);
+        return found;
       }
       default: bad("unknown type tag");
     }
@@ -532,7 +596,7 @@ class Unpacker {
 
  private:
   const uint8_t *base_, *p_, *end_;
-  std::unordered_map<size_t, PyObject*> stored_;
+  OffsetMap stored_;
 
   [[noreturn]] void bad(const char* what) {
     PyErr_Format(PyExc_ValueError, "moodist.deserialize: %s (at byte %zu)", what, consumed());
@@ -552,14 +616,7 @@ class Unpacker {
     memcpy(&v, take(sizeof(T)), sizeof(T));
     return v;
   }
-  void remember(size_t offset, PyObject* o) {
-    Py_INCREF(o);
-    auto [it, fresh] = stored_.try_emplace(offset, o);
-    if (!fresh) {
-      Py_DECREF(it->second);
-      it->second = o;
-    }
-  }
+  void remember(size_t offset, PyObject* o) { stored_.put(offset, o); }
   PyObject* keep(bool store, size_t offset, Ref r) {
     if (store) remember(offset, r.p);
     return r.release();
@@ -594,7 +651,15 @@ class Unpacker {
     Ref func(unpack());
     Ref args(unpack());
     if (!PyTuple_Check(args.p)) bad("class args must be a tuple");
-    Ref obj = checked(PyObject_Call(func.p, args.p, nullptr));
+    Ref obj;
+    PyObject* cls = PyTuple_GET_SIZE(args.p) ? PyTuple_GET_ITEM(args.p, 0) : nullptr;
+    if (func.p == g_newobj && cls && PyType_Check(cls) && ((PyTypeObject*)cls)->tp_new) {
+      // copyreg.__newobj__(cls, *rest) is cls.__new__(cls, *rest): make that call without the Python frame
+      Ref rest = checked(PyTuple_GetSlice(args.p, 1, PyTuple_GET_SIZE(args.p)));
+      obj = checked(((PyTypeObject*)cls)->tp_new((PyTypeObject*)cls, rest.p, nullptr));
+    } else {
+      obj = checked(PyObject_Call(func.p, args.p, nullptr));
+    }
     if (store) remember(offset, obj.p);
     uint8_t bits = u8();
     if (bits & 1) {
