@@ -29,11 +29,13 @@ struct Waiter {
   std::mutex mu;
   std::condition_variable cv;
   bool done = false;
+  std::atomic<bool> done_hint{false};  // set with `done`; what a waiter polls before it goes to sleep
   std::string error;
   void finish(std::string err = {}) {
     std::lock_guard<std::mutex> lk(mu);
     done = true;
     error = std::move(err);
+    done_hint.store(true, std::memory_order_release);
     cv.notify_all();
   }
 };
@@ -409,7 +411,8 @@ class HostGroupImpl final : public HostGroup {
     auto out = std::make_shared<std::vector<uint64_t>>();
     auto waiter = std::make_shared<Waiter>();
     run_on_engine([this, out, waiter] {
-      *out = {transport_.bytes_sent(), transport_.bytes_received(), transport_.bytes_direct(), (uint64_t)direct_peers_};
+      *out = {transport_.bytes_sent(), transport_.bytes_received(), transport_.bytes_direct(), (uint64_t)direct_peers_,
+              (uint64_t)transport_.unix_peers()};
       waiter->finish();
     });
     std::unique_lock<std::mutex> lk(waiter->mu);
@@ -510,6 +513,9 @@ class HostGroupImpl final : public HostGroup {
   }
 
   void wait(Waiter& wt, const char* what) {
+    // A sleeping thread costs tens of microseconds to wake; most operations of the engine finish sooner than
+    // that, so look at the flag for a short while first.
+    spin_until(wt.done_hint, spin_us_);
     std::unique_lock<std::mutex> lk(wt.mu);
     while (!wt.done) {
       wt.cv.wait_for(lk, std::chrono::milliseconds(200));
@@ -556,9 +562,14 @@ class HostGroupImpl final : public HostGroup {
     pthread_setname_np(pthread_self(), "moodist-cputhrd");
     double last_beat = now_seconds();
     double last_iter = last_beat;
+    double last_active = last_beat;
     while (!stop_) {
       bool busy = !works_.empty();
-      poller_.poll(busy ? 0 : 50);
+      // After any activity the loop keeps polling without blocking for a short while: a caller that issues
+      // operations back to back (queue gets, small collectives, store-like request / reply traffic) then never
+      // pays the wake-up of a sleeping thread.
+      bool spin = busy || (spin_us_ > 0 && now_seconds() - last_active < spin_us_ * 1e-6);
+      int events = poller_.poll(spin ? 0 : 50);
       double now = now_seconds();
       if (debug_cpu_ && now - last_iter > 0.001 && busy) log_info("engine: lost %.1f ms between iterations", (now - last_iter) * 1e3);
       last_iter = now;
@@ -569,7 +580,15 @@ class HostGroupImpl final : public HostGroup {
         std::lock_guard<std::mutex> lk(queue_mu_);
         q.swap(queue_);
       }
-      for (auto& f : q) f();
+      if (q.size() > 1) {
+        // a burst of requests (queue puts, messages): their records leave in one write per connection
+        transport_.hold_sends();
+        for (auto& f : q) f();
+        transport_.release_sends();
+      } else {
+        for (auto& f : q) f();
+      }
+      if (events > 0 || !q.empty() || busy) last_active = now;
       // progress
       for (auto it = works_.begin(); it != works_.end();) {
         if (step_work(**it))
@@ -853,6 +872,7 @@ class HostGroupImpl final : public HostGroup {
   double shutdown_deadline_ = 0, shutdown_release_at_ = 0;
   double heartbeat_s_ = 30;
   bool heartbeat_on_ = true, debug_cpu_ = false;
+  double spin_us_ = spin_microseconds();
   bool profiling_ = false;
   std::vector<TraceEvent> trace_;
 

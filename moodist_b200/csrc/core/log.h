@@ -5,6 +5,7 @@
 // format as the reference (core/logging.h:30-116).
 #pragma once
 
+#include <atomic>
 #include <chrono>
 #include <cstdarg>
 #include <cstdio>
@@ -96,6 +97,31 @@ inline bool env_flag(const char* name) { return env_long(name, 0) != 0; }
 
 inline double now_seconds() {
   return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+// How long (microseconds) a thread looks at a completion flag, and the engine thread keeps polling after its last
+// activity, before it blocks. MOODIST_SPIN_US overrides; 0 blocks at once.
+inline double spin_microseconds() {
+  static const double v = (double)env_long("MOODIST_SPIN_US", 100);
+  return v;
+}
+
+// Polls `flag` for at most `us` microseconds; true when it was seen set.
+inline bool spin_until(const std::atomic<bool>& flag, double us) {
+  if (flag.load(std::memory_order_acquire)) return true;
+  if (us <= 0) return false;
+  const double until = now_seconds() + us * 1e-6;
+  for (;;) {
+    for (int i = 0; i < 64; ++i) {
+      if (flag.load(std::memory_order_acquire)) return true;
+#if defined(__x86_64__) || defined(__i386__)
+      __builtin_ia32_pause();
+#elif defined(__aarch64__)
+      asm volatile("yield");
+#endif
+    }
+    if (now_seconds() >= until) return false;
+  }
 }
 
 }  // namespace moodist

@@ -217,10 +217,10 @@ void Conn::flush() {
         o.pass_fd = -1;
       }
     } else {
-      // gather up to 16 queued buffers into one writev
-      iovec iov[16];
+      // gather up to 64 queued buffers into one writev
+      iovec iov[64];
       int cnt = 0;
-      for (auto it = out_.begin(); it != out_.end() && cnt < 16; ++it) {
+      for (auto it = out_.begin(); it != out_.end() && cnt < 64; ++it) {
         if (it->pass_fd >= 0 && it != out_.begin()) break;
         if (it->len == it->off) {
           if (it == out_.begin()) break;
@@ -522,7 +522,7 @@ void Poller::connect(const std::string& addr, int port, std::function<void(std::
   add(fd, EPOLLIN | EPOLLRDHUP | EPOLLOUT);
 }
 
-void Poller::poll(int timeout_ms) {
+int Poller::poll(int timeout_ms) {
   epoll_event evs[64];
   int n = epoll_wait(ep_, evs, 64, timeout_ms);
   for (int i = 0; i < n; ++i) {
@@ -556,6 +556,7 @@ void Poller::poll(int timeout_ms) {
     if (evs[i].events & EPOLLOUT) c->handle_writable();
     if (c->open() && (evs[i].events & (EPOLLIN | EPOLLHUP | EPOLLRDHUP | EPOLLERR))) c->handle_readable();
   }
+  return n > 0 ? n : 0;
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -133,7 +133,7 @@ class Poller {
   void connect(const std::string& addr, int port, std::function<void(std::shared_ptr<Conn>)> done);
 
   // Run handlers for whatever is ready; waits at most timeout_ms.
-  void poll(int timeout_ms);
+  int poll(int timeout_ms);  // returns how many descriptors had events
   // Wake a poll() in progress from another thread.
   void wake();
 

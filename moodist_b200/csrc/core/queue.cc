@@ -29,15 +29,18 @@ struct Sync {
   std::mutex mu;
   std::condition_variable cv;
   bool done = false;
+  std::atomic<bool> done_hint{false};  // set with `done`; polled briefly before a waiter goes to sleep
   std::string error;
   void finish(std::string err = {}) {
     std::lock_guard<std::mutex> lk(mu);
     done = true;
     error = std::move(err);
+    done_hint.store(true, std::memory_order_release);
     cv.notify_all();
   }
   // false on timeout
   bool wait(double timeout_s) {
+    spin_until(done_hint, spin_microseconds());
     std::unique_lock<std::mutex> lk(mu);
     if (timeout_s < 0) {
       cv.wait(lk, [&] { return done; });

@@ -78,6 +78,12 @@ class TcpTransport {
   // addrs[r] = what rank r's listen() returned. Dials the higher ranks.
   void connect_all(const std::vector<std::vector<std::string>>& addrs);
   bool all_connected() const;
+  // Between hold_sends() and release_sends() records only queue on their connections; release_sends() writes each
+  // connection's backlog with as few system calls as it takes. For a caller about to send a burst.
+  // how many peers are reached over a unix-domain socket (same machine, same network namespace)
+  int unix_peers() const;
+  void hold_sends();
+  void release_sends();
   int connected_count() const;
 
   void on_recv(RecvFn f) { recv_ = std::move(f); }

@@ -53,9 +53,11 @@ PYBIND11_MODULE(_C, m) {
                 out["tcp_bytes_received"] = c.at(1);
                 out["direct_bytes"] = c.at(2);
                 out["direct_peers"] = c.at(3);
+                out["unix_socket_peers"] = c.at(4);
                 return out;
               },
-              "traffic of the host engine: bytes over TCP, bytes copied directly between processes of this machine")
+              "traffic of the host engine: bytes over its sockets, bytes copied directly between processes of this machine, "
+              "and how many peers are reached that way / over a unix-domain socket")
           .def(
               "stats",
               [](MoodistBackend& self, bool wait) {

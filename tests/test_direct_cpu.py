@@ -73,3 +73,27 @@ def test_direct_copies_between_cpu_ranks_world3():
 
 def test_forced_tcp_fallback():
     run_ranks(_body, 2, False, timeout=180, env={"MOODIST_DIRECT_CPU": 0})
+
+
+def _sockets(rank, world, port, unix_wanted):
+    dist = init_moodist(rank, world, port)
+    import moodist_b200
+
+    pg = moodist_b200.get_backend(device="cpu")
+    x = torch.full((1000,), float(rank + 1))
+    dist.all_reduce(x)
+    assert float(x[0]) == world * (world + 1) / 2
+    stats = pg.host_stats()
+    # ranks of one machine reach each other over unix-domain sockets unless that is switched off, in which case
+    # the TCP addresses advertised after it are used
+    assert stats["unix_socket_peers"] == (world - 1 if unix_wanted else 0), stats
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_same_machine_ranks_use_unix_sockets():
+    run_ranks(_sockets, 3, True, timeout=120)
+
+
+def test_tcp_when_unix_sockets_are_off():
+    run_ranks(_sockets, 2, False, timeout=120, env={"MOODIST_DISABLE_UNIX_SOCKETS": 1})
