@@ -153,6 +153,7 @@ struct WaitObj {
   std::mutex mu;
   std::condition_variable cv;
   bool done = false;
+  std::atomic<bool> done_hint{false};  // set with `done`; polled briefly before the caller sleeps
   std::string error;
   Bytes result;
   void finish(Bytes r, std::string err = {}) {
@@ -161,6 +162,7 @@ struct WaitObj {
     done = true;
     result = std::move(r);
     error = std::move(err);
+    done_hint.store(true, std::memory_order_release);
     cv.notify_all();
   }
 };
@@ -328,6 +330,7 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
     });
     double start = now_seconds();
     double limit = (double)timeout.count() / 1000.0;
+    spin_until(w->done_hint, spin_microseconds());  // most requests are answered sooner than a thread wakes up
     std::unique_lock<std::mutex> lk(w->mu);
     while (!w->done) {
       w->cv.wait_for(lk, std::chrono::milliseconds(250));  // sliced so signals and shutdown are noticed
@@ -445,8 +448,11 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
       set_fatal(e.what());
     }
     double last_tick = now_seconds();
+    double last_active = last_tick;
+    const double spin_s = spin_microseconds() * 1e-6;
     while (!stop_) {
-      poller_.poll(20);
+      // keep polling for a moment after any activity: request / reply sequences then skip the thread wake-ups
+      int events = poller_.poll(now_seconds() - last_active < spin_s ? 0 : 20);
       std::deque<std::function<void()>> q;
       {
         std::lock_guard<std::mutex> lk(queue_mu_);
@@ -454,6 +460,7 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
       }
       for (auto& f : q) f();
       double now = now_seconds();
+      if (events > 0 || !q.empty()) last_active = now;
       if (now - last_tick > 0.05) {
         last_tick = now;
         tick(now);
