@@ -71,3 +71,18 @@ def test_bench_reference_arm_answers_without_a_gpu():
     assert line["impl"] == "reference" and "unavailable" in line and "\n" not in line["unavailable"]
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--help"], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "--schedule" in r.stdout and "--gpus" in r.stdout
+
+
+def test_packaging_lists_every_subpackage_and_the_package_version():
+    out = subprocess.run([sys.executable, "setup.py", "--version"], cwd=ROOT, capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    scope = {}
+    exec(open(os.path.join(ROOT, "moodist_b200", "version.py")).read(), scope)
+    assert out.stdout.strip().splitlines()[-1] == scope["__version__"]
+    # every directory of the package that holds an __init__.py is named in setup.py (a new one is easy to forget)
+    src = open(os.path.join(ROOT, "setup.py")).read()
+    pkg = os.path.join(ROOT, "moodist_b200")
+    for d, _, files in os.walk(pkg):
+        if "__init__.py" in files:
+            name = os.path.relpath(d, ROOT).replace(os.sep, ".")
+            assert f'"{name}"' in src, f"{name} is missing from setup.py's package list"
