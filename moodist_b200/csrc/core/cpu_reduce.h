@@ -13,7 +13,18 @@
 namespace moodist {
 
 enum : int { kDtU8 = 0, kDtI8 = 1, kDtI16 = 2, kDtI32 = 3, kDtI64 = 4, kDtF16 = 5, kDtF32 = 6, kDtF64 = 7, kDtBF16 = 15 };
-enum : int { kRedSum = 0, kRedAvg = 1, kRedMin = 3, kRedMax = 4, kRedPremulSum = 8 };
+// the values of c10d::ReduceOp; product and the bitwise three exist on the host path only
+enum : int {
+  kRedSum = 0, kRedAvg = 1, kRedProduct = 2, kRedMin = 3, kRedMax = 4, kRedBand = 5, kRedBor = 6, kRedBxor = 7,
+  kRedPremulSum = 8
+};
+inline bool cpu_dtype_is_integer(int dtype) {
+  return dtype == kDtU8 || dtype == kDtI8 || dtype == kDtI16 || dtype == kDtI32 || dtype == kDtI64;
+}
+inline bool cpu_reduce_op_supported(int op, int dtype) {
+  if (op == kRedBand || op == kRedBor || op == kRedBxor) return cpu_dtype_is_integer(dtype);
+  return op == kRedSum || op == kRedAvg || op == kRedProduct || op == kRedMin || op == kRedMax || op == kRedPremulSum;
+}
 
 inline size_t cpu_dtype_size(int dt) {
   switch (dt) {
@@ -134,6 +145,17 @@ void reduce_typed(void* out, const void* const* srcs, int nsrc, size_t n, int op
         for (size_t i = 0; i < m; ++i) {
           Acc b = Tr::load(sr + i);
           acc[i] = b > acc[i] ? b : acc[i];
+        }
+      } else if (op == kRedProduct) {
+        for (size_t i = 0; i < m; ++i) acc[i] = (Acc)(acc[i] * Tr::load(sr + i));
+      } else if (op == kRedBand || op == kRedBor || op == kRedBxor) {
+        if constexpr (std::is_integral_v<Acc>) {
+          if (op == kRedBand)
+            for (size_t i = 0; i < m; ++i) acc[i] = (Acc)(acc[i] & Tr::load(sr + i));
+          else if (op == kRedBor)
+            for (size_t i = 0; i < m; ++i) acc[i] = (Acc)(acc[i] | Tr::load(sr + i));
+          else
+            for (size_t i = 0; i < m; ++i) acc[i] = (Acc)(acc[i] ^ Tr::load(sr + i));
         }
       } else {
         for (size_t i = 0; i < m; ++i) acc[i] = (Acc)(acc[i] + Tr::load(sr + i));

@@ -211,7 +211,7 @@ class HostGroupImpl final : public HostGroup {
   void reduce_scatter(const void* in, void* out, size_t count, int dtype, int op, double premul) override {
     size_t esz = cpu_dtype_size(dtype);
     if (!esz) fail("moodist: reduce_scatter: unsupported dtype for CPU tensors");
-    check_op(op);
+    check_op(op, dtype);
     size_t chunk = count * esz;
     const uint8_t* x = static_cast<const uint8_t*>(in);
     auto tmp = scratch(chunk * world_);
@@ -240,7 +240,7 @@ class HostGroupImpl final : public HostGroup {
     if (count == 0) return;
     if (world_ == 1) {
       const void* srcs[1] = {in};
-      check_op(op);
+      check_op(op, dtype);
       cpu_reduce(out, srcs, 1, count, dtype, op, premul, op == kRedPremulSum);
       return;
     }
@@ -484,9 +484,10 @@ class HostGroupImpl final : public HostGroup {
     std::shared_ptr<Waiter> waiter;
   };
 
-  void check_op(int op) {
-    if (op != kRedSum && op != kRedAvg && op != kRedMin && op != kRedMax && op != kRedPremulSum)
-      fail("moodist: unsupported reduce op (supported: SUM, AVG, MIN, MAX, PREMUL_SUM)");
+  void check_op(int op, int dtype) {
+    if (!cpu_reduce_op_supported(op, dtype))
+      fail("moodist: unsupported reduce op for this dtype (CPU tensors: SUM, AVG, PRODUCT, MIN, MAX, PREMUL_SUM, and "
+           "BAND / BOR / BXOR on integer types)");
   }
 
   std::shared_ptr<Work> new_work(uint32_t op, const char* label) {

@@ -98,8 +98,19 @@ std::pair<int, double> reduce_code(const c10d::ReduceOp& op) {
       if (sup->tensor_factor.defined()) return {MB_PREMUL_SUM, sup->tensor_factor.item<double>()};
       return {MB_PREMUL_SUM, sup->double_factor};
     }
-    default: TORCH_CHECK(false, "moodist: unsupported reduce op (supported: SUM, AVG, MIN, MAX, PREMUL_SUM)");
+    // host path only (the kernels implement the five above, as the reference's core does: core/group.h:26)
+    case c10d::ReduceOp::PRODUCT: return {2, 1.0};
+    case c10d::ReduceOp::BAND: return {5, 1.0};
+    case c10d::ReduceOp::BOR: return {6, 1.0};
+    case c10d::ReduceOp::BXOR: return {7, 1.0};
+    default: TORCH_CHECK(false, "moodist: unsupported reduce op");
   }
+}
+
+void check_cuda_op(int op) {
+  TORCH_CHECK(op == MB_SUM || op == MB_AVG || op == MB_MIN || op == MB_MAX || op == MB_PREMUL_SUM,
+              "moodist: CUDA tensors support SUM, AVG, MIN, MAX and PREMUL_SUM (PRODUCT and the bitwise reductions "
+              "exist for CPU tensors only)");
 }
 
 void check_contig(const at::Tensor& t, const char* what) {
@@ -273,15 +284,31 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::allgather(std::vector<std::vector
   auto& outs = outputs[0];
   TORCH_CHECK((int)outs.size() == size_, "moodist: all_gather output list must have world_size entries");
   at::Tensor in = inputs[0].contiguous();
+  // Ranks may contribute different amounts (the output list says how much each one sends, and is the same on every
+  // rank): everybody then gathers slots of the largest size. Checked before anything is sent, so that a wrong
+  // list is an exception here and not a rejected transfer on some other rank.
+  TORCH_CHECK(outs[rank_].numel() == in.numel(), "moodist: all_gather output ", rank_, " has ", outs[rank_].numel(),
+              " elements but this rank's input has ", in.numel());
+  int64_t slot = 0;
+  for (auto& o : outs) {
+    TORCH_CHECK(o.scalar_type() == in.scalar_type() && o.device() == in.device(),
+                "moodist: all_gather outputs must have the input's dtype and device");
+    slot = std::max<int64_t>(slot, o.numel());
+  }
+  at::Tensor padded = in.reshape({-1});
+  if (in.numel() != slot) {
+    padded = at::empty({slot}, in.options());
+    padded.narrow(0, 0, in.numel()).copy_(in.reshape({-1}), in.is_cuda());
+  }
   // gather into one buffer, then hand the pieces out (reference: wrapper/processgroup_wrapper.cc:111-129)
-  at::Tensor flat = at::empty({size_ * in.numel()}, in.options());
-  auto work = _allgather_base(flat, in, opts);
+  at::Tensor flat = at::empty({size_ * slot}, in.options());
+  auto work = _allgather_base(flat, padded, opts);
   if (in.is_cuda()) {
     c10::cuda::CUDAGuard guard(in.device());
-    for (int r = 0; r < size_; ++r) outs[r].copy_(flat.narrow(0, r * in.numel(), in.numel()).view_as(in), true);
+    for (int r = 0; r < size_; ++r) outs[r].copy_(flat.narrow(0, r * slot, outs[r].numel()).view_as(outs[r]), true);
     return c10::make_intrusive<CudaWork>(rank_, c10d::OpType::ALLGATHER, outs, c10::cuda::getCurrentCUDAStream());
   }
-  for (int r = 0; r < size_; ++r) outs[r].copy_(flat.narrow(0, r * in.numel(), in.numel()).view_as(in));
+  for (int r = 0; r < size_; ++r) outs[r].copy_(flat.narrow(0, r * slot, outs[r].numel()).view_as(outs[r]));
   return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::ALLGATHER, outs);
 }
 
@@ -305,6 +332,7 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::_reduce_scatter_base(at::Tensor& 
   auto [op, premul] = reduce_code(opts.reduceOp);
   int dt = dtype_code(input.scalar_type());
   if (input.is_cuda()) {
+    check_cuda_op(op);
     c10::cuda::CUDAGuard guard(input.device());
     auto stream = c10::cuda::getCurrentCUDAStream();
     MOODIST_TRANSLATE(cudaGroup(input.get_device())
@@ -321,6 +349,7 @@ void MoodistBackend::reduceScatterCast(at::Tensor& output, const at::Tensor& inp
   check_contig(output, "reduce_scatter output");
   check_contig(input, "reduce_scatter input");
   TORCH_CHECK(input.is_cuda() && output.is_cuda(), "moodist: reduce_scatter_cast needs CUDA tensors");
+  check_cuda_op(op);
   TORCH_CHECK(input.numel() == output.numel() * size_, "moodist: reduce_scatter input must be world_size x output");
   c10::cuda::CUDAGuard guard(input.device());
   auto stream = c10::cuda::getCurrentCUDAStream();
@@ -360,6 +389,7 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::allreduce(std::vector<at::Tensor>
   auto [op, premul] = reduce_code(opts.reduceOp);
   int dt = dtype_code(t.scalar_type());
   if (t.is_cuda()) {
+    check_cuda_op(op);
     c10::cuda::CUDAGuard guard(t.device());
     auto stream = c10::cuda::getCurrentCUDAStream();
     MOODIST_TRANSLATE(cudaGroup(t.get_device())
@@ -459,7 +489,11 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::scatter(std::vector<at::Tensor>& 
   if (rank_ == root) {
     TORCH_CHECK(inputs.size() == 1 && (int)inputs[0].size() == size_, "moodist: scatter input list size");
     std::vector<at::Tensor> fl;
-    for (auto& t : inputs[0]) fl.push_back(t.reshape({-1}));
+    for (auto& t : inputs[0]) {
+      TORCH_CHECK(t.numel() == out.numel() && t.scalar_type() == out.scalar_type(),
+                  "moodist: scatter inputs must have the output's size and dtype");
+      fl.push_back(t.reshape({-1}));
+    }
     flat = at::cat(fl);
   }
   if (out.is_cuda()) {
