@@ -166,3 +166,83 @@ def _surface(rank, world, port):
 
 def test_torch_distributed_surface_world3():
     run_ranks(_surface, 3, timeout=240)
+
+
+def _wrappers(rank, world, port):
+    """torch's own parallel wrappers running over the backend: DDP, ZeroRedundancyOptimizer, DTensor, fully_shard."""
+    dist = init_moodist(rank, world, port)
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+    from torch.distributed.optim import ZeroRedundancyOptimizer
+    from torch.distributed.tensor import Replicate, Shard, distribute_tensor
+    from torch.nn.parallel import DistributedDataParallel as DDP
+
+    def same_everywhere(module):
+        flat = torch.cat([p.detach().reshape(-1) for p in module.parameters()])
+        outs = [torch.empty_like(flat) for _ in range(world)]
+        dist.all_gather(outs, flat)
+        return all(torch.equal(o, outs[0]) for o in outs)
+
+    # DDP: different data per rank, identical parameters after every step, equal to the single-process update
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))
+    oracle = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))
+    oracle.load_state_dict(net.state_dict())
+    ddp = DDP(net)
+    opt = torch.optim.SGD(ddp.parameters(), lr=0.1)
+    oopt = torch.optim.SGD(oracle.parameters(), lr=0.1)
+    for step in range(3):
+        xs = [torch.randn(8, 16, generator=torch.Generator().manual_seed(r * 10 + step)) for r in range(world)]
+        ddp(xs[rank]).sum().backward()
+        opt.step()
+        opt.zero_grad()
+        (sum(oracle(x).sum() for x in xs) / world).backward()
+        oopt.step()
+        oopt.zero_grad()
+    assert same_everywhere(net)
+    for p, q in zip(net.parameters(), oracle.parameters()):
+        torch.testing.assert_close(p, q, rtol=1e-5, atol=1e-6)
+
+    # ZeRO-1 optimizer wrapper
+    lin = torch.nn.Linear(8, 8)
+    for p in lin.parameters():
+        dist.broadcast(p.data, 0)
+    zopt = ZeroRedundancyOptimizer(lin.parameters(), optimizer_class=torch.optim.SGD, lr=0.1)
+    lin(torch.ones(2, 8)).sum().backward()
+    for p in lin.parameters():
+        dist.all_reduce(p.grad)
+    zopt.step()
+    assert same_everywhere(lin)
+
+    # DTensor: shard, replicate, re-shard along the other dimension, reduce
+    mesh = init_device_mesh("cpu", (world,))
+    full = torch.arange(world * 4 * 6, dtype=torch.float32).view(world * 4, 6)
+    dt = distribute_tensor(full, mesh, [Shard(0)])
+    assert torch.equal(dt.to_local(), full[rank * 4 : (rank + 1) * 4])
+    assert torch.equal(dt.redistribute(mesh, [Replicate()]).to_local(), full)
+    assert torch.equal(dt.redistribute(mesh, [Shard(1)]).full_tensor(), full)
+    assert float((dt * 2).sum().full_tensor()) == float(full.sum() * 2)
+
+    # fully_shard (FSDP2) on CPU parameters: all_gather_into_tensor / reduce_scatter_tensor under torch's schedule
+    torch.manual_seed(1)
+    fs = torch.nn.Sequential(torch.nn.Linear(12, 24), torch.nn.Linear(24, 6))
+    ref = torch.nn.Sequential(torch.nn.Linear(12, 24), torch.nn.Linear(24, 6))
+    ref.load_state_dict(fs.state_dict())
+    fully_shard(fs, mesh=mesh)
+    fopt = torch.optim.SGD(fs.parameters(), lr=0.1)
+    xs = [torch.randn(4, 12, generator=torch.Generator().manual_seed(100 + r)) for r in range(world)]
+    fs(xs[rank]).sum().backward()
+    fopt.step()
+    (sum(ref(x).sum() for x in xs) / world).backward()
+    with torch.no_grad():
+        for p in ref.parameters():
+            p -= 0.1 * p.grad
+    for p, q in zip(fs.parameters(), ref.parameters()):
+        torch.testing.assert_close(p.full_tensor(), q, rtol=1e-5, atol=1e-6)
+
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_torch_parallel_wrappers_over_the_backend_world2():
+    run_ranks(_wrappers, 2, timeout=240)
