@@ -115,3 +115,106 @@ def _queues(rank, world, port):
 @pytest.mark.parametrize("world", [2, 3])
 def test_queue(world):
     run_ranks(_queues, world, timeout=180)
+
+
+def _edges(rank, world, port):
+    import gc
+    import threading
+
+    dist = init_moodist(rank, world, port)
+    import moodist_b200 as moodist
+
+    pg = moodist.get_backend(device="cpu")
+    # several consumer threads on one queue: every item is delivered exactly once
+    q = moodist.Queue(pg, location=0, name="threads")
+    n = 200
+    if rank == 1:
+        for i in range(n):
+            q.put_object(i)
+    if rank == 0:
+        got, lock = [], threading.Lock()
+
+        def consume():
+            while True:
+                try:
+                    v = q.get_object(timeout=2)
+                except Empty:
+                    return
+                with lock:
+                    got.append(v)
+
+        workers = [threading.Thread(target=consume) for _ in range(4)]
+        for t in workers:
+            t.start()
+        for t in workers:
+            t.join()
+        assert sorted(got) == list(range(n))
+    dist.barrier()
+    # a named queue travels inside an object and is usable where it arrives
+    inner = moodist.Queue(pg, location=1, name="inner")
+    carrier = moodist.Queue(pg, location=0, name="carrier")
+    if rank == world - 1:
+        carrier.put_object({"reply_to": inner})
+    if rank == 0:
+        carrier.get_object(timeout=20)["reply_to"].put_object("pong")
+    if rank == 1:
+        assert inner.get_object(timeout=20) == "pong"
+    dist.barrier()
+    # an object far larger than what a message carries inline
+    big = moodist.Queue(pg, location=0, name="big-object")
+    if rank == 1:
+        big.put_object({"blob": b"z" * (3 << 20), "numbers": list(range(10000))})
+    if rank == 0:
+        o = big.get_object(timeout=30)
+        assert len(o["blob"]) == 3 << 20 and o["numbers"][-1] == 9999
+    dist.barrier()
+    # dtype and shape survive: narrow and wide types, bool, complex, 0-d, empty, a non-contiguous view
+    dq = moodist.Queue(pg, location=0, name="dtypes")
+    kinds = (torch.float16, torch.bfloat16, torch.float64, torch.int8, torch.uint8, torch.bool, torch.int16, torch.int32, torch.complex64)
+    tensors = [torch.arange(6).to(dt).view(2, 3) for dt in kinds]
+    tensors += [torch.tensor(3.5), torch.empty(0, 4), torch.arange(24.0).view(2, 3, 4)[:, 1]]
+    if rank == 1:
+        for t in tensors:
+            dq.put_tensor(t)
+    if rank == 0:
+        for t in tensors:
+            g = dq.get_tensor(timeout=20)
+            assert g.dtype == t.dtype and g.shape == t.shape and torch.equal(g, t)
+    dist.barrier()
+    # return_size reports what is left behind
+    rs = moodist.Queue(pg, location=0, name="sizes")
+    if rank == 0:
+        for i in range(3):
+            rs.put_object(i)
+        assert rs.get_object(return_size=True) == (0, 2)
+        assert rs.get_tensor(return_size=True)[1] == 1
+        assert rs.get_object() == 2
+    dist.barrier()
+    # many queues at once, spread over the ranks
+    many = [moodist.Queue(pg, location=i % world, name=f"many-{i}") for i in range(50)]
+    for i, mq in enumerate(many):
+        if rank == (i + 1) % world:
+            mq.put_object(i)
+    for i, mq in enumerate(many):
+        if rank == i % world:
+            assert mq.get_object(timeout=20) == i
+    dist.barrier()
+    with pytest.raises(RuntimeError, match="not a rank"):
+        moodist.Queue(pg, location=world + 3)
+    # a queue handle dropped while items sit in it leaves the group usable
+    doomed = moodist.Queue(pg, location=0, name="doomed")
+    if rank == 1:
+        for i in range(10):
+            doomed.put_object(i)
+    dist.barrier()
+    del doomed
+    gc.collect()
+    t = torch.ones(3)
+    dist.all_reduce(t)
+    assert float(t[0]) == world
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_queue_edge_cases_world3():
+    run_ranks(_edges, 3, timeout=240)
