@@ -204,3 +204,44 @@ def _rendezvous(rank, world, port):
 
 def test_moodist_rendezvous_url():
     run_ranks(_rendezvous, 2, timeout=90)
+
+
+def _interop(rank, world, port):
+    """The store under torch's own machinery, and torch's store under the backend."""
+    import torch
+    import torch.distributed as dist
+
+    st = _store(rank, world, port, key="interop", timeout=timedelta(seconds=30))
+    # the Store base class's derived operations work on top of set / get / add
+    st.multi_set([f"m{rank}a", f"m{rank}b"], [b"1", b"2"])
+    assert st.multi_get([f"m{rank}a", f"m{rank}b"]) == [b"1", b"2"]
+    st.append(f"ap{rank}", b"x")
+    st.append(f"ap{rank}", b"y")
+    assert st.get(f"ap{rank}") == b"xy"
+    ps = dist.PrefixStore("pfx", st)
+    ps.set(f"a{rank}", b"1")
+    ps.wait([f"a{r}" for r in range(world)])
+    assert st.get(f"pfx/a{rank}") == b"1"
+    # gloo bootstraps through this store
+    dist.init_process_group("gloo", store=dist.PrefixStore("gloo", st), rank=rank, world_size=world)
+    t = torch.ones(3)
+    dist.all_reduce(t)
+    assert float(t[0]) == world
+    dist.destroy_process_group()
+    # the moodist backend through a PrefixStore of it, then through torch's TCPStore
+    dist.init_process_group("moodist", store=dist.PrefixStore("moo", st), rank=rank, world_size=world)
+    t = torch.ones(3)
+    dist.all_reduce(t)
+    assert float(t[0]) == world
+    dist.destroy_process_group()
+    ts = dist.TCPStore("127.0.0.1", port + 11, world, rank == 0, timeout=timedelta(seconds=30))
+    dist.init_process_group("moodist", store=ts, rank=rank, world_size=world)
+    t = torch.ones(3)
+    dist.all_reduce(t)
+    assert float(t[0]) == world
+    dist.destroy_process_group()
+    _barrier(st, rank, world, "interop-done")
+
+
+def test_store_under_torch_and_torch_store_under_the_backend():
+    run_ranks(_interop, 3, timeout=240)
