@@ -88,6 +88,7 @@ Ref checked(PyObject* o) {
 }
 
 PyObject *s_qualname, *s_module, *s_reduce_ex, *s_dict, *s_setstate, *s_dot, *s_extend, *s_append, *s_five;
+PyObject* g_dispatch_table;  // copyreg.dispatch_table: type -> reducer
 PyObject* g_newobj;  // copyreg.__newobj__, what object.__reduce_ex__(2+) names as the constructor
 
 void init_strings() {
@@ -103,9 +104,11 @@ void init_strings() {
   s_five = PyLong_FromLong(5);
   if (PyObject* copyreg = PyImport_ImportModule("copyreg")) {
     g_newobj = PyObject_GetAttrString(copyreg, "__newobj__");
+    g_dispatch_table = PyObject_GetAttrString(copyreg, "dispatch_table");
+    if (g_dispatch_table && !PyDict_Check(g_dispatch_table)) Py_CLEAR(g_dispatch_table);
     Py_DECREF(copyreg);
   }
-  if (!g_newobj) PyErr_Clear();
+  if (!g_newobj || !g_dispatch_table) PyErr_Clear();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -413,7 +416,42 @@ class Packer {
 
   void pack_global(PyObject* obj) {
     Ref name = checked(PyObject_GetAttr(obj, s_qualname));
-    Ref module = checked(PyObject_GetAttr(obj, s_module));
+    pack_global_named(obj, std::move(name));
+  }
+
+  // `obj` is to be found again as module.name (dotted). Like pickle, check now that the lookup gives this very
+  // object: a lambda, a class made inside a function or an object shadowed by another of the same name would
+  // otherwise serialize fine and fail (or come back as something else) on the receiving side.
+  void pack_global_named(PyObject* obj, Ref name) {
+    Ref module;
+    if (PyObject* m = PyObject_GetAttr(obj, s_module)) {
+      module = Ref(m);
+    } else {
+      PyErr_Clear();
+    }
+    if (!module || module.p == Py_None) {
+      // singletons such as Ellipsis carry no __module__: ask pickle where the name lives
+      Ref pickle_mod = checked(PyImport_ImportModule("pickle"));
+      module = checked(PyObject_CallMethod(pickle_mod.p, "whichmodule", "OO", obj, name.p));
+    }
+    if (!PyUnicode_Check(name.p) || !PyUnicode_Check(module.p)) {
+      PyErr_Format(PyExc_TypeError, "moodist.serialize: %R has a name or module that is not a str", obj);
+      throw PyError{};
+    }
+    bool same = false;
+    if (PyObject* mod = PyImport_Import(module.p)) {
+      Ref cur(mod);
+      Ref parts = checked(PyUnicode_Split(name.p, s_dot, -1));
+      for (Py_ssize_t i = 0; cur && i < PyList_GET_SIZE(parts.p); ++i)
+        cur = Ref(PyObject_GetAttr(cur.p, PyList_GET_ITEM(parts.p, i)));
+      same = cur && cur.p == obj;
+    }
+    if (!same) {
+      PyErr_Clear();
+      PyErr_Format(PyExc_ValueError, "moodist.serialize: cannot serialize %R: it is not what %U.%U names", obj, module.p,
+                   name.p);
+      throw PyError{};
+    }
     byte(T_GLOBAL);
     pack_temp(std::move(name));
     pack_temp(std::move(module));
@@ -428,15 +466,17 @@ class Packer {
   }
 
   void pack_reduce(PyObject* obj) {
-    Ref fn = checked(PyObject_GetAttr(obj, s_reduce_ex));
-    Ref red = checked(PyObject_CallOneArg(fn.p, s_five));
-    if (PyUnicode_Check(red.p)) {  // "this is a global with that name"
-      Ref module = checked(PyObject_GetAttr(obj, s_module));
-      byte(T_GLOBAL);
-      pack_temp(std::move(red));
-      pack_temp(std::move(module));
-      return;
+    Ref red;
+    // a reducer registered with copyreg.pickle() comes first, as in pickle (re.Pattern is served that way)
+    PyObject* registered = g_dispatch_table ? PyDict_GetItemWithError(g_dispatch_table, (PyObject*)Py_TYPE(obj)) : nullptr;
+    if (registered) {
+      red = checked(PyObject_CallOneArg(registered, obj));
+    } else {
+      if (PyErr_Occurred()) throw PyError{};
+      Ref fn = checked(PyObject_GetAttr(obj, s_reduce_ex));
+      red = checked(PyObject_CallOneArg(fn.p, s_five));
     }
+    if (PyUnicode_Check(red.p)) return pack_global_named(obj, std::move(red));  // "a global of that name"
     if (!PyTuple_Check(red.p)) {
       PyErr_Format(PyExc_TypeError, "moodist.serialize: %s.__reduce__ must return a tuple or str", Py_TYPE(obj)->tp_name);
       throw PyError{};

@@ -3,6 +3,8 @@ the reference's tests/test_serialize.py (every tag, big ints, special floats, UC
 circular references, functions, types, custom __reduce__, numpy arrays)."""
 
 import collections
+import dataclasses
+import enum
 import math
 import struct
 
@@ -140,6 +142,78 @@ def test_functions_types_and_objects():
     dq = collections.deque([1, 2, 3], maxlen=5)
     r = roundtrip(dq)
     assert r == dq and r.maxlen == 5
+
+
+class Colour(enum.Enum):
+    RED = 1
+    BLUE = 2
+
+
+@dataclasses.dataclass(frozen=True, slots=True)
+class FrozenRecord:
+    x: int
+    y: str
+
+
+class KeepsOnlyX:
+    def __init__(self):
+        self.x, self.cache = 1, "computed"
+
+    def __getstate__(self):
+        return {"x": self.x}
+
+    def __setstate__(self, state):
+        self.x, self.cache = state["x"], "rebuilt"
+
+
+Pair = collections.namedtuple("Pair", "a b")
+
+
+def test_standard_library_objects_follow_pickle():
+    """Objects whose way back is described by __reduce_ex__, __getstate__, copyreg or a bare global name."""
+    import datetime
+    import decimal
+    import fractions
+    import functools
+    import pathlib
+    import re
+    import uuid
+
+    plain = [
+        Colour.BLUE, FrozenRecord(3, "z"), Pair(1, Pair(2, 3)),
+        datetime.datetime(2024, 1, 2, 3, 4, 5, 6), datetime.date(2020, 2, 29), datetime.timedelta(days=1, microseconds=5),
+        datetime.timezone.utc, decimal.Decimal("1.2345"), fractions.Fraction(3, 7), 1 + 2j,
+        pathlib.PurePosixPath("/a/b"), uuid.UUID(int=5), range(1, 10, 2), slice(1, 2, 3),
+        collections.Counter("hello"), frozenset({(1, 2), (3, 4)}), 2**200, -(2**200),
+    ]
+    for obj in plain:
+        back = roundtrip(obj)
+        assert back == obj and type(back) is type(obj), obj
+    assert roundtrip(Colour.RED) is Colour.RED
+    # singletons that pickle stores as a bare name; they have no __module__ of their own
+    assert roundtrip([Ellipsis, NotImplemented]) == [Ellipsis, NotImplemented]
+    # a reducer registered through copyreg (how compiled regular expressions travel)
+    pattern = roundtrip(re.compile(r"a+b", re.I))
+    assert pattern.pattern == "a+b" and pattern.flags == re.compile(r"a+b", re.I).flags and pattern.match("AAB")
+    part = roundtrip(functools.partial(int, base=2))
+    assert part("101") == 5
+    state = roundtrip(KeepsOnlyX())
+    assert state.x == 1 and state.cache == "rebuilt"
+
+
+def test_objects_that_cannot_be_found_again_are_refused_when_serializing():
+    """A lambda or a class made inside a function has no importable name: like pickle, say so on the sending
+    side instead of failing on the receiving one."""
+
+    class Local:
+        pass
+
+    for obj in (lambda x: x, Local, Local()):
+        with pytest.raises(ValueError, match="cannot serialize"):
+            moodist.serialize(obj)
+    for obj in ((i for i in range(3)), collections, open(__file__)):
+        with pytest.raises(TypeError):
+            moodist.serialize(obj)
 
 
 def test_numpy_and_torch_payloads():
