@@ -123,3 +123,71 @@ def _planner_body(rank, world, port):
 def test_planner_pieces_are_2d():
     """Row -> column reshard of a [8, 8] tensor over 2 ranks: one strided piece per source."""
     run_ranks(_planner_body, 2, timeout=60)
+
+
+def _dtensors_and_errors(rank, world, port):
+    dist = init_moodist(rank, world, port)
+    import moodist_b200 as moodist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Replicate, Shard, distribute_tensor
+
+    pg = moodist.get_backend(device="cpu")
+    mesh = init_device_mesh("cpu", (world,))
+    full = torch.arange(10 * 6, dtype=torch.float32).view(10, 6)  # 10 rows over 4 ranks: 3, 3, 3, 1
+
+    # DTensors say where this rank's box lies; shape and dtype come from them
+    src = distribute_tensor(full, mesh, [Shard(0)])
+    dst = distribute_tensor(torch.zeros_like(full), mesh, [Shard(1)])
+    op = moodist.compile_op(pg, inputs=[src], outputs=[dst])
+    out = torch.empty_like(dst.to_local())
+    op([src.to_local().contiguous()], [out]).wait()
+    assert torch.equal(out, distribute_tensor(full, mesh, [Shard(1)]).to_local())
+
+    whole = distribute_tensor(torch.zeros_like(full), mesh, [Replicate()])
+    op = moodist.compile_op(pg, inputs=[src], outputs=[whole])
+    out = torch.empty(10, 6)
+    op([src.to_local().contiguous()], [out]).wait()
+    assert torch.equal(out, full)
+
+    # blocks of a 2-D mesh -> rows of a 1-D mesh
+    mesh2 = init_device_mesh("cpu", (2, world // 2))
+    big = torch.arange(8 * 12, dtype=torch.float32).view(8, 12)
+    blocks = distribute_tensor(big, mesh2, [Shard(0), Shard(1)])
+    rows = distribute_tensor(torch.zeros_like(big), mesh, [Shard(0)])
+    op = moodist.compile_op(pg, inputs=[blocks], outputs=[rows])
+    out = torch.empty_like(rows.to_local())
+    op([blocks.to_local().contiguous()], [out]).wait()
+    assert torch.equal(out, distribute_tensor(big, mesh, [Shard(0)]).to_local())
+
+    # malformed descriptions raise on the calling rank, before the collective part
+    f32 = torch.float32
+    bad_calls = [
+        (dict(shape=(4, 4), dtype=f32, inputs=[{"offset": [0, 0]}]), ValueError),
+        (dict(shape=(4, 4), dtype=f32, inputs=[{"offset": [0], "shape": [4, 4]}]), ValueError),
+        (dict(shape=(4, 4), dtype=f32, inputs=[{"offset": [0, 0.5], "shape": [4, 4]}]), TypeError),
+        (dict(shape=(4, 4), dtype="float32", inputs=None), TypeError),
+        (dict(dtype=f32, inputs=None), ValueError),
+        (dict(shape=(4, 4), dtype=f32, inputs={"offset": [0, 0], "shape": [4, 4]}), TypeError),
+    ]
+    for kwargs, exc in bad_calls:
+        with pytest.raises(exc, match="compile_op"):
+            moodist.compile_op(pg, **kwargs)
+    with pytest.raises(RuntimeError, match="exceeds the global shape"):
+        moodist.compile_op(pg, shape=(4, 4), dtype=f32, inputs=[{"offset": [2, 0], "shape": [4, 4]}], outputs=None)
+
+    # tensors that do not fit the compiled op are refused at call time and the op stays usable
+    op = moodist.compile_op(pg, shape=(world * 2, 4), dtype=f32, inputs=[{"offset": [rank * 2, 0], "shape": [2, 4]}],
+                            outputs=[{"offset": [0, 0], "shape": [world * 2, 4]}])
+    with pytest.raises(RuntimeError, match="elements"):
+        op([torch.zeros(3, 4)], [torch.empty(world * 2, 4)]).wait()
+    with pytest.raises(RuntimeError, match="dtype"):
+        op([torch.zeros(2, 4, dtype=torch.float64)], [torch.empty(world * 2, 4)]).wait()
+    out = torch.empty(world * 2, 4)
+    op([torch.full((2, 4), float(rank))], [out]).wait()
+    assert out[::2, 0].tolist() == [float(r) for r in range(world)]
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_compile_op_dtensors_and_argument_errors_world4():
+    run_ranks(_dtensors_and_errors, 4, timeout=240)
