@@ -40,6 +40,29 @@ struct Waiter {
   }
 };
 
+// Uninitialised bytes that only ever receive data: growing one neither copies the old contents nor fills
+// the new ones, which for a gigabyte costs more than the transfer it is for.
+struct Scratch {
+  uint8_t* mem = nullptr;
+  size_t capacity = 0;
+  Scratch() = default;
+  Scratch(const Scratch&) = delete;
+  Scratch& operator=(const Scratch&) = delete;
+  ~Scratch() { free(mem); }
+  void reserve(size_t bytes) {
+    if (bytes <= capacity) return;
+    free(mem);
+    mem = static_cast<uint8_t*>(malloc(bytes));
+    capacity = mem ? bytes : 0;
+    if (!mem) fail("moodist: out of memory for a receive buffer of " + std::to_string(bytes) + " bytes");
+  }
+  uint8_t* data() { return mem; }
+};
+struct ScratchPool {
+  std::mutex mu;
+  std::vector<std::unique_ptr<Scratch>> free;
+};
+
 struct Announce {
   uint64_t addr = 0;
   uint32_t key = 0;
@@ -178,28 +201,27 @@ class HostGroupImpl final : public HostGroup {
   // Receive / intermediate buffers of the collectives: reused across calls (a fresh multi-megabyte vector per
   // call costs its zero-fill and a page fault per 4 KiB). The buffer goes back to the pool when the last
   // reference (the call, or a completion still running on the engine thread) lets go of it.
-  std::shared_ptr<Bytes> scratch(size_t bytes) {
-    std::unique_ptr<Bytes> buf;
+  std::shared_ptr<Scratch> scratch(size_t bytes) {
+    std::unique_ptr<Scratch> buf;
     std::shared_ptr<ScratchPool> pool = scratch_pool_;  // the deleter keeps the pool alive, not the group
     {
       std::lock_guard<std::mutex> lk(pool->mu);
       auto& free = pool->free;
-      for (size_t i = 0; i < free.size(); ++i) {
-        if (free[i]->size() >= bytes) {
-          buf = std::move(free[i]);
-          free.erase(free.begin() + i);
-          break;
-        }
-      }
-      if (!buf && !free.empty()) {  // all too small: let one of them grow instead of keeping both
+      size_t best = free.size();
+      for (size_t i = 0; i < free.size(); ++i)  // smallest buffer that is large enough
+        if (free[i]->capacity >= bytes && (best == free.size() || free[i]->capacity < free[best]->capacity)) best = i;
+      if (best != free.size()) {
+        buf = std::move(free[best]);
+        free.erase(free.begin() + best);
+      } else if (!free.empty()) {  // all too small: replace one of them instead of keeping both
         buf = std::move(free.back());
         free.pop_back();
       }
     }
-    if (!buf) buf = std::make_unique<Bytes>();
-    if (buf->size() < bytes) buf->resize(bytes);
-    Bytes* raw = buf.release();
-    return std::shared_ptr<Bytes>(raw, [pool](Bytes* b) {
+    if (!buf) buf = std::make_unique<Scratch>();
+    buf->reserve(bytes);
+    Scratch* raw = buf.release();
+    return std::shared_ptr<Scratch>(raw, [pool](Scratch* b) {
       std::lock_guard<std::mutex> lk(pool->mu);
       if (pool->free.size() < 4)
         pool->free.emplace_back(b);
@@ -244,19 +266,39 @@ class HostGroupImpl final : public HostGroup {
       cpu_reduce(out, srcs, 1, count, dtype, op, premul, op == kRedPremulSum);
       return;
     }
-    size_t chunk = (count + world_ - 1) / world_;
-    size_t padded = chunk * world_;
-    if (padded == count) {
-      auto mine = scratch(chunk * esz);
-      reduce_scatter(in, mine->data(), chunk, dtype, op, premul);
-      all_gather(mine->data(), out, chunk * esz);
+    // Whole multiples of the world size run in place: each rank reduces its slice straight into the output and
+    // the slices are then gathered where they lie. (A peer reads slice p of this rank's input only during the
+    // reduce-scatter, which ends when those reads are acknowledged, and slice p is overwritten only by what that
+    // same peer sends afterwards, so input and output may be one buffer.) The few elements left over of a large
+    // tensor take a padded round of their own.
+    const uint8_t* x = static_cast<const uint8_t*>(in);
+    uint8_t* o = static_cast<uint8_t*>(out);
+    size_t chunk = count / world_;
+    size_t body = chunk * world_;
+    if (body != count && count * esz <= (1u << 20)) {
+      // small and not divisible: one padded round costs less than a second round for the remainder
+      size_t per = chunk + 1;
+      Bytes pin(per * world_ * esz, 0), pout(per * world_ * esz), mine(per * esz);
+      memcpy(pin.data(), x, count * esz);
+      reduce_scatter(pin.data(), mine.data(), per, dtype, op, premul);
+      all_gather(mine.data(), pout.data(), per * esz);
+      memcpy(o, pout.data(), count * esz);
       return;
     }
-    Bytes pin(padded * esz, 0), pout(padded * esz), mine(chunk * esz);
-    memcpy(pin.data(), in, count * esz);
-    reduce_scatter(pin.data(), mine.data(), chunk, dtype, op, premul);
-    all_gather(mine.data(), pout.data(), chunk * esz);
-    memcpy(out, pout.data(), count * esz);
+    if (chunk) {
+      uint8_t* mine = o + (size_t)rank_ * chunk * esz;
+      reduce_scatter(x, mine, chunk, dtype, op, premul);
+      all_gather(mine, o, chunk * esz);
+    }
+    size_t tail = count - body;
+    if (tail) {
+      // one element per rank, the first `tail` of them real; what the padding reduces to is never read
+      Bytes pin((size_t)world_ * esz, 0), pout((size_t)world_ * esz), one(esz);
+      memcpy(pin.data(), x + body * esz, tail * esz);
+      reduce_scatter(pin.data(), one.data(), 1, dtype, op, premul);
+      all_gather(one.data(), pout.data(), esz);
+      memcpy(o + body * esz, pout.data(), tail * esz);
+    }
   }
 
   void broadcast(void* data, size_t bytes, int root) override {
@@ -844,10 +886,6 @@ class HostGroupImpl final : public HostGroup {
   TcpTransport transport_;
   uint64_t probe_word_ = 0;  // same-machine peers read this word to find out whether they may read this process
   int direct_peers_ = 0;     // peers whose memory this rank reads directly (engine thread)
-  struct ScratchPool {
-    std::mutex mu;
-    std::vector<std::unique_ptr<Bytes>> free;
-  };
   std::shared_ptr<ScratchPool> scratch_pool_ = std::make_shared<ScratchPool>();
   std::thread thread_;
   std::atomic<bool> stop_{false}, mesh_ready_{false}, error_state_{false}, busy_{false}, shutdown_started_{false};

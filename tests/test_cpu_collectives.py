@@ -81,6 +81,15 @@ def _odd_sizes(rank, world, port):
         t = full[rank].clone()
         dist.all_reduce(t)
         torch.testing.assert_close(t, full.sum(0), rtol=1e-5, atol=1e-5)
+    # above 1 MiB a count that the world does not divide runs as an in-place body plus a round for the remainder
+    for n in ((1 << 19) + 1, 3 * (1 << 18) + world - 1):
+        full = _full(world, n, torch.float32, seed=n)
+        t = full[rank].clone()
+        dist.all_reduce(t, op=dist.ReduceOp.AVG)
+        torch.testing.assert_close(t, full.mean(0), rtol=1e-5, atol=1e-6)
+        big = torch.full((n,), rank + 1, dtype=torch.int64)
+        dist.all_reduce(big, op=dist.ReduceOp.MAX)
+        assert int(big[0]) == world and int(big[-1]) == world
     for i in range(100):  # back to back, mixed
         t = torch.full((16,), float(rank + i))
         dist.all_reduce(t)
@@ -90,8 +99,9 @@ def _odd_sizes(rank, world, port):
     dist.destroy_process_group()
 
 
-def test_cpu_odd_sizes_and_stress():
-    run_ranks(_odd_sizes, 2, timeout=120)
+@pytest.mark.parametrize("world", [2, 3])
+def test_cpu_odd_sizes_and_stress(world):
+    run_ranks(_odd_sizes, world, timeout=180)
 
 
 def _send_recv(rank, world, port):
