@@ -371,19 +371,29 @@ class HostGroupImpl final : public HostGroup {
   }
 
   void send(const void* data, size_t bytes, int dst, uint32_t tag) override {
+    // the payload travels inside one framed message, whose length field has 32 bits
+    if (bytes > 0xfff00000ull) fail("moodist: send: one message carries at most 4 GiB - 1 MiB; split the tensor");
     Writer wr;
     wr(tag, (uint64_t)bytes);
     wr.raw(data, bytes);
     send_message(dst, kOpSendRecv, std::move(wr.out));
   }
 
-  void recv(void* data, size_t bytes, int src, uint32_t tag) override {
+  void recv(void* data, size_t bytes, int src, uint32_t tag) override { recv_wait(recv_post(data, bytes, src, tag, nullptr)); }
+
+  std::shared_ptr<void> recv_post(void* data, size_t bytes, int src, uint32_t tag, std::shared_ptr<void> keep) override {
     auto waiter = std::make_shared<Waiter>();
     run_on_engine([=, this] {
-      pending_recvs_.push_back(PendingRecv{src, tag, data, bytes, waiter});
+      pending_recvs_.push_back(PendingRecv{src, tag, data, bytes, waiter, keep});
       match_recvs();
     });
-    wait(*waiter, "recv");
+    return waiter;
+  }
+
+  void recv_wait(const std::shared_ptr<void>& posted) override { wait(*std::static_pointer_cast<Waiter>(posted), "recv"); }
+
+  bool recv_done(const std::shared_ptr<void>& posted) override {
+    return std::static_pointer_cast<Waiter>(posted)->done_hint.load(std::memory_order_acquire);
   }
 
   // ---------------------------------------------------------------------------------------------
@@ -524,6 +534,7 @@ class HostGroupImpl final : public HostGroup {
     void* data;
     size_t bytes;
     std::shared_ptr<Waiter> waiter;
+    std::shared_ptr<void> keep;  // whatever owns `data`
   };
 
   void check_op(int op, int dtype) {

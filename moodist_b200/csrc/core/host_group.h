@@ -81,6 +81,12 @@ class HostGroup {
   virtual void barrier() = 0;
   virtual void send(const void* data, size_t bytes, int dst, uint32_t tag) = 0;
   virtual void recv(void* data, size_t bytes, int src, uint32_t tag) = 0;
+  // The receive in two steps: recv_post() files the request and returns at once (requests from one source with one
+  // tag are served in the order they were posted; `keep` is held until the data has landed, so the destination
+  // cannot go away under it), recv_wait() blocks until it is served and raises what went wrong.
+  virtual std::shared_ptr<void> recv_post(void* data, size_t bytes, int src, uint32_t tag, std::shared_ptr<void> keep) = 0;
+  virtual void recv_wait(const std::shared_ptr<void>& posted) = 0;
+  virtual bool recv_done(const std::shared_ptr<void>& posted) = 0;
 
   // ---- two-sided engine messages for subsystems layered on top (Queue, compile_op) ----
   using Handler = std::function<void(int src, Reader& body)>;  // runs on the engine thread

@@ -163,6 +163,7 @@ void Conn::send_ref(const void* p, size_t n, std::shared_ptr<void> keep, std::fu
 }
 
 void Conn::send_frame(const Bytes& body) {
+  if (body.size() > 0xffffff00ull) fail("net: a frame carries at most 4 GiB, not " + std::to_string(body.size()) + " bytes");
   Bytes f(8 + body.size());
   uint32_t sig = kFrameSig, n = (uint32_t)body.size();
   memcpy(f.data(), &sig, 4);

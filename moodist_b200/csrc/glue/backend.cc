@@ -15,6 +15,14 @@
 #include "core/log.h"
 #include "kernels/kernels_api.h"
 
+// core errors become torch errors at the boundary
+#define MOODIST_TRANSLATE(body)                 \
+  try {                                         \
+    body                                        \
+  } catch (const moodist::Error& e) {           \
+    TORCH_CHECK(false, e.what());               \
+  }
+
 namespace moodist {
 namespace {
 
@@ -64,6 +72,50 @@ class DoneWork final : public c10d::Work {
 
  private:
   std::vector<at::Tensor> outputs_;
+  c10::intrusive_ptr<at::ivalue::Future> future_;
+};
+
+// A receive that has been posted and is completed by wait(): the message is matched in posting order whatever the
+// order of the waits, so a rank may post its receives first and send afterwards (pipelines and rings do) without
+// every rank sitting in a receive that nobody has sent to yet. `after` runs once, inside wait(), when the host
+// part has arrived (the device part of a CUDA receive).
+class RecvWork final : public c10d::Work {
+ public:
+  RecvWork(int rank, std::vector<at::Tensor> outputs, c10::intrusive_ptr<MoodistBackend> owner,
+           std::shared_ptr<void> posted, std::function<void()> after)
+      : c10d::Work(rank, c10d::OpType::RECV), outputs_(std::move(outputs)), owner_(std::move(owner)),
+        posted_(std::move(posted)), after_(std::move(after)) {
+    future_ = c10::make_intrusive<at::ivalue::Future>(c10::ListType::create(c10::TensorType::get()));
+  }
+  bool isCompleted() override {
+    std::lock_guard<std::mutex> lk(mu_);
+    return done_ || (!after_ && owner_->hostGroup().recv_done(posted_));
+  }
+  bool isSuccess() const override { return true; }
+  bool wait(std::chrono::milliseconds) override {
+    std::lock_guard<std::mutex> lk(mu_);
+    if (done_) return true;
+    MOODIST_TRANSLATE(owner_->hostGroup().recv_wait(posted_);)
+    if (after_) {
+      auto f = std::move(after_);
+      after_ = nullptr;
+      f();
+    }
+    done_ = true;
+    future_->markCompleted(at::IValue(outputs_));
+    return true;
+  }
+  void synchronize() override { wait(std::chrono::milliseconds(0)); }
+  std::vector<at::Tensor> result() override { return outputs_; }
+  c10::intrusive_ptr<c10::ivalue::Future> getFuture() override { return future_; }
+
+ private:
+  std::mutex mu_;
+  bool done_ = false;
+  std::vector<at::Tensor> outputs_;
+  c10::intrusive_ptr<MoodistBackend> owner_;
+  std::shared_ptr<void> posted_;
+  std::function<void()> after_;
   c10::intrusive_ptr<at::ivalue::Future> future_;
 };
 
@@ -128,13 +180,6 @@ std::string random_name() {
 CUstream_st* raw(const c10::cuda::CUDAStream& s) { return reinterpret_cast<CUstream_st*>(s.stream()); }
 
 }  // namespace
-
-#define MOODIST_TRANSLATE(body)                 \
-  try {                                         \
-    body                                        \
-  } catch (const moodist::Error& e) {           \
-    TORCH_CHECK(false, e.what());               \
-  }
 
 namespace {
 std::mutex g_registry_mu;
@@ -647,24 +692,39 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::recv(std::vector<at::Tensor>& ten
   TORCH_CHECK(srcRank >= 0 && srcRank < size_ && srcRank != rank_, "moodist: recv: bad source rank ", srcRank);
   at::Tensor t = tensors[0];
   check_contig(t, "recv tensor");
+  auto self = c10::intrusive_ptr<MoodistBackend>::unsafe_reclaim_from_nonowning(this);
   if (t.is_cuda()) {
     if (CudaP2P* p2p = cudaP2P(t.get_device())) {
-      // the host waits for the descriptor only (the sender posts it when it calls send, whatever its stream is
-      // still busy with); the data follows in stream order on this rank's current stream
-      c10::cuda::CUDAGuard guard(t.device());
-      auto stream = c10::cuda::getCurrentCUDAStream();
-      CudaItemDescriptor d;
-      MOODIST_TRANSLATE(hostGroup().recv(&d, sizeof(d), srcRank, (uint32_t)tag ^ kCudaTagBit);)
-      TORCH_CHECK(d.magic == kCudaItemMagic && d.bytes == (uint64_t)t.nbytes(), "moodist: recv: the sender's tensor has ",
-                  d.bytes, " bytes, this one ", t.nbytes());
-      MOODIST_TRANSLATE(p2p->fetch(d, t.data_ptr(), stream.stream());)
-      return c10::make_intrusive<CudaWork>(rank_, c10d::OpType::RECV, tensors, stream);
+      // The host part is the descriptor only (the sender posts it when it calls send, whatever its stream is still
+      // busy with); once wait() has it, the data follows in stream order on the stream that was current here.
+      auto stream = c10::cuda::getCurrentCUDAStream(t.get_device());
+      auto d = std::make_shared<CudaItemDescriptor>();
+      std::shared_ptr<void> posted;
+      MOODIST_TRANSLATE(posted = hostGroup().recv_post(d.get(), sizeof(*d), srcRank, (uint32_t)tag ^ kCudaTagBit, d);)
+      auto after = [p2p, d, t, stream]() {
+        c10::cuda::CUDAGuard guard(t.device());
+        TORCH_CHECK(d->magic == kCudaItemMagic && d->bytes == (uint64_t)t.nbytes(), "moodist: recv: the sender's tensor has ",
+                    d->bytes, " bytes, this one ", t.nbytes());
+        MOODIST_TRANSLATE(p2p->fetch(*d, t.data_ptr(), stream.stream());)
+        // whoever waits may be on another stream: order it behind the copy
+        at::cuda::CUDAEvent landed;
+        landed.record(stream);
+        landed.block(c10::cuda::getCurrentCUDAStream(t.get_device()));
+      };
+      return c10::make_intrusive<RecvWork>(rank_, tensors, self, posted, after);
     }
+    // no device path between the two ranks yet: through pinned host memory
+    at::Tensor host = at::empty(t.sizes(), t.options().device(at::kCPU).pinned_memory(true));
+    std::shared_ptr<void> posted;
+    MOODIST_TRANSLATE(posted = hostGroup().recv_post(host.data_ptr(), (size_t)host.nbytes(), srcRank, (uint32_t)tag,
+                                                     std::make_shared<at::Tensor>(host));)
+    auto after = [t, host]() mutable { t.copy_(host); };  // blocking copy: `host` may be released afterwards
+    return c10::make_intrusive<RecvWork>(rank_, tensors, self, posted, after);
   }
-  at::Tensor host = t.is_cuda() ? at::empty(t.sizes(), t.options().device(at::kCPU).pinned_memory(true)) : t;
-  MOODIST_TRANSLATE(hostGroup().recv(host.data_ptr(), (size_t)host.nbytes(), srcRank, (uint32_t)tag);)
-  if (t.is_cuda()) t.copy_(host);  // blocking copy from pinned memory: `host` may be released afterwards
-  return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::RECV, tensors);
+  std::shared_ptr<void> posted;
+  MOODIST_TRANSLATE(posted = hostGroup().recv_post(t.data_ptr(), (size_t)t.nbytes(), srcRank, (uint32_t)tag,
+                                                   std::make_shared<at::Tensor>(t));)
+  return c10::make_intrusive<RecvWork>(rank_, tensors, self, posted, nullptr);
 }
 
 void MoodistBackend::cudaBarrier() {

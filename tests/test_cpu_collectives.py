@@ -135,3 +135,46 @@ def _send_recv(rank, world, port):
 def test_send_recv_ring():
     run_ranks(_send_recv, 2, timeout=120)
     run_ranks(_send_recv, 4, timeout=120)
+
+
+def _receive_first(rank, world, port):
+    dist = init_moodist(rank, world, port)
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    # a ring in which every rank posts its receive before its send: irecv must not block
+    got, mine = torch.empty(1000), torch.full((1000,), float(rank))
+    for w in dist.batch_isend_irecv([dist.P2POp(dist.irecv, got, prv), dist.P2POp(dist.isend, mine, nxt)]):
+        w.wait()
+    assert bool((got == prv).all())
+    # two receives from one source with one tag: the order they were posted in decides, not the order of the waits
+    if rank == 0:
+        dist.send(torch.full((4,), 1.0), 1, tag=5)
+        dist.send(torch.full((4,), 2.0), 1, tag=5)
+    if rank == 1:
+        first, second = torch.empty(4), torch.empty(4)
+        w1 = dist.irecv(first, 0, tag=5)
+        w2 = dist.irecv(second, 0, tag=5)
+        w2.wait()
+        w1.wait()
+        assert float(first[0]) == 1.0 and float(second[0]) == 2.0 and w1.is_completed()
+    # a posted receive whose handle was dropped still has somewhere to put its message
+    if rank == 1:
+        w = dist.irecv(torch.empty(4), 0, tag=9)
+        del w
+    dist.barrier()
+    if rank == 0:
+        dist.send(torch.ones(4), 1, tag=9)
+    dist.barrier()
+    # a message of another size is an error on the receiver, and the group stays usable
+    if rank == 0:
+        dist.send(torch.ones(3), 1, tag=11)
+    if rank == 1:
+        with pytest.raises(RuntimeError, match="size mismatch"):
+            dist.recv(torch.empty(5), 0, tag=11)
+    t = torch.ones(2)
+    dist.all_reduce(t)
+    assert float(t[0]) == world
+    dist.destroy_process_group()
+
+
+def test_receives_posted_before_sends():
+    run_ranks(_receive_first, 3, timeout=120)
