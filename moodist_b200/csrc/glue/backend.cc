@@ -211,6 +211,11 @@ MoodistBackend::MoodistBackend(const c10::intrusive_ptr<c10d::Store>& store, int
     name_ = kv_->get_str("moodist_pg_key");
   }
   opts_.prefer_kernel_less = g_default_prefer_kernel_less.load();
+  // The host engine comes up here, while every rank is inside the (ordered, collective) construction of this
+  // group. Left to the first operation, two groups first used from two threads would exchange their addresses
+  // through the shared store at the same time, each thread waiting in the store for a key that the other rank's
+  // blocked thread has yet to write.
+  MOODIST_TRANSLATE(host_ = HostGroup::create(*kv_, name_, rank_, size_);)
   std::lock_guard<std::mutex> lk(g_registry_mu);
   registry()[name_] = this;
 }

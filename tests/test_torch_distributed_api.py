@@ -246,3 +246,40 @@ def _wrappers(rank, world, port):
 
 def test_torch_parallel_wrappers_over_the_backend_world2():
     run_ranks(_wrappers, 2, timeout=240)
+
+
+def _threads(rank, world, port):
+    """Three groups over the same ranks, each driven by its own thread from its very first operation on."""
+    import threading
+
+    dist = init_moodist(rank, world, port)
+    g1 = dist.new_group(ranks=list(range(world)))
+    g2 = dist.new_group(ranks=list(range(world)))
+    errors = []
+
+    def loop(group, base):
+        try:
+            for i in range(200):
+                t = torch.full((257,), float(base + i + rank))
+                dist.all_reduce(t, group=group)
+                want = sum(base + i + r for r in range(world))
+                assert float(t[0]) == want and float(t[-1]) == want
+                out = torch.empty(world * 33)
+                dist.all_gather_into_tensor(out, torch.full((33,), float(rank + i)), group=group)
+                assert float(out[33 * (world - 1)]) == world - 1 + i
+        except Exception as e:  # reported by the main thread
+            errors.append(repr(e))
+
+    workers = [threading.Thread(target=loop, args=(g1, 0)), threading.Thread(target=loop, args=(g2, 1000))]
+    for t in workers:
+        t.start()
+    loop(None, 5000)  # the default group, from the main thread, at the same time
+    for t in workers:
+        t.join()
+    assert not errors, errors[:2]
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_groups_driven_from_separate_threads_world3():
+    run_ranks(_threads, 3, timeout=240)
