@@ -19,8 +19,10 @@
 #include "core/cpu_allocator.h"
 #include "core/compile_plan.h"
 #include "core/cpu_reduce.h"
+#include "core/host_group.h"
 #include "core/log.h"
 #include "core/numa.h"
+#include "core/queue.h"
 #include "core/topology.h"
 #include "core/setup_comms.h"
 #include "core/store.h"
@@ -438,7 +440,91 @@ static void test_heap_request() {
   close(ls);
 }
 
+// The host engine with its ranks as threads of this process: every collective against what the ranks can work out
+// themselves, receives posted before the sends of a ring, and a queue fed by every rank. (Run under the thread
+// sanitizer this is where the engine thread, the callers and the completion flags meet.)
+static void test_host_group(int world) {
+  MemStore store;
+  std::vector<std::thread> ranks;
+  for (int r = 0; r < world; ++r) {
+    ranks.emplace_back([&, r] {
+      try {
+        auto g = HostGroup::create(store, "selftest-host-group-" + std::to_string(world), r, world);
+        auto queues = QueueManager::create(*g);
+        // all_reduce: divisible, small with a remainder (padded round), large with a remainder (in place + tail)
+        for (size_t n : {(size_t)world * 64, (size_t)1000 + 1, (size_t)(300 << 10) + (size_t)world - 1}) {
+          std::vector<float> x(n);
+          for (size_t i = 0; i < n; ++i) x[i] = (float)((i % 13) + r);
+          g->all_reduce(x.data(), x.data(), n, kDtF32, kRedSum, 1.0);
+          bool ok = true;
+          for (size_t i = 0; i < n; ++i) ok = ok && x[i] == (float)(world * (i % 13) + world * (world - 1) / 2);
+          CHECK(ok);
+        }
+        // all_gather / reduce_scatter (average) / broadcast
+        std::vector<int32_t> mine(257, r), all((size_t)257 * world, -1);
+        g->all_gather(mine.data(), all.data(), mine.size() * 4);
+        for (int p = 0; p < world; ++p) CHECK(all[(size_t)p * 257] == p && all[(size_t)p * 257 + 256] == p);
+        std::vector<double> in((size_t)world * 5), out(5);
+        for (size_t i = 0; i < in.size(); ++i) in[i] = (double)(r + 1) * (double)(i / 5 + 1);
+        g->reduce_scatter(in.data(), out.data(), 5, kDtF64, kRedAvg, 1.0);
+        CHECK(std::fabs(out[0] - (double)(r + 1) * (world + 1) / 2.0) < 1e-9);
+        std::vector<uint8_t> b(3000, (uint8_t)r);
+        g->broadcast(b.data(), b.size(), world - 1);
+        CHECK(b[0] == world - 1 && b[2999] == world - 1);
+        // uneven all_to_all: rank s sends (s + d + 1) bytes to rank d
+        std::vector<uint64_t> so(world), sb(world), ro(world), rb(world);
+        uint64_t soff = 0, roff = 0;
+        for (int d = 0; d < world; ++d) {
+          so[d] = soff, sb[d] = (uint64_t)(r + d + 1), soff += sb[d];
+          ro[d] = roff, rb[d] = (uint64_t)(d + r + 1), roff += rb[d];
+        }
+        std::vector<uint8_t> sendbuf(soff), recvbuf(roff, 0xee);
+        for (int d = 0; d < world; ++d) std::fill(sendbuf.begin() + so[d], sendbuf.begin() + so[d] + sb[d], (uint8_t)(16 * r + d));
+        g->all_to_all(sendbuf.data(), recvbuf.data(), so.data(), sb.data(), ro.data(), rb.data());
+        for (int s2 = 0; s2 < world; ++s2) CHECK(recvbuf[ro[s2]] == (uint8_t)(16 * s2 + r) && recvbuf[ro[s2] + rb[s2] - 1] == (uint8_t)(16 * s2 + r));
+        // a ring whose receives are posted first
+        if (world > 1) {
+          int nxt = (r + 1) % world, prv = (r + world - 1) % world;
+          std::vector<int64_t> got(100, -1), give(100, r);
+          auto posted = g->recv_post(got.data(), got.size() * 8, prv, 7, nullptr);
+          g->send(give.data(), give.size() * 8, nxt, 7);
+          g->recv_wait(posted);
+          CHECK(g->recv_done(posted) && got[0] == prv && got[99] == prv);
+        }
+        // everybody puts into a queue that lives on rank 0
+        auto q = queues->make_queue({0}, false, std::string("selftest"));
+        int64_t item[4] = {r, r, r, r};
+        q->put(item, sizeof(item), 4, {4}, 0, nullptr)->wait();
+        if (r == 0) {
+          int64_t sum = 0;
+          for (int i = 0; i < world; ++i) {
+            auto it = q->get(true, 30.0, nullptr);
+            CHECK(it.has_value() && it->data.size() == sizeof(item));
+            if (it) {
+              int64_t v;
+              memcpy(&v, it->data.data(), 8);
+              sum += v;
+            }
+          }
+          CHECK(sum == (int64_t)world * (world - 1) / 2);
+        }
+        g->barrier();
+        q.reset();
+        queues.reset();
+        g->shutdown();
+      } catch (const std::exception& e) {
+        fprintf(stderr, "host group rank %d of %d: %s\n", r, world, e.what());
+        ++failures;
+      }
+    });
+  }
+  for (auto& t : ranks) t.join();
+}
+
 int main() {
+  test_host_group(1);
+  test_host_group(2);
+  test_host_group(4);
   test_heap_request();
   test_wire();
   test_planner_random();
