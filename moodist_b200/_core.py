@@ -34,6 +34,14 @@ TcpStore = getattr(_C, "TcpStore", None)
 cuda_copy = _C.cuda_copy
 set_prefer_kernel_less = _C.set_prefer_kernel_less
 
+# Stores that are still alive when the interpreter exits (held by a reference cycle, a module global, an exception's
+# traceback) leave through the coordinated shutdown all the same: a rank that just disappears takes the answers
+# it had queued for its peers with it.
+if hasattr(_C, "_shutdown_all_stores"):
+    import atexit
+
+    atexit.register(_C._shutdown_all_stores)
+
 _serialize = _load("_serialize")
 
 

@@ -3,6 +3,7 @@
 #include <pthread.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <atomic>
 #include <condition_variable>
 #include <cstring>
@@ -993,9 +994,37 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
 
 }  // namespace
 
+namespace {
+std::mutex g_live_mu;
+std::vector<std::weak_ptr<TcpStore>>& live_stores() {
+  static auto* v = new std::vector<std::weak_ptr<TcpStore>>();  // never destroyed: used while the process exits
+  return *v;
+}
+}  // namespace
+
 std::shared_ptr<TcpStore> TcpStore::create(const std::string& hostname, int port, const std::string& key, int world,
                                            int rank, std::chrono::milliseconds timeout) {
-  return std::make_shared<TcpStoreImpl>(hostname, port, key, world, rank, timeout);
+  auto store = std::make_shared<TcpStoreImpl>(hostname, port, key, world, rank, timeout);
+  std::lock_guard<std::mutex> lk(g_live_mu);
+  auto& live = live_stores();
+  live.erase(std::remove_if(live.begin(), live.end(), [](const std::weak_ptr<TcpStore>& w) { return w.expired(); }), live.end());
+  live.push_back(store);
+  return store;
+}
+
+void TcpStore::shutdown_all() {
+  std::vector<std::shared_ptr<TcpStore>> alive;
+  {
+    std::lock_guard<std::mutex> lk(g_live_mu);
+    for (auto& w : live_stores())
+      if (auto s = w.lock()) alive.push_back(std::move(s));
+  }
+  for (auto& s : alive) {
+    try {
+      s->shutdown();
+    } catch (...) {
+    }
+  }
 }
 
 }  // namespace moodist

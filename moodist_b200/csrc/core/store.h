@@ -53,6 +53,10 @@ class TcpStore : public KVStore {
 
   // Starts the coordinated shutdown; called by the destructor of the last handle.
   virtual void shutdown() = 0;
+  // Coordinated shutdown of every store of this process that is still alive. For the end of a process whose store
+  // objects were never destroyed (kept by a reference cycle, a global): a rank that just vanishes takes the answers
+  // it had queued for its peers with it.
+  static void shutdown_all();
 
   // Host-side fault injection for tests: from now on every `break_every`-th message this rank sends over a mesh
   // edge is lost together with its connection (0 switches it off). The edge redials and retransmits.

@@ -51,6 +51,7 @@ class TcpStoreGlue final : public c10d::Store {
     impl_->set_timeout(timeout);
   }
 #undef GUARD
+  void shutdown() { impl_->shutdown(); }
   std::string describe() const { return impl_->describe(); }
   std::vector<int> edges() const { return impl_->edges(); }
   void injectFaults(int break_every) { impl_->inject_faults(break_every); }
@@ -71,11 +72,14 @@ void bind_store(pybind11::module_& m) {
            }),
            py::arg("hostname"), py::arg("port"), py::arg("key"), py::arg("world_size"), py::arg("rank"),
            py::arg("timeout") = std::chrono::milliseconds(300000), py::call_guard<py::gil_scoped_release>())
+      .def("shutdown", &TcpStoreGlue::shutdown, py::call_guard<py::gil_scoped_release>(),
+           "coordinated shutdown now (otherwise when the last handle goes, or when the interpreter exits)")
       .def("describe", &TcpStoreGlue::describe)
       .def("edges", &TcpStoreGlue::edges)
       .def("_inject_faults", &TcpStoreGlue::injectFaults, py::arg("break_every"),
            "test hook: every N-th message this rank sends over a mesh edge is lost with its connection (0: off)")
       .def("_injected_breaks", &TcpStoreGlue::injectedBreaks);
+  m.def("_shutdown_all_stores", [] { TcpStore::shutdown_all(); }, py::call_guard<py::gil_scoped_release>());
   m.def("store_string_hash", &store_string_hash);
   m.def("store_mesh", &store_mesh);
 }

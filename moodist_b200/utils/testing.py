@@ -44,6 +44,16 @@ def _worker(fn, rank, world, port, args, env, result_dir, per_rank_logs):
         fn(rank, world, port, *args)
     except BaseException:  # noqa: BLE001 - the parent reports it
         status = traceback.format_exc()
+    if status == "ok":
+        # os._exit below skips the interpreter's exit hooks; what they would have done for a store that is still
+        # alive (kept by an exception's traceback, say) is done here: leave through the coordinated shutdown, so
+        # that the answers this rank still owes its peers reach them
+        try:
+            from .._core import _C
+
+            _C._shutdown_all_stores()
+        except Exception:  # noqa: BLE001 - leaving anyway
+            pass
     with open(os.path.join(result_dir, f"rank{rank}.status"), "w") as f:
         f.write(status)
     # leave without running destructors of half-torn-down process groups on failure

@@ -8,7 +8,7 @@ from datetime import timedelta
 
 import pytest
 
-from moodist_b200.utils.testing import run_ranks
+from moodist_b200.utils.testing import free_port, run_ranks
 
 
 def _store(rank, world, port, key="test", timeout=timedelta(seconds=20)):
@@ -245,3 +245,55 @@ def _interop(rank, world, port):
 
 def test_store_under_torch_and_torch_store_under_the_backend():
     run_ranks(_interop, 3, timeout=240)
+
+
+_LEAVER = """
+import sys, time
+from datetime import timedelta
+sys.path.insert(0, {root!r})
+import moodist_b200
+rank, port, marker = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+store = moodist_b200.TcpStore("127.0.0.1", port, "exit-hook", 2, rank, timedelta(seconds=20))
+hash_ = moodist_b200._core._C.store_string_hash
+key = next(k for k in (f"kept-by-rank-1-{{i}}" for i in range(1000)) if hash_(k) % 2 == 1)
+store.set(f"up{{rank}}", b"1")
+store.wait(["up0", "up1"])
+if rank == 1:
+    store.set(key, b"still here")
+    cycle = [store]
+    cycle.append(cycle)          # nothing destroys the store before the interpreter winds down
+    open(marker, "w").close()    # and this process ends right here
+else:
+    import os
+    while not os.path.exists(marker):
+        time.sleep(0.01)
+    assert store.get(key) == b"still here"
+    t0 = time.time()
+    try:
+        store.wait(["a key nobody sets"])
+        print("the wait returned?", flush=True)
+    except RuntimeError as e:
+        # told by the leaving rank itself, seconds later; a rank that just vanished would leave this wait to its
+        # 20 s timeout
+        print(f"ended after {{time.time() - t0:.1f}} s: {{e}}", flush=True)
+"""
+
+
+def test_store_left_alive_at_interpreter_exit_still_shuts_down_in_order(tmp_path):
+    """A rank ends its process with its store object still referenced (a cycle): between the interpreter's last
+    garbage collection and the exit hook the coordinated shutdown still runs, so the other rank's pending wait ends
+    within seconds with the name of the rank that left instead of running into its timeout."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "leaver.py"
+    script.write_text(_LEAVER.format(root=root))
+    port, marker = free_port(), str(tmp_path / "rank1-done")
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), str(port), marker], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in (0, 1)]
+    outs = [p.communicate(timeout=120)[0] for p in procs]
+    assert procs[0].returncode == 0 and "store was shut down on rank 1" in outs[0], outs
+    assert float(outs[0].split("ended after ")[1].split(" s")[0]) < 10, outs
+    assert procs[1].returncode == 0, outs
