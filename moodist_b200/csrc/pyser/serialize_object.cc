@@ -112,13 +112,14 @@ void init_strings() {
 }
 
 // ------------------------------------------------------------------------------------------------
-// Output bytes: a plain growing buffer (no zero-fill on growth, no per-byte capacity check beyond one compare).
+// Output bytes: a growing buffer that lives in the bytearray the caller finally receives (no zero-fill on growth, no
+// per-byte capacity check beyond one compare, no copy at the end).
 class ByteBuf {
  public:
   ByteBuf() = default;
   ByteBuf(const ByteBuf&) = delete;
   ByteBuf& operator=(const ByteBuf&) = delete;
-  ~ByteBuf() { free(data_); }
+  ~ByteBuf() { Py_XDECREF(array_); }
   size_t size() const { return size_; }
   uint8_t* data() { return data_; }
   uint8_t& operator[](size_t i) { return data_[i]; }
@@ -134,16 +135,33 @@ class ByteBuf {
     memcpy(data_ + size_, p, n);
     size_ += n;
   }
+  // The bytes written so far as a bytearray (a new reference); the buffer is empty afterwards. The storage IS
+  // the bytearray's, so nothing is copied however large the result.
+  PyObject* release() {
+    if (!array_) return PyByteArray_FromStringAndSize("", 0);
+    if (PyByteArray_Resize(array_, (Py_ssize_t)size_) < 0) throw PyError{};
+    PyObject* out = array_;
+    array_ = nullptr;
+    data_ = nullptr;
+    size_ = cap_ = 0;
+    return out;
+  }
 
  private:
-  void grow(size_t need) {
+  // out of line and marked cold, so that push_back / append stay a compare, a store and an add where they are inlined
+  __attribute__((noinline, cold)) void grow(size_t need) {
     size_t cap = cap_ ? cap_ * 2 : 256;
-    while (cap < need) cap *= 2;
-    void* p = realloc(data_, cap);
-    if (!p) throw std::bad_alloc();
-    data_ = static_cast<uint8_t*>(p);
+    if (cap < need) cap = need + (need >> 4);  // one large payload: no need to double past it
+    if (!array_) {
+      array_ = PyByteArray_FromStringAndSize(nullptr, (Py_ssize_t)cap);
+      if (!array_) throw PyError{};
+    } else if (PyByteArray_Resize(array_, (Py_ssize_t)cap) < 0) {
+      throw PyError{};
+    }
+    data_ = reinterpret_cast<uint8_t*>(PyByteArray_AS_STRING(array_));
     cap_ = cap;
   }
+  PyObject* array_ = nullptr;  // a bytearray whose storage is the buffer
   uint8_t* data_ = nullptr;
   size_t size_ = 0, cap_ = 0;
 };
@@ -782,7 +800,7 @@ PyObject* py_pack(PyObject*, PyObject* obj) {
     Packer pk;
     pk.out.reserve(256);
     pk.pack(obj);
-    return PyByteArray_FromStringAndSize((const char*)pk.out.data(), (Py_ssize_t)pk.out.size());
+    return pk.out.release();
   } catch (const PyError&) {
     return nullptr;
   } catch (const std::exception& e) {
