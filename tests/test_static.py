@@ -86,3 +86,18 @@ def test_packaging_lists_every_subpackage_and_the_package_version():
         if "__init__.py" in files:
             name = os.path.relpath(d, ROOT).replace(os.sep, ".")
             assert f'"{name}"' in src, f"{name} is missing from setup.py's package list"
+
+
+def test_every_environment_variable_the_sources_read_is_documented():
+    import re
+
+    used = set()
+    for top in ("moodist_b200", "bench.py", "setup.py", "benchmarks"):
+        path = os.path.join(ROOT, top)
+        files = [path] if os.path.isfile(path) else [os.path.join(d, f) for d, _, fs in os.walk(path) for f in fs
+                                                     if f.endswith((".py", ".cc", ".cu", ".h", ".cuh"))]
+        for f in files:
+            used.update(re.findall(r'"(MOODIST_[A-Z0-9_]+)"', open(f, errors="replace").read()))
+    page = open(os.path.join(ROOT, "docs", "api", "environment.md")).read()
+    missing = sorted(v for v in used if f"`{v}`" not in page)
+    assert not missing, f"not in docs/api/environment.md: {missing}"
