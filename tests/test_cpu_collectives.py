@@ -178,3 +178,47 @@ def _receive_first(rank, world, port):
 
 def test_receives_posted_before_sends():
     run_ranks(_receive_first, 3, timeout=120)
+
+
+def _many_ranks(rank, world, port):
+    dist = init_moodist(rank, world, port)
+    import moodist_b200 as moodist
+
+    pg = moodist.get_backend(device="cpu")
+    for n in (1, 1000, 100003):
+        x = torch.full((n,), float(rank))
+        dist.all_reduce(x)
+        assert float(x[0]) == world * (world - 1) / 2 and float(x[-1]) == world * (world - 1) / 2
+        out = torch.empty(world * n)
+        dist.all_gather_into_tensor(out, torch.full((n,), float(rank)))
+        assert float(out[-1]) == world - 1
+        o = torch.empty(n)
+        dist.reduce_scatter_tensor(o, torch.full((world * n,), 1.0))
+        assert float(o[0]) == world
+        b = torch.full((n,), float(rank))
+        dist.broadcast(b, src=world - 1)
+        assert float(b[0]) == world - 1
+    send = torch.cat([torch.full((d + 1,), float(rank * 100 + d)) for d in range(world)])
+    recv = torch.empty(world * (rank + 1))
+    dist.all_to_all_single(recv, send, output_split_sizes=[rank + 1] * world, input_split_sizes=[d + 1 for d in range(world)])
+    assert [float(recv[s * (rank + 1)]) for s in range(world)] == [float(s * 100 + rank) for s in range(world)]
+    q = moodist.Queue(pg, location=range(world), name="to-everyone")
+    if rank == 3:
+        q.put_object("hello everyone")
+    assert q.get_object(timeout=60) == "hello everyone"
+    rows = 4
+    op = moodist.compile_op(pg, shape=(rows * world, 8), dtype=torch.float32,
+                            inputs=[{"offset": [rank * rows, 0], "shape": [rows, 8]}],
+                            outputs=[{"offset": [0, 0], "shape": [rows * world, 8]}])
+    out = torch.empty(rows * world, 8)
+    op([torch.full((rows, 8), float(rank))], [out]).wait()
+    assert out[::rows, 0].tolist() == [float(r) for r in range(world)]
+    stats = pg.host_stats()
+    assert stats["unix_socket_peers"] == world - 1, stats
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sixteen_cpu_ranks():
+    """Twice as many ranks as a node has GPUs: the host engine, the multicast queue and compile_op have no such limit."""
+    run_ranks(_many_ranks, 16, timeout=300)
