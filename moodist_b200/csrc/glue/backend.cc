@@ -84,12 +84,13 @@ class RecvWork final : public c10d::Work {
   RecvWork(int rank, std::vector<at::Tensor> outputs, c10::intrusive_ptr<MoodistBackend> owner,
            std::shared_ptr<void> posted, std::function<void()> after)
       : c10d::Work(rank, c10d::OpType::RECV), outputs_(std::move(outputs)), owner_(std::move(owner)),
-        posted_(std::move(posted)), after_(std::move(after)) {
+        posted_(std::move(posted)), after_(std::move(after)), has_after_(static_cast<bool>(after_)) {
     future_ = c10::make_intrusive<at::ivalue::Future>(c10::ListType::create(c10::TensorType::get()));
   }
   bool isCompleted() override {
-    std::lock_guard<std::mutex> lk(mu_);
-    return done_ || (!after_ && owner_->hostGroup().recv_done(posted_));
+    // never blocks, also while another thread sits in wait(): a receive with a device part counts as complete
+    // once wait() has run it
+    return done_.load() || (!has_after_ && owner_->hostGroup().recv_done(posted_));
   }
   bool isSuccess() const override { return true; }
   bool wait(std::chrono::milliseconds) override {
@@ -111,11 +112,12 @@ class RecvWork final : public c10d::Work {
 
  private:
   std::mutex mu_;
-  bool done_ = false;
+  std::atomic<bool> done_{false};
   std::vector<at::Tensor> outputs_;
   c10::intrusive_ptr<MoodistBackend> owner_;
   std::shared_ptr<void> posted_;
   std::function<void()> after_;
+  const bool has_after_;
   c10::intrusive_ptr<at::ivalue::Future> future_;
 };
 
