@@ -600,7 +600,22 @@ class Unpacker {
       case T_LIST: {
         int64_t n = unpack_len();
         Ref list = checked(PyList_New(n));
-        if (store) remember(offset, list.p);
+        if (store) {
+          // The list can be reached through a back reference while it is being filled (it may contain itself).
+          // A damaged stream could hand it, half filled, to any callable: no slot is ever left empty.
+          for (int64_t i = 0; i < n; ++i) {
+            Py_INCREF(Py_None);
+            PyList_SET_ITEM(list.p, i, Py_None);
+          }
+          remember(offset, list.p);
+          for (int64_t i = 0; i < n; ++i) {
+            PyObject* item = unpack();
+            PyObject* placeholder = PyList_GET_ITEM(list.p, i);
+            PyList_SET_ITEM(list.p, i, item);
+            Py_DECREF(placeholder);
+          }
+          return list.release();
+        }
         for (int64_t i = 0; i < n; ++i) PyList_SET_ITEM(list.p, i, unpack());
         return list.release();
       }
@@ -733,6 +748,7 @@ class Unpacker {
     }
     if (bits & 2) {
       Ref items(unpack());
+      if (!PyList_Check(items.p)) bad("list items of an object are not a list");
       if (PyObject_HasAttr(obj.p, s_extend)) {
         checked(PyObject_CallMethodOneArg(obj.p, s_extend, items.p));
       } else {

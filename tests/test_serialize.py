@@ -295,3 +295,26 @@ def test_truncated_and_corrupt_input_raise():
             moodist.deserialize(bytes(b))
         except Exception:
             pass
+    # the same for streams with objects rebuilt through callables, back references and lists that contain
+    # themselves: damage there can point a reference at a container that is still being filled, or put
+    # something that is not a list where list items are expected
+    shared = [1, 2, 3]
+    cyclic = [shared, shared, {"again": shared}]
+    cyclic.append(cyclic)
+    rich = [Point(1, [2, 3]), WithSlots(), collections.OrderedDict(a=1), collections.deque([1, 2], maxlen=4), cyclic,
+            collections.defaultdict(list, {"k": [1]}), Colour.RED, FrozenRecord(1, "y"), frozenset({(1, 2)})]
+    blob = bytes(moodist.serialize(rich).numpy().tobytes())
+    assert moodist.deserialize(blob)[0] == Point(1, [2, 3])
+    for cut in range(len(blob)):
+        try:
+            moodist.deserialize(blob[:cut])
+        except Exception:
+            pass
+    for _ in range(4000):
+        b = bytearray(blob)
+        for _ in range(rng.randint(1, 3)):
+            b[rng.randrange(len(b))] = rng.randrange(256)
+        try:
+            moodist.deserialize(bytes(b))
+        except Exception:
+            pass
