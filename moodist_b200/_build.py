@@ -57,14 +57,14 @@ def _q(s) -> str:
 SANITIZERS = ("address", "thread", "undefined")
 
 
-def generate(with_torch: bool = True, sanitize: str | None = None) -> Path:
+def generate(with_torch: bool = True, sanitize: str | None = None, python: bool = False) -> Path:
     """Write the ninja file.  ``sanitize`` ("address", "thread" or "undefined") describes a second build of the
     torch-free core with that sanitizer, in ``build/native-<sanitizer>/`` (nothing in-tree is touched): the host
     sources are recompiled with ``-fsanitize=...``, the CUDA objects of the regular build are linked in as they
     are.  The reference has the same switches in its CMake file (``ENABLE_ASAN`` / ``ENABLE_TSAN``,
     ``CMakeLists.txt:6-25, 213-218``)."""
     if sanitize is not None:
-        return _generate_sanitized(sanitize)
+        return _generate_sanitized(sanitize, python)
     cuda = _cuda_home()
     BUILD.mkdir(parents=True, exist_ok=True)
     pyinc = sysconfig.get_paths()["include"]
@@ -158,7 +158,34 @@ def sanitized_dir(sanitize: str) -> Path:
     return BUILD.parent / f"native-{sanitize}"
 
 
-def _generate_sanitized(sanitize: str) -> Path:
+def sanitized_package_dir(sanitize: str) -> Path:
+    """Where the instrumented copy of the Python package lives (``--python``): put it first on ``sys.path``."""
+    return sanitized_dir(sanitize) / "pkg"
+
+
+def sanitized_env(sanitize: str) -> dict:
+    """Environment for a Python process that imports the instrumented package: the sanitizer's runtime has to be
+    loaded before the interpreter (which is not linked against it), together with libstdc++, whose exception
+    entry points the runtime wraps; Python's own small-object allocator is switched off so that the sanitizer sees
+    every object."""
+    cxx = os.environ.get("MOODIST_CXX", "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
+    runtime = {"address": "libasan.so", "thread": "libtsan.so", "undefined": "libubsan.so"}[sanitize]
+
+    def where(lib):
+        return subprocess.run([cxx, f"-print-file-name={lib}"], capture_output=True, text=True).stdout.strip()
+
+    env = {
+        "LD_PRELOAD": f"{where(runtime)}:{where('libstdc++.so')}",
+        "PYTHONMALLOC": "malloc",
+        "PYTHONPATH": str(sanitized_package_dir(sanitize)),
+        "ASAN_OPTIONS": "detect_leaks=0:abort_on_error=0:exitcode=97",
+        "UBSAN_OPTIONS": "print_stacktrace=1:halt_on_error=1:exitcode=97",
+        "TSAN_OPTIONS": "exitcode=97",
+    }
+    return env
+
+
+def _generate_sanitized(sanitize: str, python: bool = False) -> Path:
     if sanitize not in SANITIZERS:
         raise ValueError(f"unknown sanitizer {sanitize!r}: one of {SANITIZERS}")
     cuda = _cuda_home()
@@ -190,7 +217,60 @@ def _generate_sanitized(sanitize: str) -> Path:
     lib = out / "libmoodist_b200.so"
     lines.append(f"build {_q(lib)}: link {' '.join(_q(o) for o in objs + kernel_objs)}")
     lines.append(f"  ldflags = {san} -L{cuda}/lib64 -lcudart_static -lrt -ldl -pthread")
-    lines.append(f"default {_q(lib)}")
+    targets = [lib]
+    if python:
+        # The whole package, instrumented: the serializer and the torch bindings compiled with the sanitizer too,
+        # next to links to the Python sources, so that `import moodist_b200` from there runs the same code with
+        # every native line checked.
+        import torch
+        from torch.utils import cpp_extension
+
+        pkg = sanitized_package_dir(sanitize) / "moodist_b200"
+        pkg.mkdir(parents=True, exist_ok=True)
+        for entry in ROOT.iterdir():
+            if entry.name in ("csrc", "__pycache__") or entry.suffix == ".so":
+                continue
+            link = pkg / entry.name
+            if link.is_symlink() or link.exists():
+                continue
+            link.symlink_to(entry)
+        pyinc = sysconfig.get_paths()["include"]
+        tinc = " ".join(f"-isystem {p}" for p in cpp_extension.include_paths())
+        tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
+        abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+        lines += ["rule cxx_extra", "  command = $cxx $cflags $extra -MMD -MF $out.d -c $in -o $out", "  depfile = $out.d",
+                  "  deps = gcc"]
+        ser_objs = []
+        for src in _sources("pyser", (".cc",)):
+            obj = out / "pyser" / (src.stem + ".o")
+            lines.append(f"build {_q(obj)}: cxx_extra {_q(src)}")
+            lines.append(f"  extra = -I{pyinc}")
+            ser_objs.append(obj)
+        ser_lib = pkg / "_serialize.so"
+        lines.append(f"build {_q(ser_lib)}: link {' '.join(_q(o) for o in ser_objs)}")
+        lines.append(f"  ldflags = {san} -pthread")
+        glue_extra = (
+            f"{tinc} -isystem {pyinc} -D_GLIBCXX_USE_CXX11_ABI={abi} -DTORCH_EXTENSION_NAME=_C "
+            "-DTORCH_API_INCLUDE_EXTENSION_H -DUSE_C10D -Wno-deprecated-declarations -Wno-sign-compare"
+        )
+        glue_objs = []
+        for src in _sources("glue", (".cc",)):
+            obj = out / "glue" / (src.stem + ".o")
+            lines.append(f"build {_q(obj)}: cxx_extra {_q(src)}")
+            lines.append(f"  extra = {glue_extra}")
+            glue_objs.append(obj)
+        core_copy = pkg / "libmoodist_b200.so"
+        lines.append("rule copy")
+        lines.append("  command = cp -f $in $out")
+        lines.append(f"build {_q(core_copy)}: copy {_q(lib)}")
+        glue_lib = pkg / "_C.so"
+        lines.append(f"build {_q(glue_lib)}: link {' '.join(_q(o) for o in glue_objs)} | {_q(core_copy)}")
+        lines.append(
+            f"  ldflags = {san} -L{pkg} -lmoodist_b200 -L{tlib} -ltorch -ltorch_cpu -ltorch_python -lc10 "
+            f"-lc10_cuda -ltorch_cuda -Wl,-rpath,'$$ORIGIN' -Wl,-rpath,{tlib} -pthread"
+        )
+        targets += [ser_lib, core_copy, glue_lib]
+    lines.append("default " + " ".join(_q(t) for t in targets))
     path = out / "build.ninja"
     text = "\n".join(lines) + "\n"
     if not path.exists() or path.read_text() != text:
@@ -198,13 +278,14 @@ def _generate_sanitized(sanitize: str) -> Path:
     return path
 
 
-def build(with_torch: bool = True, verbose: bool = False, sanitize: str | None = None) -> None:
-    """Build (incrementally) all native libraries for sm_100a; with ``sanitize`` the instrumented core as well."""
+def build(with_torch: bool = True, verbose: bool = False, sanitize: str | None = None, python: bool = False) -> None:
+    """Build (incrementally) all native libraries for sm_100a; with ``sanitize`` the instrumented core as well, and
+    with ``python`` an instrumented copy of the whole package (``sanitized_package_dir``, ``sanitized_env``)."""
     generate(with_torch)
     jobs = os.environ.get("MOODIST_BUILD_JOBS", str(os.cpu_count() or 4))
     if sanitize is not None:
         build(with_torch=False, verbose=verbose)  # the CUDA objects come from the regular build
-        generate(sanitize=sanitize)
+        generate(sanitize=sanitize, python=python)
         cmd = [sys.executable, "-m", "ninja", "-C", str(sanitized_dir(sanitize)), "-j", jobs]
         r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         if r.returncode != 0:
@@ -227,8 +308,11 @@ if __name__ == "__main__":
     if "--sanitize" in sys.argv:
         san = sys.argv[sys.argv.index("--sanitize") + 1]
     if san:
-        build(sanitize=san, verbose="-v" in sys.argv)
+        build(sanitize=san, verbose="-v" in sys.argv, python="--python" in sys.argv)
         print("built:", sanitized_dir(san) / "libmoodist_b200.so")
+        if "--python" in sys.argv:
+            print("instrumented package:", sanitized_package_dir(san))
+            print("run with:", " ".join(f"{k}={v}" for k, v in sanitized_env(san).items()), "python ...")
     else:
         build(with_torch="--no-torch" not in sys.argv, verbose="-v" in sys.argv)
         print("built:", ", ".join(p.name for p in sorted(ROOT.glob("*.so"))))

@@ -2,7 +2,9 @@
 UndefinedBehaviorSanitizer: `python moodist_b200/_build.py --sanitize <kind>` builds an instrumented copy of the
 library outside the tree, and the stand-alone C++ self-tests (wire format, planner, store mesh, transport, the
 host engine with 2-8 ranks as threads doing every CPU collective) run against it.  Any report fails the test.
-The reference has the same switches (ENABLE_ASAN / ENABLE_TSAN in its CMakeLists.txt:6-25)."""
+With `--python` the serializer and the torch bindings are instrumented as well and a Python scenario runs against
+that copy of the package.  The reference has the same switches (ENABLE_ASAN / ENABLE_TSAN in its
+CMakeLists.txt:6-25)."""
 
 import importlib.util
 import os
@@ -41,3 +43,22 @@ def test_core_selftests_under_sanitizer(kind, tmp_path):
             assert r.returncode == 0 and "SELFTEST OK" in out, out[-6000:]
             for marker in ("ERROR: AddressSanitizer", "ERROR: LeakSanitizer", "WARNING: ThreadSanitizer", "runtime error:"):
                 assert marker not in out, out[-6000:]
+
+
+def test_python_package_under_address_sanitizer(tmp_path):
+    """`_build.py --sanitize address --python` makes an instrumented copy of the whole package (serializer, torch
+    bindings and core compiled with AddressSanitizer next to links to the Python sources); a scenario of
+    serializer fuzzing and three CPU ranks runs against it in a fresh interpreter with the sanitizer's runtime
+    preloaded.  Rank processes inherit the environment, so their native code is checked as well."""
+    import sys
+
+    b = _builder()
+    b.build(sanitize="address", python=True)
+    env = dict(os.environ)
+    env.update(b.sanitized_env("address"))
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "sanitized_scenario.py"), "200"], cwd=str(tmp_path),
+                       capture_output=True, text=True, timeout=1500, env=env)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0 and "SCENARIO OK" in out, out[-6000:]
+    assert str(b.sanitized_package_dir("address")) in out, out[-2000:]  # the instrumented copy is what ran
+    assert "ERROR: AddressSanitizer" not in out, out[-6000:]
