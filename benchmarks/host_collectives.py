@@ -50,6 +50,8 @@ def _rank(rank, world, port, backend, sizes_mib, warmup, iters, extras):
     else:
         dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     rows = []
+    # the average is what sharded training asks for; gloo has none, so it is timed on the sum
+    rs_op, rs_name = (dist.ReduceOp.AVG, "avg") if backend == "moodist" else (dist.ReduceOp.SUM, "sum")
     for mib in sizes_mib:
         n = int(mib * (1 << 20)) // 4
         n -= n % world
@@ -60,7 +62,7 @@ def _rank(rank, world, port, backend, sizes_mib, warmup, iters, extras):
         for name, fn, moved in (
             ("all_reduce", lambda: dist.all_reduce(x), 2 * n * 4 * (world - 1) / world),
             ("all_gather", lambda: dist.all_gather_into_tensor(out, x), n * 4 * (world - 1)),
-            ("reduce_scatter", lambda: dist.reduce_scatter_tensor(o, x), n * 4 * (world - 1) / world),
+            ("reduce_scatter " + rs_name, lambda: dist.reduce_scatter_tensor(o, x, op=rs_op), n * 4 * (world - 1) / world),
             ("broadcast", lambda: dist.broadcast(x, 0), n * 4),
         ):
             med, best = _time(dist, fn, warmup, its)

@@ -101,10 +101,10 @@ def _store_breaks(rank, world, port):
     store.set(f"hello{rank}", b"x")
     store.wait([f"hello{r}" for r in range(world)])
     store._inject_faults(3)  # every third message is lost with its connection
-    for i in range(40):
+    for i in range(20):
         store.set(f"k{rank}/{i}", str(i).encode())
     for r in range(world):
-        for i in range(40):
+        for i in range(20):
             assert store.get(f"k{r}/{i}") == str(i).encode()
     assert store.add("counter", 1) >= 1
     store.wait(["counter"])
