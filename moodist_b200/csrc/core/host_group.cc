@@ -104,6 +104,16 @@ struct Work {
 struct Mail {
   uint32_t tag;
   Bytes data;
+  // a large payload that waits in the sender's memory to be fetched
+  bool offer = false;
+  uint64_t bytes = 0, addr = 0;
+  uint32_t key = 0, id = 0;
+};
+
+struct Offer {
+  std::shared_ptr<Waiter> waiter;
+  uint32_t key = 0;
+  std::shared_ptr<void> keep;
 };
 
 class HostGroupImpl final : public HostGroup {
@@ -370,13 +380,35 @@ class HostGroupImpl final : public HostGroup {
     submit_and_wait(w);
   }
 
-  void send(const void* data, size_t bytes, int dst, uint32_t tag) override {
-    // the payload travels inside one framed message, whose length field has 32 bits
-    if (bytes > 0xfff00000ull) fail("moodist: send: one message carries at most 4 GiB - 1 MiB; split the tensor");
-    Writer wr;
-    wr(tag, (uint64_t)bytes);
-    wr.raw(data, bytes);
-    send_message(dst, kOpSendRecv, std::move(wr.out));
+  void send(const void* data, size_t bytes, int dst, uint32_t tag) override { send_wait(send_post(data, bytes, dst, tag, nullptr)); }
+
+  std::shared_ptr<void> send_post(const void* data, size_t bytes, int dst, uint32_t tag, std::shared_ptr<void> keep) override {
+    auto waiter = std::make_shared<Waiter>();
+    if (bytes <= kEagerSendBytes) {
+      // small: inside the message, buffered at the receiver until a receive asks for it
+      Writer wr;
+      wr(tag, (uint64_t)bytes);
+      wr.raw(data, bytes);
+      send_message(dst, kOpSendRecv, std::move(wr.out));
+      waiter->finish();
+      return waiter;
+    }
+    run_on_engine([=, this] {
+      uint32_t id = ++next_offer_;
+      Offer o;
+      o.waiter = waiter;
+      o.key = MrTable::instance().add(const_cast<void*>(data), bytes);
+      o.keep = keep;
+      offers_[id] = std::move(o);
+      send_message(dst, kOpSendOffer, encode(tag, (uint64_t)bytes, (uint64_t)(uintptr_t)data, offers_[id].key, id));
+    });
+    return waiter;
+  }
+
+  void send_wait(const std::shared_ptr<void>& posted) override { wait(*std::static_pointer_cast<Waiter>(posted), "send"); }
+
+  bool send_done(const std::shared_ptr<void>& posted) override {
+    return std::static_pointer_cast<Waiter>(posted)->done_hint.load(std::memory_order_acquire);
   }
 
   void recv(void* data, size_t bytes, int src, uint32_t tag) override { recv_wait(recv_post(data, bytes, src, tag, nullptr)); }
@@ -784,6 +816,26 @@ class HostGroupImpl final : public HostGroup {
           match_recvs();
           return;
         }
+        case kOpSendOffer: {
+          Mail m;
+          m.offer = true;
+          r(m.tag, m.bytes, m.addr, m.key, m.id);
+          mailbox_[src].push_back(std::move(m));
+          match_recvs();
+          return;
+        }
+        case kOpSendTaken: {
+          uint32_t id;
+          bool ok;
+          std::string text;
+          r(id, ok, text);
+          auto it = offers_.find(id);
+          if (it == offers_.end()) return;
+          MrTable::instance().remove(it->second.key);
+          it->second.waiter->finish(ok ? std::string() : text);
+          offers_.erase(it);
+          return;
+        }
         case kOpBarrier:
         case kOpAllGatherCpu:
         case kOpReduceScatterCpu:
@@ -834,8 +886,21 @@ class HostGroupImpl final : public HostGroup {
       bool matched = false;
       for (auto m = box.begin(); m != box.end(); ++m) {
         if (m->tag != it->tag) continue;
-        if (m->data.size() != it->bytes) {
-          it->waiter->finish(strf("recv size mismatch: expected %zu bytes, message has %zu", it->bytes, m->data.size()));
+        size_t have = m->offer ? (size_t)m->bytes : m->data.size();
+        if (have != it->bytes) {
+          std::string text = strf("recv size mismatch: expected %zu bytes, message has %zu", it->bytes, have);
+          if (m->offer) send_message(it->src, kOpSendTaken, encode(m->id, false, "the receiver's " + text));
+          it->waiter->finish(text);
+        } else if (m->offer) {
+          // fetch the payload out of the sender's memory into the caller's; both ends learn how it went
+          int src = it->src;
+          uint32_t id = m->id;
+          auto waiter = it->waiter;
+          auto keep = it->keep;
+          post_read(src, it->data, it->bytes, m->key, m->addr, [this, src, id, waiter, keep](bool ok) {
+            send_message(src, kOpSendTaken, encode(id, ok, std::string(ok ? "" : "the receiver could not read the payload")));
+            waiter->finish(ok ? std::string() : "reading the sender's payload failed");
+          });
         } else {
           if (it->bytes) memcpy(it->data, m->data.data(), it->bytes);
           it->waiter->finish();
@@ -913,6 +978,10 @@ class HostGroupImpl final : public HostGroup {
   std::map<uint64_t, Announce> announces_;
   std::map<int, uint32_t> next_seq_to_, next_seq_from_;
   std::map<int, std::deque<Mail>> mailbox_;
+  // payloads up to this size travel inside their message; larger ones are fetched by the receiver
+  static constexpr size_t kEagerSendBytes = 64 << 10;
+  std::map<uint32_t, Offer> offers_;  // large sends waiting to be fetched (engine thread)
+  uint32_t next_offer_ = 0;
   std::map<uint32_t, std::deque<std::pair<int, Bytes>>> unhandled_;
   std::list<PendingRecv> pending_recvs_;
   std::vector<double> last_heard_;

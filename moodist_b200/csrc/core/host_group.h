@@ -48,6 +48,8 @@ enum OpType : uint32_t {
   kOpScatterCpu = 100,  // not in the reference (scatter throws there)
   kOpSendRecv = 101,    // point-to-point payloads (send/recv are unsupported in the reference)
   kOpCudaItemDone = 103, // a receiver has copied a point-to-point CUDA tensor: the sender may release its buffer
+  kOpSendOffer = 104,    // a large point-to-point payload is ready to be fetched: tag, size, address, key, id
+  kOpSendTaken = 105,    // the receiver has fetched (or refused) the payload of offer `id`
   kOpErrorNotice = 102, // "this rank entered its error state because ...": the receivers enter theirs at once
                         // (the reference's ranks learn of a peer's error state only when that process exits)
 };
@@ -81,6 +83,13 @@ class HostGroup {
   virtual void barrier() = 0;
   virtual void send(const void* data, size_t bytes, int dst, uint32_t tag) = 0;
   virtual void recv(void* data, size_t bytes, int src, uint32_t tag) = 0;
+  // The send in two steps. Small payloads travel inside their message and the returned request is complete at
+  // once; a large one is offered to the receiver, which fetches it straight out of the caller's memory (one copy,
+  // made by the receiving process where the two share a machine) once a matching receive exists, so the memory
+  // (held through `keep`) must stay unchanged until send_wait() returns.
+  virtual std::shared_ptr<void> send_post(const void* data, size_t bytes, int dst, uint32_t tag, std::shared_ptr<void> keep) = 0;
+  virtual void send_wait(const std::shared_ptr<void>& posted) = 0;
+  virtual bool send_done(const std::shared_ptr<void>& posted) = 0;
   // The receive in two steps: recv_post() files the request and returns at once (requests from one source with one
   // tag are served in the order they were posted; `keep` is held until the data has landed, so the destination
   // cannot go away under it), recv_wait() blocks until it is served and raises what went wrong.

@@ -81,22 +81,26 @@ class DoneWork final : public c10d::Work {
 // part has arrived (the device part of a CUDA receive).
 class RecvWork final : public c10d::Work {
  public:
+  // `send` = true makes it the work of a posted send (completed when the receiver has taken the payload)
   RecvWork(int rank, std::vector<at::Tensor> outputs, c10::intrusive_ptr<MoodistBackend> owner,
-           std::shared_ptr<void> posted, std::function<void()> after)
-      : c10d::Work(rank, c10d::OpType::RECV), outputs_(std::move(outputs)), owner_(std::move(owner)),
-        posted_(std::move(posted)), after_(std::move(after)), has_after_(static_cast<bool>(after_)) {
+           std::shared_ptr<void> posted, std::function<void()> after, bool send = false)
+      : c10d::Work(rank, send ? c10d::OpType::SEND : c10d::OpType::RECV), outputs_(std::move(outputs)),
+        owner_(std::move(owner)), posted_(std::move(posted)), after_(std::move(after)),
+        has_after_(static_cast<bool>(after_)), send_(send) {
     future_ = c10::make_intrusive<at::ivalue::Future>(c10::ListType::create(c10::TensorType::get()));
   }
   bool isCompleted() override {
     // never blocks, also while another thread sits in wait(): a receive with a device part counts as complete
     // once wait() has run it
-    return done_.load() || (!has_after_ && owner_->hostGroup().recv_done(posted_));
+    if (done_.load()) return true;
+    if (has_after_) return false;
+    return send_ ? owner_->hostGroup().send_done(posted_) : owner_->hostGroup().recv_done(posted_);
   }
   bool isSuccess() const override { return true; }
   bool wait(std::chrono::milliseconds) override {
     std::lock_guard<std::mutex> lk(mu_);
     if (done_) return true;
-    MOODIST_TRANSLATE(owner_->hostGroup().recv_wait(posted_);)
+    MOODIST_TRANSLATE(if (send_) owner_->hostGroup().send_wait(posted_); else owner_->hostGroup().recv_wait(posted_);)
     if (after_) {
       auto f = std::move(after_);
       after_ = nullptr;
@@ -118,6 +122,7 @@ class RecvWork final : public c10d::Work {
   std::shared_ptr<void> posted_;
   std::function<void()> after_;
   const bool has_after_;
+  const bool send_;
   c10::intrusive_ptr<at::ivalue::Future> future_;
 };
 
@@ -690,8 +695,13 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::send(std::vector<at::Tensor>& ten
     }
   }
   at::Tensor host = t.is_cuda() ? t.cpu() : t;  // .cpu() synchronises with the producing stream
-  MOODIST_TRANSLATE(hostGroup().send(host.data_ptr(), (size_t)host.nbytes(), dstRank, (uint32_t)tag);)
-  return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::SEND, tensors);
+  // posted, not waited for: a large payload stays where it is until the receiver fetches it, and a rank that posts
+  // its sends before its receives (isend, then irecv) must not sit here until the other side gets to its receive
+  std::shared_ptr<void> posted;
+  MOODIST_TRANSLATE(posted = hostGroup().send_post(host.data_ptr(), (size_t)host.nbytes(), dstRank, (uint32_t)tag,
+                                                   std::make_shared<at::Tensor>(host));)
+  auto self = c10::intrusive_ptr<MoodistBackend>::unsafe_reclaim_from_nonowning(this);
+  return c10::make_intrusive<RecvWork>(rank_, tensors, self, posted, nullptr, true);
 }
 
 c10::intrusive_ptr<c10d::Work> MoodistBackend::recv(std::vector<at::Tensor>& tensors, int srcRank, int tag) {

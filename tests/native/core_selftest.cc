@@ -490,6 +490,13 @@ static void test_host_group(int world) {
           g->send(give.data(), give.size() * 8, nxt, 7);
           g->recv_wait(posted);
           CHECK(g->recv_done(posted) && got[0] == prv && got[99] == prv);
+          // the same with payloads that are not copied into a message but fetched by the receiver, the send
+          // posted first this time
+          std::vector<int64_t> big_got(100000, -1), big_give(100000, r + 1000);
+          auto sent = g->send_post(big_give.data(), big_give.size() * 8, nxt, 8, nullptr);
+          g->recv(big_got.data(), big_got.size() * 8, prv, 8);
+          g->send_wait(sent);
+          CHECK(g->send_done(sent) && big_got[0] == prv + 1000 && big_got[99999] == prv + 1000);
         }
         // everybody puts into a queue that lives on rank 0
         auto q = queues->make_queue({0}, false, std::string("selftest"));

@@ -170,6 +170,32 @@ def _receive_first(rank, world, port):
     if rank == 1:
         with pytest.raises(RuntimeError, match="size mismatch"):
             dist.recv(torch.empty(5), 0, tag=11)
+    # large payloads are not copied into a message: the receiver fetches them from the sender's tensor. Sends posted
+    # before receives and the other way round, several in flight, then the blocking forms
+    n = 300_000
+    for sends_first in (True, False):
+        outs = [torch.full((n,), float(10 * rank + k)) for k in range(3)]
+        ins = [torch.empty(n) for _ in range(3)]
+        sends = [dist.P2POp(dist.isend, outs[k], nxt, tag=20 + k) for k in range(3)]
+        recvs = [dist.P2POp(dist.irecv, ins[k], prv, tag=20 + k) for k in range(3)]
+        for w in dist.batch_isend_irecv(sends + recvs if sends_first else recvs + sends):
+            w.wait()
+        for k in range(3):
+            assert float(ins[k][0]) == 10 * prv + k and float(ins[k][-1]) == 10 * prv + k
+    big = torch.arange(n, dtype=torch.float64) + rank
+    if rank == 0:
+        dist.send(big, 1, tag=30)
+    if rank == 1:
+        got = torch.empty(n, dtype=torch.float64)
+        dist.recv(got, 0, tag=30)
+        assert torch.equal(got, torch.arange(n, dtype=torch.float64))
+    # a large message of another size fails on both sides, with the reason
+    if rank == 0:
+        with pytest.raises(RuntimeError, match="size mismatch"):
+            dist.send(torch.ones(n), 1, tag=31)
+    if rank == 1:
+        with pytest.raises(RuntimeError, match="size mismatch"):
+            dist.recv(torch.empty(n + 1), 0, tag=31)
     t = torch.ones(2)
     dist.all_reduce(t)
     assert float(t[0]) == world
