@@ -67,6 +67,21 @@ def _rank(rank, world, port, backend, sizes_mib, warmup, iters, extras):
         ):
             med, best = _time(dist, fn, warmup, its)
             rows.append((f"{name} {mib:g} MiB fp32", med, best, moved))
+    if world >= 2:
+        # point to point between ranks 0 and 1: from the barrier until the receiver has the tensor
+        for mib in [1 / 1024] + list(sizes_mib):
+            n = max(1, int(mib * (1 << 20)) // 4)
+            x, y = torch.randn(n), torch.empty(n)
+
+            def exchange():
+                if rank == 0:
+                    dist.send(x, 1)
+                elif rank == 1:
+                    dist.recv(y, 0)
+
+            med, best = _time(dist, exchange, warmup, max(3, iters // 4) if mib >= 64 else iters)
+            size = f"{mib:g} MiB" if mib >= 1 else f"{mib * 1024:g} KiB"
+            rows.append((f"send -> recv {size} fp32", med, best, n * 4))
     small = torch.ones(16)
     med, best = _time(dist, lambda: dist.all_reduce(small), warmup * 5, iters * 10)
     rows.append(("all_reduce 16 elements", med, best, 0))
