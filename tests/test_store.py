@@ -83,7 +83,9 @@ def test_store_operations(world):
 
 
 def _timeouts(rank, world, port):
-    store = _store(rank, world, port, key="timeout_test", timeout=timedelta(milliseconds=500))
+    # joined with a generous limit (the ranks' processes start seconds apart on a busy machine), then shortened
+    store = _store(rank, world, port, key="timeout_test", timeout=timedelta(seconds=30))
+    store.set_timeout(timedelta(milliseconds=500))
     t0 = time.time()
     with pytest.raises(RuntimeError, match="timed out"):
         store.get("this_key_does_not_exist")
