@@ -114,7 +114,7 @@ def _graceful(rank, world, port):
     time.sleep(min(0.01 * rank, 0.5))  # staggered destruction must not raise anywhere
     t0 = time.time()
     del store
-    assert time.time() - t0 < 3.5
+    assert time.time() - t0 < 6  # at most 2 s + 1 s + 50 ms of waiting for the others by design
 
 
 def test_store_graceful_shutdown():
