@@ -75,6 +75,11 @@ def test_forced_tcp_fallback():
     run_ranks(_body, 2, False, timeout=180, env={"MOODIST_DIRECT_CPU": 0})
 
 
+def test_plain_tcp_as_between_machines():
+    """Neither same-machine shortcut: every byte over loopback TCP, the path ranks on different hosts take."""
+    run_ranks(_body, 3, False, timeout=180, env={"MOODIST_DIRECT_CPU": 0, "MOODIST_DISABLE_UNIX_SOCKETS": 1})
+
+
 def _sockets(rank, world, port, unix_wanted):
     dist = init_moodist(rank, world, port)
     import moodist_b200
