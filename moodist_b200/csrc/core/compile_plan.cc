@@ -254,13 +254,16 @@ struct RemoteInput {
 class CustomRouter {
  public:
   using Fn = std::function<void(int src, uint32_t call, uint8_t kind, Reader& r)>;
+  // One router per group, kept by the group itself: it goes when the group goes. (A process-wide table keyed by
+  // the group's address would hand a stale router, whose handler was installed on a group that no longer
+  // exists, to the next group that happens to be allocated at the same address.)
   static CustomRouter& of(HostGroup& g) {
     static std::mutex mu;
-    static std::map<HostGroup*, std::unique_ptr<CustomRouter>> routers;
     std::lock_guard<std::mutex> lk(mu);
-    auto& r = routers[&g];
-    if (!r) {
-      r = std::make_unique<CustomRouter>();
+    std::shared_ptr<void>& slot = g.extension("custom-op-router");
+    if (!slot) {
+      auto r = std::make_shared<CustomRouter>();
+      slot = r;
       CustomRouter* p = r.get();
       g.set_handler(kOpCustom, [p](int src, Reader& rd) {
         uint32_t op, call;
@@ -278,7 +281,7 @@ class CustomRouter {
           p->early_[op].emplace_back(src, call, kind, Bytes(rd.p, rd.end));
       });
     }
-    return *r;
+    return *static_cast<CustomRouter*>(slot.get());
   }
   void add(HostGroup& g, uint32_t op, Fn fn) {
     {

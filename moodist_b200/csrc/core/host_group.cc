@@ -481,6 +481,10 @@ class HostGroupImpl final : public HostGroup {
   }
 
   bool on_engine_thread() const override { return std::this_thread::get_id() == thread_.get_id(); }
+  std::shared_ptr<void>& extension(const std::string& key) override {
+    std::lock_guard<std::mutex> lk(extensions_mu_);
+    return extensions_[key];
+  }
   void post_read(int src, void* local, size_t bytes, uint32_t rkey, uint64_t raddr,
                  std::function<void(bool ok)> done) override {
     transport_.post_read(src, local, bytes, rkey, (uintptr_t)raddr, std::move(done));
@@ -977,6 +981,8 @@ class HostGroupImpl final : public HostGroup {
   std::list<std::shared_ptr<Work>> works_;
   std::map<uint64_t, Announce> announces_;
   std::map<int, uint32_t> next_seq_to_, next_seq_from_;
+  std::mutex extensions_mu_;
+  std::map<std::string, std::shared_ptr<void>> extensions_;  // per-group state of layered subsystems
   std::map<int, std::deque<Mail>> mailbox_;
   // payloads up to this size travel inside their message; larger ones are fetched by the receiver
   static constexpr size_t kEagerSendBytes = 64 << 10;

@@ -103,6 +103,9 @@ class HostGroup {
   virtual void send_message(int dst, uint32_t op, Bytes body) = 0;
   // Post a closure to the engine thread.
   virtual void run_on_engine(std::function<void()> fn) = 0;
+  // A place for subsystems layered on the group to keep per-group state that must die with it (looked up by
+  // name; the reference is valid for the life of the group, the caller synchronises its own use of the object).
+  virtual std::shared_ptr<void>& extension(const std::string& key) = 0;
   virtual bool on_engine_thread() const = 0;
   // One-sided read of a peer's registered memory (engine thread only). Register with MrTable.
   virtual void post_read(int src, void* local, size_t bytes, uint32_t rkey, uint64_t raddr,

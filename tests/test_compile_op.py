@@ -191,3 +191,30 @@ def _dtensors_and_errors(rank, world, port):
 
 def test_compile_op_dtensors_and_argument_errors_world4():
     run_ranks(_dtensors_and_errors, 4, timeout=240)
+
+
+def _successive_groups(rank, world, port):
+    """Four default groups one after the other in the same processes, each used for compile_op and a queue (state a
+    subsystem keeps per group must go with the group: the next one may live at the same address)."""
+    import moodist_b200 as moodist
+
+    for generation in range(4):
+        dist = init_moodist(rank, world, port + generation)
+        pg = moodist.get_backend(device="cpu")
+        op = moodist.compile_op(pg, shape=(world * 2, 4), dtype=torch.float32,
+                                inputs=[{"offset": [rank * 2, 0], "shape": [2, 4]}],
+                                outputs=[{"offset": [0, 0], "shape": [world * 2, 4]}])
+        out = torch.empty(world * 2, 4)
+        op([torch.full((2, 4), float(rank + generation))], [out]).wait()
+        assert out[::2, 0].tolist() == [float(r + generation) for r in range(world)]
+        q = moodist.Queue(pg, location=0, name="per-generation")
+        q.put_object(generation)
+        if rank == 0:
+            assert sorted(q.get_object(timeout=30) for _ in range(world)) == [generation] * world
+        dist.barrier()
+        del op, q, pg
+        dist.destroy_process_group()
+
+
+def test_compile_op_and_queue_on_successive_groups():
+    run_ranks(_successive_groups, 2, timeout=120)
