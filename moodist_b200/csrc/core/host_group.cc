@@ -609,10 +609,18 @@ class HostGroupImpl final : public HostGroup {
     std::unique_lock<std::mutex> lk(wt.mu);
     while (!wt.done) {
       wt.cv.wait_for(lk, std::chrono::milliseconds(200));
-      if (!wt.done && in_error()) {
-        lk.unlock();
-        fail(std::string("moodist: ") + what + " failed: " + error_text());
+      if (wt.done) break;
+      lk.unlock();
+      if (in_error()) fail(std::string("moodist: ") + what + " failed: " + error_text());
+      try {
+        check_interrupt();
+      } catch (...) {
+        // The caller is about to unwind and may free the buffers this operation still refers to: nothing of this
+        // group may touch them any more, and the peers should learn that this rank is not coming.
+        set_error(std::string("interrupted by a signal while waiting for ") + what);
+        throw;
       }
+      lk.lock();
     }
     if (!wt.error.empty()) fail(std::string("moodist: ") + what + " failed: " + wt.error);
   }

@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <functional>
 #include <ctime>
 #include <stdexcept>
 #include <string>
@@ -97,6 +98,18 @@ inline bool env_flag(const char* name) { return env_long(name, 0) != 0; }
 
 inline double now_seconds() {
   return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+// Called by long waits of caller threads between slices, with none of the library's locks held. The Python
+// bindings install a function that lets pending signal handlers run (and throws when one of them raised, e.g.
+// KeyboardInterrupt), so that Ctrl-C ends a collective that will never complete. Set once, before any wait.
+inline std::function<void()>& interrupt_hook() {
+  static std::function<void()> hook;
+  return hook;
+}
+inline void check_interrupt() {
+  auto& hook = interrupt_hook();
+  if (hook) hook();
 }
 
 // How long (microseconds) a thread looks at a completion flag, and the engine thread keeps polling after its last

@@ -39,14 +39,28 @@ struct Sync {
     cv.notify_all();
   }
   // false on timeout
-  bool wait(double timeout_s) {
+  // `interruptible`: between slices pending signal handlers get to run, and what they raise (Ctrl-C) comes out of
+  // here; for waits that may last as long as the caller likes, not for the short round trips to the engine thread
+  bool wait(double timeout_s, bool interruptible = false) {
     spin_until(done_hint, spin_microseconds());
+    const double deadline = timeout_s < 0 ? -1 : now_seconds() + timeout_s;
     std::unique_lock<std::mutex> lk(mu);
-    if (timeout_s < 0) {
-      cv.wait(lk, [&] { return done; });
-      return true;
+    while (!done) {
+      double slice = 0.2;
+      if (deadline >= 0) {
+        double left = deadline - now_seconds();
+        if (left <= 0) return false;
+        slice = std::min(slice, left);
+      }
+      cv.wait_for(lk, std::chrono::duration<double>(slice), [&] { return done; });
+      if (done) break;
+      if (interruptible) {
+        lk.unlock();
+        check_interrupt();
+        lk.lock();
+      }
     }
-    return cv.wait_for(lk, std::chrono::duration<double>(timeout_s), [&] { return done; });
+    return true;
   }
 };
 
@@ -455,14 +469,20 @@ class QueueImpl final : public Queue {
           m_.serve(s);
         }
       });
-      if (!gw->wait(block ? timeout_s : -1)) {
-        // timed out: withdraw on the engine thread, then look once more (the item may have just arrived)
+      std::exception_ptr interrupted;
+      if (!wait_or_note(*gw, block ? timeout_s : -1, interrupted)) {
+        // timed out (or interrupted by a signal): withdraw on the engine thread, then look once more (the item may
+        // have just arrived)
         auto fin = std::make_shared<Sync>();
         m_.g_.run_on_engine([gw, fin] {
           gw->cancelled = true;
           fin->finish();
         });
         fin->wait(-1);
+        if (interrupted) {
+          give_back(gw);
+          std::rethrow_exception(interrupted);
+        }
         std::lock_guard<std::mutex> lk(gw->mu);
         if (!gw->done) return std::nullopt;
       }
@@ -490,7 +510,8 @@ class QueueImpl final : public Queue {
     started->wait(-1);
     // A non-blocking remote get still has to ask the owner; give the round trip a short moment.
     double limit = block ? timeout_s : 0.05;
-    if (!gw->wait(limit)) {
+    std::exception_ptr interrupted;
+    if (!wait_or_note(*gw, limit, interrupted)) {
       auto ack = std::make_shared<Sync>();
       m_.g_.run_on_engine([this, key, ack] {
         m_.stop_acks_[key] = ack;
@@ -506,12 +527,51 @@ class QueueImpl final : public Queue {
         fin->finish();
       });
       fin->wait(-1);
+      if (interrupted) {
+        give_back(gw);
+        std::rethrow_exception(interrupted);
+      }
       std::lock_guard<std::mutex> lk(gw->mu);
       if (!gw->done) return std::nullopt;
     }
     check_error();
     if (queue_size) *queue_size = gw->size_after;
     return std::move(gw->item);
+  }
+
+  // The long wait of a get: false on timeout, and also when a signal handler raised in the meantime (the exception
+  // is kept for the caller to rethrow once the request has been withdrawn).
+  static bool wait_or_note(Sync& s, double timeout_s, std::exception_ptr& interrupted) {
+    try {
+      return s.wait(timeout_s, true);
+    } catch (...) {
+      interrupted = std::current_exception();
+      return false;
+    }
+  }
+
+  // An item that arrived for a get which is being abandoned goes back to the head of the line.
+  void give_back(const std::shared_ptr<GetWait>& gw) {
+    std::shared_ptr<QueueItem> item;
+    {
+      std::lock_guard<std::mutex> lk(gw->mu);
+      if (!gw->done || !gw->item) return;
+      item = std::make_shared<QueueItem>(std::move(*gw->item));
+      gw->item.reset();
+    }
+    bool local = get_target_ == m_.g_.rank();
+    m_.g_.run_on_engine([this, item, local] {
+      if (local) {
+        Storage& st = m_.storage(id_, name_, locations_);
+        auto slot = std::make_shared<Slot>();
+        slot->item = std::move(*item);
+        slot->ready = true;
+        st.items.push_front(slot);
+        m_.serve(st);
+      } else {
+        m_.inbox_[id_].push_front(std::move(*item));
+      }
+    });
   }
 
   size_t qsize() override {
@@ -548,12 +608,13 @@ class QueueImpl final : public Queue {
         else
           st.nonempty_waiters.push_back(s);
       });
-      return s->wait(timeout_s);
+      return s->wait(timeout_s, true);
     }
     double deadline = now_seconds() + (timeout_s < 0 ? 1e18 : timeout_s);
     for (;;) {
       if (qsize() > 0) return true;
       if (now_seconds() >= deadline) return false;
+      check_interrupt();
       std::this_thread::sleep_for(std::chrono::milliseconds(2));
     }
   }

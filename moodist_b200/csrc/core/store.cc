@@ -335,6 +335,16 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
     std::unique_lock<std::mutex> lk(w->mu);
     while (!w->done) {
       w->cv.wait_for(lk, std::chrono::milliseconds(250));  // sliced so signals and shutdown are noticed
+      if (!w->done) {
+        lk.unlock();
+        try {
+          check_interrupt();
+        } catch (...) {
+          post([this, idp] { pending_.erase(*idp); });
+          throw;
+        }
+        lk.lock();
+      }
       if (!w->done && now_seconds() - start > limit) {
         lk.unlock();
         std::string diag = diagnose(dest, what);

@@ -11,11 +11,19 @@
 
 #include "backend.h"
 #include "bindings.h"
+#include "core/log.h"
 
 namespace py = pybind11;
 using namespace moodist;
 
 PYBIND11_MODULE(_C, m) {
+  // Long waits of the core call this between slices (none of its locks held, the GIL released): pending signal
+  // handlers run, and if one raised (KeyboardInterrupt) the wait ends with that exception.
+  moodist::interrupt_hook() = [] {
+    if (!Py_IsInitialized()) return;
+    pybind11::gil_scoped_acquire gil;
+    if (PyErr_CheckSignals() != 0) throw pybind11::error_already_set();
+  };
   m.doc() = "moodist_b200 native extension";
   py::module::import("torch.distributed");
 

@@ -2,6 +2,7 @@
 others' next collective raise with the reason instead of hanging; a silent peer is reported by the heartbeat."""
 
 import os
+import signal
 import time
 
 import pytest
@@ -66,3 +67,47 @@ def _silent_peer(rank, world, port):
 def test_silent_peer_is_reported_by_the_heartbeat():
     statuses = run_ranks(_silent_peer, 2, timeout=90, expect_failure=True, env={"MOODIST_HEARTBEAT_MS": 500})
     assert statuses[0] == "ok", statuses
+
+
+def _interrupts(rank, world, port):
+    """A signal handler that raises (Ctrl-C) ends a wait that would never end by itself: a get on an empty queue, a
+    store wait for a key nobody sets, a receive nobody sends to."""
+    import threading
+    from datetime import timedelta
+
+    import moodist_b200 as moodist
+
+    dist = init_moodist(rank, world, port)
+    pg = moodist.get_backend(device="cpu")
+    store = moodist.TcpStore("127.0.0.1", port + 5, "signals", world, rank, timedelta(seconds=60))
+    q = moodist.Queue(pg, location=0, name="signals")
+    dist.barrier()
+
+    def interrupted(blocking_call):
+        threading.Timer(0.5, lambda: signal.raise_signal(signal.SIGINT)).start()
+        t0 = time.time()
+        with pytest.raises(KeyboardInterrupt):
+            blocking_call()
+        assert time.time() - t0 < 10
+
+    if rank == 0:
+        interrupted(lambda: q.get_object())
+        interrupted(lambda: store.wait(["a key nobody sets"]))
+        q.put_object("later")  # the queue and the store are as usable as before
+        assert q.get_object(timeout=10) == "later"
+        store.set("still", b"works")
+        assert store.get("still") == b"works"
+        # a collective or a receive refers to the caller's buffers: after the interrupt nothing of the group may touch
+        # them any more, so the group goes into its error state and tells the others why
+        interrupted(lambda: dist.recv(torch.empty(4), src=1))
+        with pytest.raises(RuntimeError, match="interrupted by a signal"):
+            dist.all_reduce(torch.ones(2))
+    else:
+        with pytest.raises(RuntimeError, match="rank 0 reported: interrupted by a signal"):
+            for _ in range(100):
+                dist.all_reduce(torch.ones(2))
+                time.sleep(0.1)
+
+
+def test_a_signal_ends_waits_that_would_never_end():
+    run_ranks(_interrupts, 2, timeout=90)
