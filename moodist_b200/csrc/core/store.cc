@@ -504,9 +504,17 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
     }
     if (rank_ == 0) {
       // rendezvous listener on the user's port
+      errno = 0;
       int a = poller_.listen("0.0.0.0", port_, [this](std::shared_ptr<Conn> c) { on_rendezvous_accept(std::move(c)); });
+      int err4 = a <= 0 ? errno : 0;
+      errno = 0;
       int b = poller_.listen("::", port_, [this](std::shared_ptr<Conn> c) { on_rendezvous_accept(std::move(c)); });
-      if (a <= 0 && b <= 0) fail(strf("rank 0 cannot listen on port %d: %s", port_, strerror(errno)));
+      int err6 = b <= 0 ? errno : 0;
+      // A port that somebody else holds for one address family is not ours, even if the other family could be bound:
+      // the other ranks would reach that somebody. (A family this host does not have is no reason to fail.)
+      if (err4 == EADDRINUSE || err6 == EADDRINUSE || (a <= 0 && b <= 0))
+        fail(strf("rank 0 cannot listen on port %d: %s", port_,
+                  strerror(err4 == EADDRINUSE || err6 == EADDRINUSE ? EADDRINUSE : (err4 ? err4 : err6))));
       directory_[0] = my_addresses_;
       directory_uid_[0] = uid_;
       maybe_publish_directory();

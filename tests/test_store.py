@@ -299,3 +299,20 @@ def test_store_left_alive_at_interpreter_exit_still_shuts_down_in_order(tmp_path
     assert procs[0].returncode == 0 and "store was shut down on rank 1" in outs[0], outs
     assert float(outs[0].split("ended after ")[1].split(" s")[0]) < 10, outs
     assert procs[1].returncode == 0, outs
+
+
+def test_rendezvous_port_in_use_is_reported_at_once():
+    import socket
+
+    import moodist_b200 as moodist
+
+    with socket.socket() as holder:
+        holder.bind(("127.0.0.1", 0))
+        holder.listen(1)
+        port = holder.getsockname()[1]
+        t0 = time.time()
+        with pytest.raises(RuntimeError, match=f"rank 0 cannot listen on port {port}: Address already in use"):
+            moodist.TcpStore("127.0.0.1", port, "busy", 2, 0, timedelta(seconds=30))
+        assert time.time() - t0 < 5  # not after the 30 s it would take to notice that nobody joins
+    with pytest.raises(RuntimeError, match="bad rank"):
+        moodist.TcpStore("127.0.0.1", port, "busy", 2, 5, timedelta(seconds=2))
