@@ -758,6 +758,15 @@ class HostGroupImpl final : public HostGroup {
       o.posted = true;
       if (o.bytes == 0) continue;
       const Announce& a = it->second;
+      if (a.base_off + o.remote_off + o.bytes > a.size) {
+        // the peer would refuse the write: say what is wrong instead of "rejected"
+        set_error(strf("%s: the ranks disagree on sizes (rank %d made room for %llu bytes, this rank sends %zu bytes to offset "
+                       "%llu): every rank must pass tensors of the same size and dtype",
+                       w.label.c_str(), o.peer, (unsigned long long)a.size, o.bytes,
+                       (unsigned long long)(a.base_off + o.remote_off)));
+        w.failed = true;
+        continue;
+      }
       ++w.acks_pending;
       Work* wp = &w;
       transport_.post_write(o.peer, o.src, o.bytes, a.key, (uintptr_t)(a.addr + a.base_off + o.remote_off),

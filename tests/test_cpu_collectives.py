@@ -248,3 +248,22 @@ def _many_ranks(rank, world, port):
 def test_sixteen_cpu_ranks():
     """Twice as many ranks as a node has GPUs: the host engine, the multicast queue and compile_op have no such limit."""
     run_ranks(_many_ranks, 16, timeout=300)
+
+
+def _mismatch(rank, world, port, kind):
+    dist = init_moodist(rank, world, port)
+    dist.barrier()
+    if kind == "size":
+        with pytest.raises(RuntimeError, match="the ranks disagree on sizes"):
+            dist.all_reduce(torch.ones(100 if rank == 0 else 200))
+    else:
+        with pytest.raises(RuntimeError, match="mismatched collectives"):
+            if rank == 0:
+                dist.all_reduce(torch.ones(100))
+            else:
+                dist.all_gather_into_tensor(torch.empty(100 * world), torch.ones(100))
+
+
+@pytest.mark.parametrize("kind", ["size", "operation"])
+def test_ranks_that_disagree_get_an_error_not_a_hang(kind):
+    run_ranks(_mismatch, 2, kind, timeout=60)
