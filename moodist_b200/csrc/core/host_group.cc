@@ -667,7 +667,13 @@ class HostGroupImpl final : public HostGroup {
       // operations back to back (queue gets, small collectives, store-like request / reply traffic) then never
       // pays the wake-up of a sleeping thread.
       bool spin = busy || (spin_us_ > 0 && now_seconds() - last_active < spin_us_ * 1e-6);
-      int events = poller_.poll(spin ? 0 : 50);
+      int events = 0;
+      try {
+        events = poller_.poll(spin ? 0 : 50);
+      } catch (const std::exception& e) {
+        // nothing a peer (or a stranger on one of the listening ports) sends may end this thread
+        set_error(strf("engine thread: %s", e.what()));
+      }
       double now = now_seconds();
       if (debug_cpu_ && now - last_iter > 0.001 && busy) log_info("engine: lost %.1f ms between iterations", (now - last_iter) * 1e3);
       last_iter = now;
@@ -678,13 +684,18 @@ class HostGroupImpl final : public HostGroup {
         std::lock_guard<std::mutex> lk(queue_mu_);
         q.swap(queue_);
       }
-      if (q.size() > 1) {
-        // a burst of requests (queue puts, messages): their records leave in one write per connection
-        transport_.hold_sends();
-        for (auto& f : q) f();
+      try {
+        if (q.size() > 1) {
+          // a burst of requests (queue puts, messages): their records leave in one write per connection
+          transport_.hold_sends();
+          for (auto& f : q) f();
+          transport_.release_sends();
+        } else {
+          for (auto& f : q) f();
+        }
+      } catch (const std::exception& e) {
         transport_.release_sends();
-      } else {
-        for (auto& f : q) f();
+        set_error(strf("engine thread: %s", e.what()));
       }
       if (events > 0 || !q.empty() || busy) last_active = now;
       // progress

@@ -367,7 +367,15 @@ void Conn::handle_readable() {
       }
       if (!on_data_) break;
       std::shared_ptr<DataFn> fn = on_data_;
-      size_t used = (*fn)(in_mem_.get() + pos, in_len_ - pos);
+      size_t used;
+      try {
+        used = (*fn)(in_mem_.get() + pos, in_len_ - pos);
+      } catch (const std::exception& e) {
+        // Bytes that do not decode (a stranger on this port, a damaged stream) end this connection, not the thread
+        // that serves all of them.
+        close(std::string("undecodable data: ") + e.what());
+        return;
+      }
       if (used == SIZE_MAX) {
         close("protocol error");
         return;

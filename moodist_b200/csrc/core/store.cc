@@ -463,13 +463,19 @@ class TcpStoreImpl final : public TcpStore, public std::enable_shared_from_this<
     const double spin_s = spin_microseconds() * 1e-6;
     while (!stop_) {
       // keep polling for a moment after any activity: request / reply sequences then skip the thread wake-ups
-      int events = poller_.poll(now_seconds() - last_active < spin_s ? 0 : 20);
+      int events = 0;
       std::deque<std::function<void()>> q;
-      {
-        std::lock_guard<std::mutex> lk(queue_mu_);
-        q.swap(queue_);
+      try {
+        events = poller_.poll(now_seconds() - last_active < spin_s ? 0 : 20);
+        {
+          std::lock_guard<std::mutex> lk(queue_mu_);
+          q.swap(queue_);
+        }
+        for (auto& f : q) f();
+      } catch (const std::exception& e) {
+        // nothing a peer (or a stranger on the rendezvous port) sends may end this thread
+        log_error("TcpStore rank %d: %s", rank_, e.what());
       }
-      for (auto& f : q) f();
       double now = now_seconds();
       if (events > 0 || !q.empty()) last_active = now;
       if (now - last_tick > 0.05) {

@@ -111,3 +111,71 @@ def _interrupts(rank, world, port):
 
 def test_a_signal_ends_waits_that_would_never_end():
     run_ranks(_interrupts, 2, timeout=90)
+
+
+def _listening_ports():
+    """TCP ports this process listens on (from /proc)."""
+    inodes = set()
+    for fd in os.listdir("/proc/self/fd"):
+        try:
+            link = os.readlink(f"/proc/self/fd/{fd}")
+        except OSError:
+            continue
+        if link.startswith("socket:["):
+            inodes.add(link[8:-1])
+    ports = set()
+    for table in ("/proc/net/tcp", "/proc/net/tcp6"):
+        for line in open(table).read().splitlines()[1:]:
+            field = line.split()
+            if field[3] == "0A" and field[9] in inodes:  # state LISTEN
+                ports.add((table.endswith("6"), int(field[1].rsplit(":", 1)[1], 16)))
+    return sorted(ports)
+
+
+def _strangers(rank, world, port):
+    """Whatever arrives on the ports a rank listens on (a port scanner, a stray client, a damaged stream) costs that
+    connection only: the engine and the store keep serving the group."""
+    import socket
+    import struct
+    from datetime import timedelta
+
+    import moodist_b200 as moodist
+
+    dist = init_moodist(rank, world, port)
+    store = moodist.TcpStore("127.0.0.1", port + 9, "strangers", world, rank, timedelta(seconds=30))
+    dist.barrier()
+    if rank == 0:
+        ports = _listening_ports()
+        assert len(ports) >= 3, ports  # the engine's, the store's, the rendezvous port
+        frame = 0x40EA69F4
+        junk = [b"GET / HTTP/1.1\r\n\r\n", os.urandom(64), os.urandom(100_000),
+                struct.pack("<II", frame, 0xFFFFFFFF) + b"x" * 100,   # a frame that claims 4 GiB
+                struct.pack("<II", frame, 8) + os.urandom(8),          # a well-formed frame of noise
+                struct.pack("<II", frame, 0), struct.pack("<II", frame + 1, 4) + b"abcd", struct.pack("<II", frame, 1 << 30)]
+        for v6, p in ports:
+            for payload in junk:
+                try:
+                    with socket.socket(socket.AF_INET6 if v6 else socket.AF_INET) as s:
+                        s.settimeout(1)
+                        s.connect(("::1" if v6 else "127.0.0.1", p))
+                        s.sendall(payload)
+                        time.sleep(0.01)
+                except OSError:
+                    pass
+    dist.barrier()
+    for _ in range(20):
+        t = torch.ones(1000)
+        dist.all_reduce(t)
+        assert float(t[0]) == world
+    store.set(f"after{rank}", b"1")
+    store.wait([f"after{r}" for r in range(world)])
+    q = moodist.Queue(moodist.get_backend(device="cpu"), 0, name="after-the-noise")
+    q.put_object(rank)
+    if rank == 0:
+        assert sorted(q.get_object(timeout=10) for _ in range(world)) == list(range(world))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_garbage_on_the_listening_ports_is_survived():
+    run_ranks(_strangers, 2, timeout=120)
