@@ -46,6 +46,8 @@ struct PyQueue {
   std::map<uint32_t, std::vector<CudaItemDescriptor>> tx_items;  // CUDA items of open transactions
 
   std::shared_ptr<PyQueueWork> put(const at::Tensor& tensor, uint32_t transaction, bool wait_on_destroy) {
+    TORCH_CHECK(tensor.layout() == at::kStrided, "moodist.Queue: only dense tensors can be queued, not ", tensor.layout(),
+                " (use put_object for anything else)");
     if (tensor.is_cuda()) {
       if (CudaP2P* p2p = owner->cudaP2P(tensor.get_device())) {
         // Stream-ordered: nothing waits for the GPU here. The item that travels is a descriptor; whoever gets it

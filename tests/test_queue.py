@@ -201,6 +201,12 @@ def _edges(rank, world, port):
     dist.barrier()
     with pytest.raises(RuntimeError, match="not a rank"):
         moodist.Queue(pg, location=world + 3)
+    with pytest.raises(RuntimeError, match="only dense tensors"):
+        dq.put_tensor(torch.arange(4).to_sparse())
+    if rank == 1:
+        dq.put_object(torch.arange(4).to_sparse())  # travels as an object instead
+    if rank == 0:
+        assert torch.equal(dq.get_object(timeout=20).to_dense(), torch.arange(4))
     # a queue handle dropped while items sit in it leaves the group usable
     doomed = moodist.Queue(pg, location=0, name="doomed")
     if rank == 1:
