@@ -268,3 +268,85 @@ def _mismatch(rank, world, port, kind):
 @pytest.mark.parametrize("kind", ["size", "operation"])
 def test_ranks_that_disagree_get_an_error_not_a_hang(kind):
     run_ranks(_mismatch, 2, kind, timeout=60)
+
+
+def _random_operations(rank, world, port, seed, count):
+    """Every rank draws the same sequence of operations, roots, sizes and peers from one seed and checks every
+    result: collectives of all kinds and sizes, point-to-point with either end posted first, a multicast queue,
+    a compiled redistribution, back to back in random order."""
+    import random
+
+    import moodist_b200 as moodist
+
+    dist = init_moodist(rank, world, port)
+    pg = moodist.get_backend(device="cpu")
+    q = moodist.Queue(pg, location=range(world), name="random-operations")
+    rows = 3
+    reshard = moodist.compile_op(pg, shape=(rows * world, 5), dtype=torch.float32,
+                                 inputs=[{"offset": [rank * rows, 0], "shape": [rows, 5]}],
+                                 outputs=[{"offset": [0, 0], "shape": [rows * world, 5]}])
+    rng = random.Random(seed)
+    kinds = ["all_reduce", "all_reduce_max", "all_gather", "reduce_scatter", "broadcast", "all_to_all", "p2p", "queue",
+             "compile_op", "gather", "barrier"]
+    for i in range(count):
+        kind = rng.choice(kinds)
+        n = rng.choice([1, 7, 100, 4097, 70_001, 300_000])
+        where = (i, kind, n)
+        if kind == "all_reduce":
+            t = torch.full((n,), float(rank + i))
+            dist.all_reduce(t)
+            assert float(t[-1]) == sum(r + i for r in range(world)), where
+        elif kind == "all_reduce_max":
+            t = torch.full((n,), rank + i, dtype=torch.int64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            assert int(t[0]) == world - 1 + i, where
+        elif kind == "all_gather":
+            out = torch.empty(world * n)
+            dist.all_gather_into_tensor(out, torch.full((n,), float(rank * 3 + i)))
+            assert [float(out[r * n]) for r in range(world)] == [float(r * 3 + i) for r in range(world)], where
+        elif kind == "reduce_scatter":
+            out = torch.empty(n)
+            dist.reduce_scatter_tensor(out, torch.full((world * n,), float(rank)), op=dist.ReduceOp.AVG)
+            assert abs(float(out[0]) - (world - 1) / 2) < 1e-5, where
+        elif kind == "broadcast":
+            root = rng.randrange(world)
+            t = torch.full((n,), float(rank))
+            dist.broadcast(t, src=root)
+            assert float(t[-1]) == root, where
+        elif kind == "all_to_all":
+            send = torch.cat([torch.full((d + 1,), float(rank * 100 + d)) for d in range(world)])
+            recv = torch.empty(world * (rank + 1))
+            dist.all_to_all_single(recv, send, output_split_sizes=[rank + 1] * world, input_split_sizes=[d + 1 for d in range(world)])
+            assert float(recv[0]) == rank and float(recv[-1]) == (world - 1) * 100 + rank, where
+        elif kind == "p2p":
+            shift = rng.randrange(1, world)
+            dst, src = (rank + shift) % world, (rank - shift) % world
+            got = torch.empty(n)
+            ops = [dist.P2POp(dist.isend, torch.full((n,), float(rank + i)), dst, tag=i), dist.P2POp(dist.irecv, got, src, tag=i)]
+            for w in dist.batch_isend_irecv(ops if rng.random() < 0.5 else ops[::-1]):
+                w.wait()
+            assert float(got[-1]) == src + i, where
+        elif kind == "queue":
+            who = rng.randrange(world)
+            if rank == who:
+                q.put_object((i, who))
+            assert q.get_object(timeout=60) == (i, who), where
+        elif kind == "compile_op":
+            out = torch.empty(rows * world, 5)
+            reshard([torch.full((rows, 5), float(rank + i))], [out]).wait()
+            assert out[::rows, 0].tolist() == [float(r + i) for r in range(world)], where
+        elif kind == "gather":
+            root = rng.randrange(world)
+            parts = [torch.empty(3) for _ in range(world)] if rank == root else None
+            dist.gather(torch.full((3,), float(rank)), parts, dst=root)
+            if rank == root:
+                assert [float(x[0]) for x in parts] == [float(r) for r in range(world)], where
+        else:
+            dist.barrier()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,seed", [(4, 1), (3, 3)])
+def test_random_sequences_of_operations(world, seed):
+    run_ranks(_random_operations, world, seed, 250, timeout=300)
