@@ -82,6 +82,7 @@ class Writer {
   Bytes out;
 
   void raw(const void* p, size_t n) {
+    if (n == 0) return;  // p may be null then
     const uint8_t* b = static_cast<const uint8_t*>(p);
     out.insert(out.end(), b, b + n);
   }
@@ -157,7 +158,10 @@ class Reader {
     p += n;
     return r;
   }
-  void raw(void* dst, size_t n) { std::memcpy(dst, take(n), n); }
+  void raw(void* dst, size_t n) {
+    const uint8_t* src = take(n);
+    if (n) std::memcpy(dst, src, n);  // an empty vector's data() may be null, which memcpy must not be given
+  }
 
   template <class... T>
   Reader& operator()(T&... v) {

@@ -127,6 +127,48 @@ static void test_wire() {
   CHECK(from_hex(to_hex(b)) == b);
 }
 
+// Decoding bytes nobody encoded: damaged copies of a valid message, cut copies, and noise. Every attempt either
+// succeeds or throws WireError; under the address sanitizer a read past the buffer or a huge allocation driven by a
+// length field would show.
+static void test_wire_fuzz() {
+  Bytes good = encode((uint32_t)7, std::string("hello world"), std::vector<uint16_t>{1, 2, 3, 4}, true, std::optional<uint8_t>(7),
+                      std::variant<int32_t, std::string>(std::string("z")), std::map<std::string, int32_t>{{"k", -1}, {"l", 2}},
+                      std::vector<std::string>{"a", "bb"});
+  uint64_t state = 12345;
+  auto rnd = [&] {
+    state = state * 6364136223846793005ull + 1442695040888963407ull;
+    return (uint32_t)(state >> 33);
+  };
+  int decoded = 0, refused = 0;
+  for (int round = 0; round < 20000; ++round) {
+    Bytes b = good;
+    int mode = round % 3;
+    if (mode == 0) {
+      for (int k = 0; k < 1 + (int)(rnd() % 3); ++k) b[rnd() % b.size()] = (uint8_t)rnd();
+    } else if (mode == 1) {
+      b.resize(rnd() % (b.size() + 1));
+    } else {
+      b.resize(rnd() % 64);
+      for (auto& x : b) x = (uint8_t)rnd();
+    }
+    try {
+      uint32_t a;
+      std::string s;
+      std::vector<uint16_t> v;
+      bool flag;
+      std::optional<uint8_t> o;
+      std::variant<int32_t, std::string> var;
+      std::map<std::string, int32_t> m;
+      std::vector<std::string> vs;
+      decode_exact(b, a, s, v, flag, o, var, m, vs);
+      ++decoded;
+    } catch (const WireError&) {
+      ++refused;
+    }
+  }
+  CHECK(decoded + refused == 20000 && refused > 10000);
+}
+
 static void test_mr_table() {
   std::vector<uint8_t> buf(1000);
   uint32_t k = MrTable::instance().add(buf.data(), buf.size());
@@ -534,6 +576,7 @@ int main() {
   test_host_group(4);
   test_heap_request();
   test_wire();
+  test_wire_fuzz();
   test_planner_random();
   test_topology();
   test_mr_table();
