@@ -224,3 +224,75 @@ def _edges(rank, world, port):
 
 def test_queue_edge_cases_world3():
     run_ranks(_edges, 3, timeout=240)
+
+
+def _producers_and_getters(rank, world, port):
+    """Every rank produces 300 items (objects, tensors, transactions of 1-5 items, in random alternation) into a queue
+    on rank 0 while rank 0 (locally) and rank 2 (as a remote getter) both consume: nothing is lost, nothing arrives
+    twice, and each getter sees each producer's items in the order they were put."""
+    import random
+    import threading
+
+    dist = init_moodist(rank, world, port)
+    import moodist_b200 as moodist
+
+    pg = moodist.get_backend(device="cpu")
+    q = moodist.Queue(pg, location=0, name="many-to-two")
+    results = moodist.Queue(pg, location=0, name="what-the-getters-saw")
+    count, getters = 300, (0, 2)
+    seen, stop = [], threading.Event()
+
+    def consume():
+        while not stop.is_set():
+            try:
+                t = q.get_tensor(timeout=0.2)
+            except Empty:
+                continue
+            seen.append(moodist.deserialize(t) if t.dtype == torch.uint8 else tuple(t.tolist()))
+
+    consumer = None
+    if rank in getters:
+        consumer = threading.Thread(target=consume)
+        consumer.start()
+    rng = random.Random(rank)
+    i = 0
+    while i < count:
+        draw = rng.random()
+        if draw < 0.3:
+            k = min(count - i, rng.randint(1, 5))
+            with q.transaction() as tx:
+                for j in range(k):
+                    tx.put_object((rank, i + j))
+            i += k
+        elif draw < 0.65:
+            q.put_object((rank, i))
+            i += 1
+        else:
+            q.put_tensor(torch.tensor([rank, i]))
+            i += 1
+    dist.barrier()
+    deadline = time.time() + 60
+    while rank == 0 and q.qsize() > 0 and time.time() < deadline:
+        time.sleep(0.05)
+    dist.barrier()
+    time.sleep(0.5)  # a getter may hold one more item that was already on its way
+    stop.set()
+    if consumer is not None:
+        consumer.join()
+        results.put_object((rank, seen))
+    if rank == 0:
+        everything = []
+        for _ in getters:
+            getter, items = results.get_object(timeout=60)
+            last = {}
+            for producer, number in items:
+                assert last.get(producer, -1) < number, (getter, producer, number, last.get(producer))
+                last[producer] = number
+            everything += items
+        assert sorted(everything) == [(p, n) for p in range(world) for n in range(count)], len(everything)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_many_producers_two_getters_exactly_once_in_order():
+    run_ranks(_producers_and_getters, 4, timeout=240)
