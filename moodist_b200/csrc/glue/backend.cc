@@ -166,6 +166,14 @@ std::pair<int, double> reduce_code(const c10d::ReduceOp& op) {
   }
 }
 
+// A bool tensor holds bytes 0 and 1, and must keep doing so: its "sum" is the logical or, its product the and.
+int bool_op(at::ScalarType t, int op) {
+  if (t != at::kBool) return op;
+  if (op == MB_SUM || op == MB_AVG || op == MB_PREMUL_SUM || op == 6 /* BOR */) return MB_MAX;
+  if (op == 2 /* PRODUCT */ || op == 5 /* BAND */) return MB_MIN;
+  return op;
+}
+
 void check_cuda_op(int op) {
   TORCH_CHECK(op == MB_SUM || op == MB_AVG || op == MB_MIN || op == MB_MAX || op == MB_PREMUL_SUM,
               "moodist: CUDA tensors support SUM, AVG, MIN, MAX and PREMUL_SUM (PRODUCT and the bitwise reductions "
@@ -387,6 +395,7 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::_reduce_scatter_base(at::Tensor& 
   TORCH_CHECK(output.scalar_type() == input.scalar_type(), "moodist: reduce_scatter dtype mismatch");
   TORCH_CHECK(input.numel() == output.numel() * size_, "moodist: reduce_scatter input must be world_size x output");
   auto [op, premul] = reduce_code(opts.reduceOp);
+  op = bool_op(input.scalar_type(), op);
   int dt = dtype_code(input.scalar_type());
   if (input.is_cuda()) {
     check_cuda_op(op);
@@ -444,6 +453,7 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::allreduce(std::vector<at::Tensor>
   at::Tensor& t = tensors[0];
   check_contig(t, "all_reduce");
   auto [op, premul] = reduce_code(opts.reduceOp);
+  op = bool_op(t.scalar_type(), op);
   int dt = dtype_code(t.scalar_type());
   if (t.is_cuda()) {
     check_cuda_op(op);

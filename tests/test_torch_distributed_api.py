@@ -130,6 +130,16 @@ def _surface(rank, world, port):
     out = torch.empty(2, dtype=torch.uint8)
     dist.reduce_scatter_tensor(out, torch.full((2 * world,), 1 << rank, dtype=torch.uint8), op=dist.ReduceOp.BOR)
     assert out.tolist() == [7, 7]
+    # bool tensors keep bytes 0 / 1: their sum is "any", their product "all"; complex numbers reduce as pairs of reals
+    anyone = torch.tensor([True, False, rank == 0, rank == 1])
+    dist.all_reduce(anyone)
+    assert anyone.tolist() == [True, False, True, True] and anyone.view(torch.uint8).tolist() == [1, 0, 1, 1]
+    everyone = torch.tensor([True, False, rank == 0, rank != 5])
+    dist.all_reduce(everyone, op=dist.ReduceOp.PRODUCT)
+    assert everyone.tolist() == [True, False, False, True]
+    z = torch.full((4,), complex(rank + 1, -rank))
+    dist.all_reduce(z)
+    assert z[0] == complex(sum(range(1, world + 1)), -sum(range(world)))
 
     # ---- empty tensors ----
     dist.all_reduce(torch.empty(0))
