@@ -179,7 +179,8 @@ def test_torch_distributed_surface_world3():
 
 
 def _wrappers(rank, world, port):
-    """torch's own parallel wrappers running over the backend: DDP, ZeroRedundancyOptimizer, DTensor, fully_shard."""
+    """torch's own parallel wrappers running over the backend: DDP, ZeroRedundancyOptimizer, DTensor, fully_shard,
+    distributed checkpointing."""
     dist = init_moodist(rank, world, port)
     from torch.distributed.device_mesh import init_device_mesh
     from torch.distributed.fsdp import fully_shard
@@ -249,6 +250,23 @@ def _wrappers(rank, world, port):
             p -= 0.1 * p.grad
     for p, q in zip(fs.parameters(), ref.parameters()):
         torch.testing.assert_close(p.full_tensor(), q, rtol=1e-5, atol=1e-6)
+
+    # torch.distributed.checkpoint: saved sharded by rows, loaded sharded by columns
+    import shutil
+    import tempfile
+
+    import torch.distributed.checkpoint as dcp
+
+    where = [tempfile.mkdtemp(prefix="moodist-dcp-") if rank == 0 else None]
+    dist.broadcast_object_list(where, src=0)
+    table = torch.arange(24.0).view(6, 4)
+    dcp.save({"w": distribute_tensor(table, mesh, [Shard(0)]), "step": torch.tensor(7)}, checkpoint_id=where[0])
+    loaded = {"w": distribute_tensor(torch.zeros(6, 4), mesh, [Shard(1)]), "step": torch.tensor(0)}
+    dcp.load(loaded, checkpoint_id=where[0])
+    assert torch.equal(loaded["w"].full_tensor(), table) and int(loaded["step"]) == 7
+    dist.barrier()
+    if rank == 0:
+        shutil.rmtree(where[0], ignore_errors=True)
 
     dist.barrier()
     dist.destroy_process_group()
