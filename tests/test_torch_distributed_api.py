@@ -180,7 +180,7 @@ def test_torch_distributed_surface_world3():
 
 def _wrappers(rank, world, port):
     """torch's own parallel wrappers running over the backend: DDP, ZeroRedundancyOptimizer, DTensor, fully_shard,
-    distributed checkpointing."""
+    distributed checkpointing, pipeline schedules."""
     dist = init_moodist(rank, world, port)
     from torch.distributed.device_mesh import init_device_mesh
     from torch.distributed.fsdp import fully_shard
@@ -267,6 +267,30 @@ def _wrappers(rank, world, port):
     dist.barrier()
     if rank == 0:
         shutil.rmtree(where[0], ignore_errors=True)
+
+    # torch.distributed.pipelining: one layer per rank, GPipe and 1F1B schedules (receives are posted before sends)
+    from torch.distributed.pipelining import PipelineStage, Schedule1F1B, ScheduleGPipe
+
+    torch.manual_seed(3)
+    layers = [torch.nn.Linear(8, 8) for _ in range(world)]
+    stage = PipelineStage(layers[rank], rank, world, torch.device("cpu"))
+    batch = torch.randn(8, 8, generator=torch.Generator().manual_seed(4))
+    for schedule_class in (ScheduleGPipe, Schedule1F1B):
+        schedule = schedule_class(stage, n_microbatches=4, loss_fn=lambda y, t: ((y - t) ** 2).mean())
+        losses = []
+        if rank == 0:
+            schedule.step(batch)
+        elif rank == world - 1:
+            schedule.step(target=torch.zeros(8, 8), losses=losses)
+        else:
+            schedule.step()
+        if rank == world - 1:
+            whole = batch
+            for layer in layers:
+                whole = layer(whole)
+            want = [(chunk**2).mean().item() for chunk in whole.chunk(4)]
+            assert all(abs(a.item() - b) < 1e-5 for a, b in zip(losses, want)), (losses, want)
+        dist.barrier()
 
     dist.barrier()
     dist.destroy_process_group()
