@@ -180,7 +180,7 @@ def test_torch_distributed_surface_world3():
 
 def _wrappers(rank, world, port):
     """torch's own parallel wrappers running over the backend: DDP, ZeroRedundancyOptimizer, DTensor, fully_shard,
-    distributed checkpointing, pipeline schedules."""
+    distributed checkpointing, tensor parallelism, pipeline schedules."""
     dist = init_moodist(rank, world, port)
     from torch.distributed.device_mesh import init_device_mesh
     from torch.distributed.fsdp import fully_shard
@@ -267,6 +267,29 @@ def _wrappers(rank, world, port):
     dist.barrier()
     if rank == 0:
         shutil.rmtree(where[0], ignore_errors=True)
+
+    # tensor parallelism through DTensor: column-parallel up, row-parallel down, forward and backward
+    from torch.distributed.tensor.parallel import ColwiseParallel, RowwiseParallel, parallelize_module
+
+    class MLP(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.up = torch.nn.Linear(16, 32)
+            self.down = torch.nn.Linear(32, 16)
+
+        def forward(self, x):
+            return self.down(torch.relu(self.up(x)))
+
+    torch.manual_seed(5)
+    whole_mlp, split_mlp = MLP(), MLP()
+    split_mlp.load_state_dict(whole_mlp.state_dict())
+    split_mlp = parallelize_module(split_mlp, mesh, {"up": ColwiseParallel(), "down": RowwiseParallel()})
+    x = torch.randn(4, 16, generator=torch.Generator().manual_seed(6))
+    y_split, y_whole = split_mlp(x), whole_mlp(x)
+    y_split.sum().backward()
+    y_whole.sum().backward()
+    torch.testing.assert_close(y_split, y_whole, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(split_mlp.up.weight.grad.full_tensor(), whole_mlp.up.weight.grad, rtol=1e-5, atol=1e-5)
 
     # torch.distributed.pipelining: one layer per rank, GPipe and 1F1B schedules (receives are posted before sends)
     from torch.distributed.pipelining import PipelineStage, Schedule1F1B, ScheduleGPipe
