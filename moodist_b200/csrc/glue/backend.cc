@@ -377,6 +377,34 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::allgather(std::vector<std::vector
   return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::ALLGATHER, outs);
 }
 
+c10::intrusive_ptr<c10d::Work> MoodistBackend::allgather_coalesced(std::vector<std::vector<at::Tensor>>& output_lists,
+                                                                   std::vector<at::Tensor>& inputs,
+                                                                   const c10d::AllgatherOptions& opts) {
+  TORCH_CHECK(output_lists.size() == inputs.size(), "moodist: all_gather_coalesced list size mismatch");
+  c10::intrusive_ptr<c10d::Work> last;
+  for (size_t i = 0; i < inputs.size(); ++i) {
+    std::vector<std::vector<at::Tensor>> outs{output_lists[i]};
+    std::vector<at::Tensor> in{inputs[i]};
+    last = allgather(outs, in, opts);
+  }
+  if (!last) return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::ALLGATHER_COALESCED, std::vector<at::Tensor>{});
+  return last;
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::endCoalescing() {
+  bool on_gpu = false;
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    on_gpu = cuda_ != nullptr;
+  }
+  if (on_gpu) {
+    c10::cuda::CUDAGuard guard((c10::DeviceIndex)cuda_->device());
+    return c10::make_intrusive<CudaWork>(rank_, c10d::OpType::COALESCED, std::vector<at::Tensor>{},
+                                         c10::cuda::getCurrentCUDAStream());
+  }
+  return c10::make_intrusive<DoneWork>(rank_, c10d::OpType::COALESCED, std::vector<at::Tensor>{});
+}
+
 c10::intrusive_ptr<c10d::Work> MoodistBackend::allgather_into_tensor_coalesced(std::vector<at::Tensor>& outputs,
                                                                                std::vector<at::Tensor>& inputs,
                                                                                const c10d::AllgatherOptions& opts) {

@@ -56,6 +56,13 @@ class MoodistBackend final : public c10d::Backend {
                                            const c10d::AllgatherOptions& opts = c10d::AllgatherOptions()) override;
   c10::intrusive_ptr<c10d::Work> _allgather_base(at::Tensor& output, at::Tensor& input,
                                                  const c10d::AllgatherOptions& opts = c10d::AllgatherOptions()) override;
+  c10::intrusive_ptr<c10d::Work> allgather_coalesced(std::vector<std::vector<at::Tensor>>& output_lists,
+                                                     std::vector<at::Tensor>& inputs,
+                                                     const c10d::AllgatherOptions& opts = c10d::AllgatherOptions()) override;
+  // Operations run as they are issued (in stream order on a GPU), so a coalescing block has nothing to hold back:
+  // it starts nothing and ends with a completed work.
+  void startCoalescing() override {}
+  c10::intrusive_ptr<c10d::Work> endCoalescing() override;
   c10::intrusive_ptr<c10d::Work> allgather_into_tensor_coalesced(
       std::vector<at::Tensor>& outputs, std::vector<at::Tensor>& inputs,
       const c10d::AllgatherOptions& opts = c10d::AllgatherOptions()) override;

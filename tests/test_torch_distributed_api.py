@@ -66,6 +66,25 @@ def _surface(rank, world, port):
     dist.all_to_all(outs, ins)
     assert [float(o[0]) for o in outs] == [float(s * 10 + rank) for s in range(world)]
 
+    # ---- coalesced forms, the coalescing manager, functional collectives ----
+    pair = [torch.ones(3), torch.ones(5)]
+    dist.all_reduce_coalesced(pair)
+    assert float(pair[1][0]) == world
+    lists = [[torch.empty(3) for _ in range(world)], [torch.empty(2) for _ in range(world)]]
+    dist.all_gather_coalesced(lists, [torch.full((3,), float(rank)), torch.full((2,), float(rank))])
+    assert float(lists[1][world - 1][0]) == world - 1 and float(lists[0][1][2]) == 1.0
+    a, b = torch.ones(4), torch.ones(8) * 2
+    with dist._coalescing_manager(device=torch.device("cpu")):
+        dist.all_reduce(a)
+        dist.all_reduce(b)
+    assert float(a[0]) == world and float(b[0]) == 2 * world
+    import torch.distributed._functional_collectives as funcol
+
+    assert float(funcol.all_reduce(torch.ones(4), "sum", dist.group.WORLD)[0]) == world
+    assert funcol.all_gather_tensor(torch.full((2,), float(rank)), 0, dist.group.WORLD).shape == (2 * world,)
+    assert float(funcol.reduce_scatter_tensor(torch.ones(2 * world), "avg", 0, dist.group.WORLD)[0]) == 1.0
+    assert float(funcol.all_to_all_single(torch.arange(world, dtype=torch.float32), None, None, dist.group.WORLD)[0]) == rank
+
     # ---- rooted collectives ----
     t = torch.full((4,), float(rank + 1))
     dist.reduce(t, dst=1)
