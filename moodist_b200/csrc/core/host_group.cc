@@ -31,6 +31,7 @@ struct Waiter {
   bool done = false;
   std::atomic<bool> done_hint{false};  // set with `done`; what a waiter polls before it goes to sleep
   std::string error;
+  std::atomic<int> source{-1};  // receives: the rank the message came from
   void finish(std::string err = {}) {
     std::lock_guard<std::mutex> lk(mu);
     done = true;
@@ -427,6 +428,7 @@ class HostGroupImpl final : public HostGroup {
   bool recv_done(const std::shared_ptr<void>& posted) override {
     return std::static_pointer_cast<Waiter>(posted)->done_hint.load(std::memory_order_acquire);
   }
+  int recv_source(const std::shared_ptr<void>& posted) override { return std::static_pointer_cast<Waiter>(posted)->source.load(); }
 
   // ---------------------------------------------------------------------------------------------
   // messages
@@ -914,38 +916,47 @@ class HostGroupImpl final : public HostGroup {
 
   void match_recvs() {
     for (auto it = pending_recvs_.begin(); it != pending_recvs_.end();) {
-      auto& box = mailbox_[it->src];
-      bool matched = false;
-      for (auto m = box.begin(); m != box.end(); ++m) {
-        if (m->tag != it->tag) continue;
-        size_t have = m->offer ? (size_t)m->bytes : m->data.size();
-        if (have != it->bytes) {
-          std::string text = strf("recv size mismatch: expected %zu bytes, message has %zu", it->bytes, have);
-          if (m->offer) send_message(it->src, kOpSendTaken, encode(m->id, false, "the receiver's " + text));
-          it->waiter->finish(text);
-        } else if (m->offer) {
-          // fetch the payload out of the sender's memory into the caller's; both ends learn how it went
-          int src = it->src;
-          uint32_t id = m->id;
-          auto waiter = it->waiter;
-          auto keep = it->keep;
-          post_read(src, it->data, it->bytes, m->key, m->addr, [this, src, id, waiter, keep](bool ok) {
-            send_message(src, kOpSendTaken, encode(id, ok, std::string(ok ? "" : "the receiver could not read the payload")));
-            waiter->finish(ok ? std::string() : "reading the sender's payload failed");
-          });
-        } else {
-          if (it->bytes) memcpy(it->data, m->data.data(), it->bytes);
-          it->waiter->finish();
-        }
-        box.erase(m);
-        matched = true;
-        break;
-      }
-      if (matched)
+      if (serve_recv(*it))
         it = pending_recvs_.erase(it);
       else
         ++it;
     }
+  }
+
+  // Hands the oldest message with the request's tag to it: from its source, or (source -1: anybody) from the first
+  // rank that has one. False when nothing matches yet.
+  bool serve_recv(PendingRecv& want) {
+    const int first = want.src < 0 ? 0 : want.src, last = want.src < 0 ? world_ - 1 : want.src;
+    for (int from = first; from <= last; ++from) {
+      auto box_it = mailbox_.find(from);
+      if (box_it == mailbox_.end()) continue;
+      auto& box = box_it->second;
+      for (auto m = box.begin(); m != box.end(); ++m) {
+        if (m->tag != want.tag) continue;
+        want.waiter->source.store(from);
+        size_t have = m->offer ? (size_t)m->bytes : m->data.size();
+        if (have != want.bytes) {
+          std::string text = strf("recv size mismatch: expected %zu bytes, message has %zu", want.bytes, have);
+          if (m->offer) send_message(from, kOpSendTaken, encode(m->id, false, "the receiver's " + text));
+          want.waiter->finish(text);
+        } else if (m->offer) {
+          // fetch the payload out of the sender's memory into the caller's; both ends learn how it went
+          uint32_t id = m->id;
+          auto waiter = want.waiter;
+          auto keep = want.keep;
+          post_read(from, want.data, want.bytes, m->key, m->addr, [this, from, id, waiter, keep](bool ok) {
+            send_message(from, kOpSendTaken, encode(id, ok, std::string(ok ? "" : "the receiver could not read the payload")));
+            waiter->finish(ok ? std::string() : "reading the sender's payload failed");
+          });
+        } else {
+          if (want.bytes) memcpy(want.data, m->data.data(), want.bytes);
+          want.waiter->finish();
+        }
+        box.erase(m);
+        return true;
+      }
+    }
+    return false;
   }
 
   // Liveness: ping up to 16 neighbours on each side; silence for 3 intervals is logged, for 6 it puts

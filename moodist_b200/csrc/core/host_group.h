@@ -96,6 +96,8 @@ class HostGroup {
   virtual std::shared_ptr<void> recv_post(void* data, size_t bytes, int src, uint32_t tag, std::shared_ptr<void> keep) = 0;
   virtual void recv_wait(const std::shared_ptr<void>& posted) = 0;
   virtual bool recv_done(const std::shared_ptr<void>& posted) = 0;
+  // `src` = -1 in recv_post takes the first matching message of any rank; after recv_wait this says whose it was.
+  virtual int recv_source(const std::shared_ptr<void>& posted) = 0;
 
   // ---- two-sided engine messages for subsystems layered on top (Queue, compile_op) ----
   using Handler = std::function<void(int src, Reader& body)>;  // runs on the engine thread

@@ -113,6 +113,8 @@ class RecvWork final : public c10d::Work {
   void synchronize() override { wait(std::chrono::milliseconds(0)); }
   std::vector<at::Tensor> result() override { return outputs_; }
   c10::intrusive_ptr<c10::ivalue::Future> getFuture() override { return future_; }
+  // of a completed receive: the rank the message came from (what a receive from anybody wants to know)
+  int sourceRank() const override { return send_ ? -1 : owner_->hostGroup().recv_source(posted_); }
 
  private:
   std::mutex mu_;
@@ -778,6 +780,18 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::recv(std::vector<at::Tensor>& ten
   }
   std::shared_ptr<void> posted;
   MOODIST_TRANSLATE(posted = hostGroup().recv_post(t.data_ptr(), (size_t)t.nbytes(), srcRank, (uint32_t)tag,
+                                                   std::make_shared<at::Tensor>(t));)
+  return c10::make_intrusive<RecvWork>(rank_, tensors, self, posted, nullptr);
+}
+
+c10::intrusive_ptr<c10d::Work> MoodistBackend::recvAnysource(std::vector<at::Tensor>& tensors, int tag) {
+  TORCH_CHECK(tensors.size() == 1, "moodist: recv takes one tensor");
+  at::Tensor t = tensors[0];
+  check_contig(t, "recv tensor");
+  TORCH_CHECK(!t.is_cuda(), "moodist: a receive from any rank is served for CPU tensors (name the source for a CUDA tensor)");
+  auto self = c10::intrusive_ptr<MoodistBackend>::unsafe_reclaim_from_nonowning(this);
+  std::shared_ptr<void> posted;
+  MOODIST_TRANSLATE(posted = hostGroup().recv_post(t.data_ptr(), (size_t)t.nbytes(), -1, (uint32_t)tag,
                                                    std::make_shared<at::Tensor>(t));)
   return c10::make_intrusive<RecvWork>(rank_, tensors, self, posted, nullptr);
 }

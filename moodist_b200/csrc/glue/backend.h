@@ -91,6 +91,7 @@ class MoodistBackend final : public c10d::Backend {
   // host thread (cuda_p2p.h) once the group has run a CUDA collective, through host memory before that
   c10::intrusive_ptr<c10d::Work> send(std::vector<at::Tensor>& tensors, int dstRank, int tag) override;
   c10::intrusive_ptr<c10d::Work> recv(std::vector<at::Tensor>& tensors, int srcRank, int tag) override;
+  c10::intrusive_ptr<c10d::Work> recvAnysource(std::vector<at::Tensor>& tensors, int tag) override;
 
   // ---- moodist-specific surface (reference: wrapper/module.cc:836-849) ----
   std::string moodistName() const { return name_; }

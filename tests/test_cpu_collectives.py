@@ -170,6 +170,22 @@ def _receive_first(rank, world, port):
     if rank == 1:
         with pytest.raises(RuntimeError, match="size mismatch"):
             dist.recv(torch.empty(5), 0, tag=11)
+    # a receive that names no source takes the first message of any rank and says whose it was
+    if rank == 0:
+        senders = set()
+        for _ in range(world - 1):
+            box = torch.empty(3)
+            who = dist.recv(box, tag=40)
+            assert float(box[0]) == who and who not in senders
+            senders.add(who)
+        assert senders == set(range(1, world))
+        big_box = torch.empty(200_000)
+        assert dist.recv(big_box, tag=41) == world - 1 and float(big_box[-1]) == 7.0
+    else:
+        dist.send(torch.full((3,), float(rank)), 0, tag=40)
+        if rank == world - 1:
+            dist.send(torch.full((200_000,), 7.0), 0, tag=41)
+    dist.barrier()
     # large payloads are not copied into a message: the receiver fetches them from the sender's tensor. Sends posted
     # before receives and the other way round, several in flight, then the blocking forms
     n = 300_000
