@@ -722,7 +722,7 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::send(std::vector<at::Tensor>& ten
   TORCH_CHECK(tensors.size() == 1, "moodist: send takes one tensor");
   TORCH_CHECK(dstRank >= 0 && dstRank < size_ && dstRank != rank_, "moodist: send: bad destination rank ", dstRank);
   at::Tensor t = tensors[0];
-  check_contig(t, "send tensor");
+  check_contig(t, "send");
   if (t.is_cuda()) {
     if (CudaP2P* p2p = cudaP2P(t.get_device())) {
       // Nothing here waits for the GPU: the bytes become readable to the receiver in stream order, a flag kernel
@@ -748,7 +748,7 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::recv(std::vector<at::Tensor>& ten
   TORCH_CHECK(tensors.size() == 1, "moodist: recv takes one tensor");
   TORCH_CHECK(srcRank >= 0 && srcRank < size_ && srcRank != rank_, "moodist: recv: bad source rank ", srcRank);
   at::Tensor t = tensors[0];
-  check_contig(t, "recv tensor");
+  check_contig(t, "recv");
   auto self = c10::intrusive_ptr<MoodistBackend>::unsafe_reclaim_from_nonowning(this);
   if (t.is_cuda()) {
     if (CudaP2P* p2p = cudaP2P(t.get_device())) {
@@ -787,7 +787,7 @@ c10::intrusive_ptr<c10d::Work> MoodistBackend::recv(std::vector<at::Tensor>& ten
 c10::intrusive_ptr<c10d::Work> MoodistBackend::recvAnysource(std::vector<at::Tensor>& tensors, int tag) {
   TORCH_CHECK(tensors.size() == 1, "moodist: recv takes one tensor");
   at::Tensor t = tensors[0];
-  check_contig(t, "recv tensor");
+  check_contig(t, "recv");
   TORCH_CHECK(!t.is_cuda(), "moodist: a receive from any rank is served for CPU tensors (name the source for a CUDA tensor)");
   auto self = c10::intrusive_ptr<MoodistBackend>::unsafe_reclaim_from_nonowning(this);
   std::shared_ptr<void> posted;

@@ -366,3 +366,46 @@ def _random_operations(rank, world, port, seed, count):
 @pytest.mark.parametrize("world,seed", [(4, 1), (3, 3)])
 def test_random_sequences_of_operations(world, seed):
     run_ranks(_random_operations, world, seed, 250, timeout=300)
+
+
+def _any_dtype(rank, world, port):
+    dist = init_moodist(rank, world, port)
+    # operations that only move bytes take every dtype, also those that cannot be reduced
+    for dtype in (torch.float8_e4m3fn, torch.float8_e5m2, torch.uint16, torch.uint32, torch.complex128, torch.bool):
+        mine = (torch.arange(24) % 2 + rank).to(torch.float32).to(dtype)
+        first = (torch.arange(24) % 2).to(torch.float32).to(dtype)
+        out = torch.zeros(24 * world).to(dtype)
+        dist.all_gather_into_tensor(out, mine)
+        assert torch.equal(out.view(torch.uint8).view(world, -1)[rank], mine.view(torch.uint8)), dtype
+        assert torch.equal(out.view(torch.uint8).view(world, -1)[0], first.view(torch.uint8)), dtype
+        got = mine.clone()
+        dist.broadcast(got, 0)
+        assert torch.equal(got.view(torch.uint8), first.view(torch.uint8)), dtype
+        swapped = torch.zeros(24).to(dtype)
+        dist.all_to_all_single(swapped, mine)
+        if rank == 0:
+            dist.send(mine, 1)
+        elif rank == 1:
+            dist.recv(got, 0)
+            assert torch.equal(got.view(torch.uint8), first.view(torch.uint8)), dtype
+    with pytest.raises(RuntimeError, match="unsupported dtype"):
+        dist.all_reduce(torch.ones(8).to(torch.float8_e4m3fn))
+    # views that are not contiguous are refused by name before anything is sent
+    grid = torch.zeros(6, 6)
+    with pytest.raises(RuntimeError, match="all_reduce tensor must be contiguous"):
+        dist.all_reduce(grid.t())
+    with pytest.raises(RuntimeError, match="broadcast tensor must be contiguous"):
+        dist.broadcast(grid[::2, 1::2], 0)
+    if rank == 0:
+        with pytest.raises(RuntimeError, match="send tensor must be contiguous"):
+            dist.send(grid.t(), 1)
+    x = torch.tensor(float(rank))  # no dimensions, and no elements
+    dist.all_reduce(x)
+    assert x.item() == sum(range(world))
+    dist.all_reduce(torch.empty(0))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_moving_operations_take_any_dtype_and_views_are_refused():
+    run_ranks(_any_dtype, 3, timeout=120)
