@@ -218,3 +218,69 @@ def _successive_groups(rank, world, port):
 
 def test_compile_op_and_queue_on_successive_groups():
     run_ranks(_successive_groups, 2, timeout=120)
+
+
+def _split_box(box, rng, depth):
+    offset, shape = box
+    dims = [d for d in range(len(shape)) if shape[d] > 1]
+    if depth == 0 or not dims or rng.random() < 0.2:
+        return [box]
+    d = rng.choice(dims)
+    cut = rng.randrange(1, shape[d])
+    low = (list(offset), list(shape))
+    low[1][d] = cut
+    high = (list(offset), list(shape))
+    high[0][d] += cut
+    high[1][d] -= cut
+    return _split_box(low, rng, depth - 1) + _split_box(high, rng, depth - 1)
+
+
+def _random_reshards(rank, world, port, seed, count):
+    import random
+
+    dist = init_moodist(rank, world, port)
+    import moodist_b200 as moodist
+
+    pg = moodist.get_backend(device="cpu")
+    rng = random.Random(seed)  # the same on every rank: all of them know every rank's boxes
+    for case in range(count):
+        nd = rng.randint(1, 4)
+        shape = [rng.randint(1, (200, 40, 12, 7)[nd - 1]) for _ in range(nd)]
+        dtype = rng.choice([torch.float32, torch.bfloat16, torch.int64, torch.uint8, torch.float64])
+        full = torch.randint(0, 200, shape, generator=torch.Generator().manual_seed(seed * 1000 + case)).to(dtype)
+        # inputs: the tensor cut into up to 16 boxes dealt to random ranks, some of them held by a second rank too;
+        # outputs: up to three arbitrary boxes per rank, which straddle the inputs as they please
+        pieces = _split_box(([0] * nd, shape), rng, rng.randint(0, 4))
+        held = {r: [] for r in range(world)}
+        for piece in pieces:
+            held[rng.randrange(world)].append(piece)
+            second = rng.randrange(world)
+            if rng.random() < 0.2 and piece not in held[second]:
+                held[second].append(piece)
+        wanted = {r: [] for r in range(world)}
+        for r in range(world):
+            for _ in range(rng.randint(0, 3)):
+                offset = [rng.randrange(s) for s in shape]
+                wanted[r].append((offset, [rng.randint(1, s - o) for s, o in zip(shape, offset)]))
+
+        def boxes(items):
+            return [{"offset": list(o), "shape": list(s)} for o, s in items] or None
+
+        op = moodist.compile_op(pg, shape=tuple(shape), dtype=dtype, inputs=boxes(held[rank]), outputs=boxes(wanted[rank]))
+        for it in range(2):
+            src = full + it if dtype != torch.uint8 else full
+
+            def cut(box):
+                return src[tuple(slice(o, o + s) for o, s in zip(*box))].contiguous()
+
+            outs = [torch.full(box[1], 99, dtype=dtype) for box in wanted[rank]]
+            op([cut(box) for box in held[rank]], outs).wait()
+            for out, box in zip(outs, wanted[rank]):
+                assert torch.equal(out, cut(box)), (case, it, shape, box, held, wanted)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("direct", ["1", "0"])
+def test_compile_op_random_boxes_in_one_to_four_dimensions(direct):
+    run_ranks(_random_reshards, 3, 7 + int(direct), 40, timeout=240, env={"MOODIST_DIRECT_CPU": direct})
