@@ -296,3 +296,58 @@ def _producers_and_getters(rank, world, port):
 
 def test_many_producers_two_getters_exactly_once_in_order():
     run_ranks(_producers_and_getters, 4, timeout=240)
+
+
+def _multicast_transactions(rank, world, port, seed):
+    """Every rank puts single items and transactions of 1-6 items (objects and tensors mixed) into one multicast
+    queue that lives on all ranks but the last.  Every location must receive every item, each producer's items
+    in the order it put them, and the items of a transaction next to one another although the other ranks put
+    at the same time."""
+    import random
+
+    dist = init_moodist(rank, world, port)
+    import moodist_b200 as moodist
+
+    pg = moodist.get_backend(device="cpu")
+    q = moodist.Queue(pg, location=list(range(world - 1)), name="multicast-transactions")
+    rng = random.Random(seed + rank)
+    total = 0
+    for t in range(60):
+        k = rng.randint(1, 6)
+        if rng.random() < 0.5:
+            with q.transaction() as tx:
+                for i in range(k):
+                    if rng.random() < 0.5:
+                        tx.put_object(("together", rank, t, i, k))
+                    else:
+                        tx.put_tensor(torch.tensor([rank, t, i, k]))
+        else:
+            for i in range(k):
+                q.put_object(("single", rank, t, i, k))
+        total += k
+    counts = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(counts, torch.tensor([total]))
+    if rank < world - 1:
+        items = []
+        for _ in range(int(sum(c.item() for c in counts))):
+            item = q.get_tensor(timeout=30)
+            items.append(moodist.deserialize(item) if item.dtype == torch.uint8 else ("together", *item.tolist()))
+        assert q.qsize() == 0
+        last = {}
+        at = 0
+        while at < len(items):
+            kind, producer, t, i, k = items[at]
+            assert last.get(producer, (-1, -1)) < (t, i), (producer, last.get(producer), t, i)
+            if kind == "together":
+                assert items[at:at + k] == [("together", producer, t, j, k) for j in range(k)], items[at:at + k]
+                at += k
+                last[producer] = (t, k - 1)
+            else:
+                at += 1
+                last[producer] = (t, i)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_multicast_queue_keeps_concurrent_transactions_together():
+    run_ranks(_multicast_transactions, 4, 5, timeout=240)
