@@ -316,3 +316,71 @@ def test_rendezvous_port_in_use_is_reported_at_once():
         assert time.time() - t0 < 5  # not after the 30 s it would take to notice that nobody joins
     with pytest.raises(RuntimeError, match="bad rank"):
         moodist.TcpStore("127.0.0.1", port, "busy", 2, 5, timedelta(seconds=2))
+
+
+def _random_store_operations(rank, world, port, seed, break_every, steps):
+    """Random operations per rank on keys only this rank writes, checked against a dictionary; then a counter
+    that everybody adds to.  With `break_every`, every so many messages are lost together with their connection:
+    retransmission must apply an add, a compare_set or a delete exactly once."""
+    import os
+    import random
+
+    import moodist_b200
+
+    store = moodist_b200.TcpStore("127.0.0.1", port, "random", world, rank, timedelta(seconds=60))
+    store.set(f"up{rank}", b"1")
+    store.wait([f"up{r}" for r in range(world)])
+    if break_every:
+        store._inject_faults(break_every)
+    rng = random.Random(seed * 100 + rank)
+    model = {}
+    for step in range(steps):
+        key = f"rank{rank}/key{rng.randrange(30)}"
+        held = model.get(key)
+        op = rng.choice(["set", "get", "add", "compare_set", "delete", "check", "append", "multi"])
+        if op == "set":
+            model[key] = os.urandom(rng.choice([0, 1, 10, 1000, 70000]))
+            store.set(key, model[key])
+        elif op == "get" and held is not None:
+            assert store.get(key) == held, (step, key)
+        elif op == "add" and (held is None or held.lstrip(b"-").isdigit()):
+            delta = rng.randint(-5, 5)
+            expected = int(held or b"0") + delta
+            assert store.add(key, delta) == expected, (step, key)
+            model[key] = str(expected).encode()
+        elif op == "compare_set":
+            new = os.urandom(5)
+            if held is None or rng.random() < 0.5:  # an absent key matches an empty expectation
+                assert store.compare_set(key, held or b"", new) == new, (step, key)
+                model[key] = new
+            else:
+                assert store.compare_set(key, held + b"?", new) == held, (step, key)
+        elif op == "delete":
+            assert store.delete_key(key) == (held is not None), (step, key)
+            model.pop(key, None)
+        elif op == "check":
+            assert store.check([key]) == (held is not None), (step, key)
+        elif op == "append":
+            more = os.urandom(3)
+            store.append(key, more)
+            model[key] = (held or b"") + more
+        elif op == "multi":
+            keys = [f"rank{rank}/key{rng.randrange(30)}" for _ in range(3)]
+            values = [os.urandom(4) for _ in keys]
+            store.multi_set(keys, values)
+            model.update(zip(keys, values))
+            assert store.multi_get(list(model)[:5]) == list(model.values())[:5], step
+    for _ in range(50):
+        store.add("shared", 1)
+    breaks = store._injected_breaks()
+    store._inject_faults(0)
+    store.set(f"done{rank}", str(len(model)).encode())
+    store.wait([f"done{r}" for r in range(world)])
+    assert int(store.get("shared")) == 50 * world
+    assert store.num_keys() == sum(int(store.get(f"done{r}")) for r in range(world)) + 2 * world + 1
+    assert (breaks > 20) == bool(break_every), breaks
+
+
+@pytest.mark.parametrize("break_every,steps", [(0, 1000), (7, 250)])
+def test_random_store_operations_match_a_dictionary(break_every, steps):
+    run_ranks(_random_store_operations, 4, 3, break_every, steps, port=free_port(), timeout=180)
