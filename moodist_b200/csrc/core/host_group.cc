@@ -434,29 +434,52 @@ class HostGroupImpl final : public HostGroup {
   // messages
   // ---------------------------------------------------------------------------------------------
   void set_handler(uint32_t op, Handler h) override {
+    std::vector<std::pair<uint32_t, Handler>> one;
+    one.emplace_back(op, std::move(h));
+    set_handlers(std::move(one));
+  }
+
+  // Messages may arrive before their subsystem registers (a peer may be a step ahead). They wait in `unhandled_`,
+  // in arrival order over all message types, and are replayed on the engine thread once handlers exist. Until that
+  // replay has run, new arrivals join the waiting ones instead of overtaking them, and a subsystem registers all
+  // of its handlers in one call, so that messages of different types keep their order too (a queue's put,
+  // then the commit of its transaction, then the next put).
+  void set_handlers(std::vector<std::pair<uint32_t, Handler>> list) override {
+    bool replay = false;
     {
       std::lock_guard<std::mutex> lk(handlers_mu_);
-      handlers_[op] = std::move(h);
-    }
-    // messages of this type that arrived before the subsystem registered (a peer may be a step ahead)
-    run_on_engine([this, op] {
-      auto it = unhandled_.find(op);
-      if (it == unhandled_.end()) return;
-      auto list = std::move(it->second);
-      unhandled_.erase(it);
-      Handler h;
-      {
-        std::lock_guard<std::mutex> lk(handlers_mu_);
-        h = handlers_[op];
+      for (auto& [op, h] : list) {
+        replay |= (bool)h;
+        handlers_[op] = std::move(h);
       }
-      for (auto& [src, body] : list) {
+      if (replay) ++pending_replays_;
+    }
+    if (!replay) return;
+    run_on_engine([this] {
+      std::deque<Parked> keep;
+      while (!unhandled_.empty()) {
+        Parked m = std::move(unhandled_.front());
+        unhandled_.pop_front();
+        Handler h;
+        {
+          std::lock_guard<std::mutex> lk(handlers_mu_);
+          auto it = handlers_.find(m.op);
+          if (it != handlers_.end()) h = it->second;
+        }
+        if (!h) {
+          keep.push_back(std::move(m));
+          continue;
+        }
         try {
-          Reader r(body);
-          h(src, r);
+          Reader r(m.body);
+          h(m.src, r);
         } catch (const std::exception& e) {
-          set_error(strf("bad message from rank %d: %s", src, e.what()));
+          set_error(strf("bad message from rank %d: %s", m.src, e.what()));
         }
       }
+      unhandled_ = std::move(keep);
+      std::lock_guard<std::mutex> lk(handlers_mu_);
+      --pending_replays_;
     });
   }
 
@@ -895,19 +918,19 @@ class HostGroupImpl final : public HostGroup {
         default: break;
       }
       Handler h;
+      bool replay_pending;
       {
         std::lock_guard<std::mutex> lk(handlers_mu_);
         auto it = handlers_.find(op);
         if (it != handlers_.end()) h = it->second;
+        replay_pending = pending_replays_ > 0;
       }
-      if (h) {
+      if (h && !(replay_pending && !unhandled_.empty())) {
         h(src, r);
+      } else if (unhandled_.size() < 65536) {
+        unhandled_.push_back(Parked{op, src, Bytes(r.p, r.end)});  // see set_handlers()
       } else {
-        auto& list = unhandled_[op];
-        if (list.size() < 65536)
-          list.emplace_back(src, Bytes(r.p, r.end));
-        else
-          log_error("engine: dropping message type %u from rank %d: nobody handles it", op, src);
+        log_error("engine: dropping message type %u from rank %d: nobody handles it", op, src);
       }
     } catch (const std::exception& e) {
       set_error(strf("bad message from rank %d: %s", src, e.what()));
@@ -1027,7 +1050,13 @@ class HostGroupImpl final : public HostGroup {
   static constexpr size_t kEagerSendBytes = 64 << 10;
   std::map<uint32_t, Offer> offers_;  // large sends waiting to be fetched (engine thread)
   uint32_t next_offer_ = 0;
-  std::map<uint32_t, std::deque<std::pair<int, Bytes>>> unhandled_;
+  struct Parked {
+    uint32_t op;
+    int src;
+    Bytes body;
+  };
+  std::deque<Parked> unhandled_;  // engine thread only
+  int pending_replays_ = 0;       // guarded by handlers_mu_
   std::list<PendingRecv> pending_recvs_;
   std::vector<double> last_heard_;
   std::vector<int> peer_shutdown_;

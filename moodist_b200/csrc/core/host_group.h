@@ -102,6 +102,8 @@ class HostGroup {
   // ---- two-sided engine messages for subsystems layered on top (Queue, compile_op) ----
   using Handler = std::function<void(int src, Reader& body)>;  // runs on the engine thread
   virtual void set_handler(uint32_t op, Handler h) = 0;
+  // several at once: messages of these types that came early are then replayed in the order they arrived in
+  virtual void set_handlers(std::vector<std::pair<uint32_t, Handler>> handlers) = 0;
   virtual void send_message(int dst, uint32_t op, Bytes body) = 0;
   // Post a closure to the engine thread.
   virtual void run_on_engine(std::function<void()> fn) = 0;

@@ -128,12 +128,15 @@ class WorkImpl final : public QueueWork {
 class ManagerImpl final : public QueueManager {
  public:
   explicit ManagerImpl(HostGroup& g) : g_(g) {
-    g_.set_handler(kOpCreateQueueNamed, [this](int src, Reader& r) { on_create(src, r); });
-    g_.set_handler(kOpCreateQueueNamedResult, [](int, Reader&) {});
-    g_.set_handler(kOpQueuePut, [this](int src, Reader& r) { on_put(src, r); });
-    g_.set_handler(kOpQueueReadFinished, [this](int src, Reader& r) { on_read_finished(src, r); });
-    g_.set_handler(kOpQueueGet, [this](int src, Reader& r) { on_get(src, r); });
-    g_.set_handler(kOpQueueTransaction, [this](int src, Reader& r) { on_transaction(src, r); });
+    // in one call: what peers sent before this rank made its first queue is replayed in arrival order over all types
+    std::vector<std::pair<uint32_t, HostGroup::Handler>> handlers;
+    handlers.emplace_back(kOpCreateQueueNamed, [this](int src, Reader& r) { on_create(src, r); });
+    handlers.emplace_back(kOpCreateQueueNamedResult, [](int, Reader&) {});
+    handlers.emplace_back(kOpQueuePut, [this](int src, Reader& r) { on_put(src, r); });
+    handlers.emplace_back(kOpQueueReadFinished, [this](int src, Reader& r) { on_read_finished(src, r); });
+    handlers.emplace_back(kOpQueueGet, [this](int src, Reader& r) { on_get(src, r); });
+    handlers.emplace_back(kOpQueueTransaction, [this](int src, Reader& r) { on_transaction(src, r); });
+    g_.set_handlers(std::move(handlers));
   }
 
   std::shared_ptr<Queue> make_queue(const std::vector<int>& locations, bool streaming,

@@ -27,6 +27,7 @@
 
 #include <cstdint>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 #include <new>
 #include <stdexcept>
@@ -292,6 +293,11 @@ class Packer {
     if (Py_REFCNT(obj) != 1) {
       auto [slot, fresh] = memo_.try_emplace(obj, out.size());
       if (!fresh) {
+        if (type == &PyFrozenSet_Type && std::find(open_frozensets_.begin(), open_frozensets_.end(), obj) != open_frozensets_.end()) {
+          // it exists only once its members do, so a reader could not hand it to the member that wants it
+          PyErr_SetString(PyExc_ValueError, "moodist.serialize: a frozenset that contains itself cannot be serialized");
+          throw PyError{};
+        }
         out[*slot] |= 0x80;
         byte(T_OFFSET);
         u64(*slot);
@@ -309,6 +315,7 @@ class Packer {
 
  private:
   PtrMap memo_;
+  std::vector<PyObject*> open_frozensets_;  // those whose members are being written
   std::vector<Ref> keepalive_;  // temporaries (reduce results) must outlive the memo entries that point at them
   int depth_ = 0;
 
@@ -404,12 +411,14 @@ class Packer {
     if (type == &PySet_Type || type == &PyFrozenSet_Type) {
       byte(type == &PySet_Type ? T_SET : T_FROZENSET);
       u64(PySet_GET_SIZE(obj));
+      if (type == &PyFrozenSet_Type) open_frozensets_.push_back(obj);
       Ref it = checked(PyObject_GetIter(obj));
       while (PyObject* item = PyIter_Next(it.p)) {
         Ref hold(item);
         pack(item);
       }
       if (PyErr_Occurred()) throw PyError{};
+      if (type == &PyFrozenSet_Type) open_frozensets_.pop_back();
       return;
     }
     // classes of any metaclass are globals (the reference only recognises exact `type`, so e.g. numpy.dtype fails there)
@@ -622,9 +631,27 @@ class Unpacker {
       case T_TUPLE: {
         int64_t n = unpack_len();
         Ref tup = checked(PyTuple_New(n));
-        // a tuple can only reach itself through a mutable member, which is stored on its own
+        if (store) {
+          // A tuple can contain itself through a list, a dict or an object, and the writer then refers to it from
+          // inside (as the reference's reader expects, which also stores a tuple before filling it: wrapper/
+          // serialize/serialize_object.cc:1034). So a referenced tuple is handed out early like a list, with None
+          // in every slot that has no member yet. The collector stops tracking a tuple of atoms if it runs in
+          // between; the tuple is tracked again once it is whole, since it may hold containers by then.
+          for (int64_t i = 0; i < n; ++i) {
+            Py_INCREF(Py_None);
+            PyTuple_SET_ITEM(tup.p, i, Py_None);
+          }
+          remember(offset, tup.p);
+          for (int64_t i = 0; i < n; ++i) {
+            PyObject* item = unpack();
+            PyObject* placeholder = PyTuple_GET_ITEM(tup.p, i);
+            PyTuple_SET_ITEM(tup.p, i, item);
+            Py_DECREF(placeholder);
+          }
+          if (!PyObject_GC_IsTracked(tup.p)) PyObject_GC_Track(tup.p);
+          return tup.release();
+        }
         for (int64_t i = 0; i < n; ++i) PyTuple_SET_ITEM(tup.p, i, unpack());
-        if (store) remember(offset, tup.p);
         return tup.release();
       }
       case T_DICT: {

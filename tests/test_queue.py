@@ -351,3 +351,36 @@ def _multicast_transactions(rank, world, port, seed):
 
 def test_multicast_queue_keeps_concurrent_transactions_together():
     run_ranks(_multicast_transactions, 4, 5, timeout=240)
+
+
+def _owner_comes_late(rank, world, port):
+    """The producers put (single items, a transaction, more single items) before the owning rank has made its
+    first queue: their messages wait on the owner, and must come out in the order in which each producer sent
+    them, the transaction's commit between the puts around it."""
+    dist = init_moodist(rank, world, port)
+    import moodist_b200 as moodist
+
+    pg = moodist.get_backend(device="cpu")
+    if rank == 0:
+        time.sleep(0.7)
+    q = moodist.Queue(pg, location=0, name="late-owner")
+    if rank != 0:
+        for i in range(20):
+            q.put_object((rank, i))
+        with q.transaction() as tx:
+            for i in range(20, 25):
+                tx.put_object((rank, i))
+        for i in range(25, 60):
+            q.put_object((rank, i))
+    else:
+        seen = {}
+        for _ in range(60 * (world - 1)):
+            producer, i = q.get_object(timeout=30)
+            assert seen.get(producer, -1) == i - 1, (producer, seen.get(producer), i)
+            seen[producer] = i
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_messages_that_arrive_before_the_owner_made_its_queue_keep_their_order():
+    run_ranks(_owner_comes_late, 3, timeout=120)

@@ -81,6 +81,120 @@ def test_circular_reference():
     assert r["self"] is r
 
 
+class _Pair:
+    def __init__(self):
+        self.a = self.b = None
+
+
+class _HashableHolder:
+    held = None
+
+    def __hash__(self):
+        return 7
+
+
+def test_tuples_that_contain_themselves_keep_their_identity():
+    # the writer refers to the tuple from inside its own members; the reader hands a referenced tuple out before
+    # it is whole, as it does with a list (and as the reference's reader does)
+    inner = []  # a single reference: not in the writer's memo
+    t = (inner,)
+    inner.extend([t, t])
+    r = roundtrip(t)
+    assert r[0][0] is r and r[0][1] is r and len(r) == 1 and len(r[0]) == 2
+    import gc
+
+    assert gc.is_tracked(r)  # it is part of a cycle, so the collector must see it
+    shared = []
+    t = (shared, "x")
+    shared.append(t)
+    r = roundtrip([t, t, shared])
+    assert r[0] is r[1] and r[2][0] is r[0] and r[0][0] is r[2] and r[0][1] == "x"
+    node = _Pair()
+    node.a = (node, {"back": node})
+    node.b = node.a
+    r = roundtrip(node)
+    assert r.a is r.b and r.a[0] is r and r.a[1]["back"] is r
+    # a frozenset has no such early form: refused when writing, not when some other rank reads
+    holder = _HashableHolder()
+    holder.held = frozenset([holder, 1])
+    with pytest.raises(ValueError, match="frozenset that contains itself"):
+        pack([holder.held])
+    assert roundtrip([frozenset([1, 2]), frozenset([1, 2])]) == [frozenset([1, 2])] * 2
+
+
+def _random_graph(rng, n):
+    nodes = []
+    for _ in range(n):
+        kind = rng.choice(["list", "dict", "pair", "frozenset", "bytes", "str", "int", "float", "tuple"])
+        if kind == "list":
+            nodes.append([])
+        elif kind == "dict":
+            nodes.append({})
+        elif kind == "pair":
+            nodes.append(_Pair())
+        elif kind == "frozenset":
+            nodes.append(frozenset(rng.sample(range(100), rng.randint(0, 4))))
+        elif kind == "bytes":
+            nodes.append(bytes(rng.randrange(256) for _ in range(rng.randint(0, 300))))
+        elif kind == "str":
+            nodes.append("s" * rng.randint(0, 5) + str(rng.random()))
+        elif kind == "int":
+            nodes.append(rng.choice([0, -1, 2**31, 2**63, -(2**64), 10**40, rng.randrange(1000)]))
+        elif kind == "float":
+            nodes.append(rng.random())
+        else:  # tuples of earlier nodes: they get into cycles through the lists, dicts and pairs filled below
+            nodes.append(tuple(rng.choice(nodes) for _ in range(rng.randint(0, 3))) if nodes else ())
+    for node in nodes:
+        if isinstance(node, list):
+            node.extend(rng.choice(nodes) for _ in range(rng.randint(0, 5)))
+        elif isinstance(node, dict):
+            for _ in range(rng.randint(0, 4)):
+                node[rng.choice(["k1", "k2", 3, (1, 2), 4.5, b"z"])] = rng.choice(nodes)
+        elif isinstance(node, _Pair):
+            node.a, node.b = rng.choice(nodes), rng.choice(nodes)
+    return [nodes[0], nodes[-1], nodes]
+
+
+def _shape_with_identities(root):
+    """The graph as a flat list in traversal order; a container met again appears as the number of its first visit."""
+    seen, out, todo = {}, [], [root]
+    while todo:
+        o = todo.pop()
+        if isinstance(o, (list, dict, _Pair, tuple)):
+            if id(o) in seen:
+                out.append(("again", seen[id(o)]))
+                continue
+            seen[id(o)] = len(seen)
+        if isinstance(o, (list, tuple)):
+            out.append((type(o).__name__, len(o)))
+            todo.extend(reversed(o))
+        elif isinstance(o, dict):
+            out.append(("dict", list(o)))
+            todo.extend(reversed(list(o.values())))
+        elif isinstance(o, _Pair):
+            out.append(("pair",))
+            todo.extend([o.b, o.a])
+        else:
+            out.append((type(o).__name__, o))
+    return out
+
+
+def test_random_object_graphs_with_shared_members_and_cycles():
+    import random
+
+    deep = 0
+    for seed in range(300):
+        rng = random.Random(seed)
+        graph = _random_graph(rng, rng.randint(1, 60))
+        try:
+            back = roundtrip(graph)
+        except RecursionError:  # a chain deeper than the writer's limit: refused, which is fine
+            deep += 1
+            continue
+        assert _shape_with_identities(back) == _shape_with_identities(graph), seed
+    assert deep < 30
+
+
 def test_scalars_and_special_floats():
     for v in (0, 1, -1, 2**7, -(2**7), 2**15, -(2**15) - 1, 2**31, -(2**31) - 1, 2**62, 2**63, -(2**63), 2**200, -(2**200)):
         assert roundtrip(v) == v
